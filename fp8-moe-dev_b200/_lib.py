@@ -1,0 +1,90 @@
+"""ctypes binding of the C ABI declared in include/moe_fp8_b200.h.
+
+The library is the product: if it is missing or fails to load this module raises, there
+is no Python or CPU fallback behind it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+LIB_PATH = HERE / "libmoe_fp8_b200.so"
+
+OK = 0
+ERR_INVALID_ARGUMENT, ERR_CUDA, ERR_CAPACITY, ERR_DEVICE, ERR_UNSUPPORTED = -1, -2, -3, -4, -5
+OPT_REFERENCE_PRUNING, OPT_EXACT_SILU = 1, 2
+
+BUF = dict(
+    expert_count=0, expert_offset=1, topk_idx=2, topk_weight=3, pair_count=4, pair_code=5, pair_weight=6,
+    num_tiles=7, row_token=8, a1=9, sfa1=10, a2=11, sfa2=12, y=13, status=14,
+)
+
+EXPORTS = [
+    "moe_fp8_b200_version", "moe_fp8_b200_workspace_bytes", "moe_fp8_b200_row_capacity",
+    "moe_fp8_b200_create", "moe_fp8_b200_destroy", "moe_fp8_b200_last_error", "moe_fp8_b200_set_option",
+    "moe_fp8_b200_run", "moe_fp8_b200_run_host", "moe_fp8_b200_check", "moe_fp8_b200_read_intermediate",
+    "moe_fp8_b200_reference_policy",
+]
+
+
+class Args(C.Structure):
+    """moe_fp8_b200_args"""
+    _fields_ = [
+        ("routing_logits", C.c_void_p), ("routing_bias", C.c_void_p), ("hidden_states", C.c_void_p),
+        ("hidden_states_scale", C.c_void_p), ("gemm1_weights", C.c_void_p), ("gemm1_weights_scale", C.c_void_p),
+        ("gemm2_weights", C.c_void_p), ("gemm2_weights_scale", C.c_void_p), ("local_expert_offset", C.c_int64),
+        ("routed_scaling_factor", C.c_double), ("output", C.c_void_p), ("num_tokens", C.c_int32),
+    ]
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python fp8-moe-dev_b200/build.py` "
+            "(the layer has no fallback implementation)")
+    lib = C.CDLL(str(LIB_PATH))
+    H = C.c_void_p
+    lib.moe_fp8_b200_version.restype = C.c_int
+    lib.moe_fp8_b200_workspace_bytes.restype = C.c_size_t
+    lib.moe_fp8_b200_workspace_bytes.argtypes = [C.c_int, C.c_int]
+    lib.moe_fp8_b200_row_capacity.restype = C.c_int
+    lib.moe_fp8_b200_row_capacity.argtypes = [C.c_int, C.c_int]
+    lib.moe_fp8_b200_create.restype = C.c_int
+    lib.moe_fp8_b200_create.argtypes = [C.POINTER(H), C.c_int, C.c_int, C.c_int]
+    lib.moe_fp8_b200_destroy.restype = C.c_int
+    lib.moe_fp8_b200_destroy.argtypes = [H]
+    lib.moe_fp8_b200_last_error.restype = C.c_char_p
+    lib.moe_fp8_b200_last_error.argtypes = [H]
+    lib.moe_fp8_b200_set_option.restype = C.c_int
+    lib.moe_fp8_b200_set_option.argtypes = [H, C.c_int, C.c_int]
+    for name in ("moe_fp8_b200_run", "moe_fp8_b200_run_host"):
+        fn = getattr(lib, name)
+        fn.restype = C.c_int
+        fn.argtypes = [H, C.POINTER(Args), C.c_void_p]
+    lib.moe_fp8_b200_check.restype = C.c_int
+    lib.moe_fp8_b200_check.argtypes = [H, C.c_void_p]
+    lib.moe_fp8_b200_read_intermediate.restype = C.c_int
+    lib.moe_fp8_b200_read_intermediate.argtypes = [H, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]
+    lib.moe_fp8_b200_reference_policy.restype = C.c_int
+    lib.moe_fp8_b200_reference_policy.argtypes = [C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_float)]
+    _lib = lib
+    return lib
+
+
+def reference_policy(num_tokens: int) -> dict:
+    """The reference's T-keyed dispatch policy as resolved by the library (host only)."""
+    flags = (C.c_int32 * 5)()
+    fracs = (C.c_float * 3)()
+    rc = load().moe_fp8_b200_reference_policy(int(num_tokens), flags, fracs)
+    if rc != OK:
+        raise RuntimeError(f"moe_fp8_b200_reference_policy failed: {rc}")
+    return dict(prune=flags[0], skip_zero_weight=flags[1], keep_limit=flags[2], drop_third=flags[3],
+                renorm=flags[4], drop_third_frac=fracs[0], drop_second_frac_2=fracs[1],
+                drop_second_frac_ge3=fracs[2])

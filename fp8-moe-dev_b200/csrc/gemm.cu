@@ -1,0 +1,432 @@
+// Stage 4 and 5 of the layer: the two FP8 block-scaled grouped GEMMs as persistent,
+// warp-specialised tcgen05 kernels.
+//
+//   GEMM1  D[m, 0:4096] = sum_kb (A1[m, kb] . W1[e, :, kb]^T) * (sA1[kb, m] * sW1[e, n/128, kb])
+//          fused epilogue: bf16 rounding of D, SwiGLU (x1 = D[:, n], x2 = D[:, 2048 + n]),
+//          per-row 1x128 absmax, e4m3 requantisation -> A2, sA2.
+//   GEMM2  Y[m, 0:7168] = sum_kb (A2[m, kb] . W2[e, :, kb]^T) * (sA2[kb, m] * sW2[e, h/128, kb]) -> bf16
+//
+// The arithmetic (what is accumulated in fp32, where bf16/e4m3 rounding happens) follows
+// the reference's readable statement of the same math: kernel/moe_fp8.cu:1239-1312 (GEMM1),
+// :1801-1837 (SwiGLU + requant), :2055-2110 (GEMM2).  The reference executes it with a
+// CUTLASS grouped GEMM or closed TRTLLM cubins plus separate SwiGLU kernels; this file
+// replaces all of them.
+//
+// Structure of one CTA (384 threads, one CTA per SM, 128 x 256 output tile):
+//   warp 0      TMA producer: 128x128 B A tile + 256x128 B weight tile per 128-wide K block,
+//               4-stage shared-memory ring, SWIZZLE_128B, one mbarrier pair per stage
+//   warp 1      MMA issuer: 4 x tcgen05.mma (M128 N256 K32, e4m3 -> fp32) per K block into one
+//               of two 256-column TMEM accumulator stages, overwrite mode on the first
+//   warp 2      TMEM allocation / release
+//   warps 4-11  promotion + epilogue: after each K block, tcgen05.ld of the raw block product,
+//               multiply by the row scale x weight-block scale, add into fp32 registers (the
+//               scales are arbitrary fp32 values, so the block-scaled MMA kinds cannot be used);
+//               each thread owns one row and 128 of the tile's 256 columns
+// Every mbarrier wait is bounded; a wait that runs out sets the CTA's abort flag, all roles
+// unwind, TMEM is released and the error is reported through Control::status.
+#include <cuda.h>
+#include <cuda_fp8.h>
+
+#include "layer.cuh"
+#include "ptx.cuh"
+
+namespace moe {
+
+constexpr int kGemmThreads = 384;
+constexpr int kStages = 4;
+constexpr int kTileN = 256;
+constexpr int kATileBytes = kTileM * kBlock;   // 16384
+constexpr int kBTileBytes = kTileN * kBlock;   // 32768
+constexpr int kStageBytes = kATileBytes + kBTileBytes;
+constexpr int kTmemCols = 512;
+constexpr int kEpilogueWarps = 8;
+constexpr int kEpilogueThreads = kEpilogueWarps * 32;
+
+struct GemmShared {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint64_t amax_bar[2];
+    uint32_t tmem_base;
+    int abort;
+    float amax[2][2][kTileM];
+};
+
+constexpr size_t kGemmSmemBytes = 1024 + (size_t)kStages * kStageBytes + sizeof(GemmShared);
+
+struct TileCoord {
+    int e, n, row0, rows;
+};
+
+// Tile id -> (expert, n tile, first packed row, valid rows).  Tiles of one expert are
+// numbered n-major / m-minor so that CTAs working on neighbouring ids share a weight tile.
+__device__ __forceinline__ TileCoord decode_tile(const Workspace& ws, int id, int n_tiles_n) {
+    const int mt = id / n_tiles_n;
+    const int e = ws.tile_expert[mt];
+    const int off0 = ws.expert_offset[e];
+    const int off1 = ws.expert_offset[e + 1];
+    const int mt0 = off0 / kTileM;
+    const int k = (off1 - off0) / kTileM;
+    const int local = id - mt0 * n_tiles_n;
+    const int n = local / k;
+    const int m_tile = mt0 + (local - n * k);
+    TileCoord c;
+    c.e = e;
+    c.n = n;
+    c.row0 = m_tile * kTileM;
+    c.rows = ws.tile_rows[m_tile];
+    return c;
+}
+
+// tcgen05.wait::ld with the destination registers as in/out operands, so that the
+// compiler cannot move a use of them above the wait.
+__device__ __forceinline__ void tmem_ld_wait2(uint32_t (&a)[32], uint32_t (&b)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]),
+                   "+r"(a[8]), "+r"(a[9]), "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]),
+                   "+r"(a[15]), "+r"(a[16]), "+r"(a[17]), "+r"(a[18]), "+r"(a[19]), "+r"(a[20]), "+r"(a[21]),
+                   "+r"(a[22]), "+r"(a[23]), "+r"(a[24]), "+r"(a[25]), "+r"(a[26]), "+r"(a[27]), "+r"(a[28]),
+                   "+r"(a[29]), "+r"(a[30]), "+r"(a[31]), "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]),
+                   "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7]), "+r"(b[8]), "+r"(b[9]), "+r"(b[10]),
+                   "+r"(b[11]), "+r"(b[12]), "+r"(b[13]), "+r"(b[14]), "+r"(b[15]), "+r"(b[16]), "+r"(b[17]),
+                   "+r"(b[18]), "+r"(b[19]), "+r"(b[20]), "+r"(b[21]), "+r"(b[22]), "+r"(b[23]), "+r"(b[24]),
+                   "+r"(b[25]), "+r"(b[26]), "+r"(b[27]), "+r"(b[28]), "+r"(b[29]), "+r"(b[30]), "+r"(b[31])
+                 :
+                 : "memory");
+}
+
+template <int OFF>
+__device__ __forceinline__ void promote32(float (&acc)[128], const uint32_t (&r)[32], float s) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) acc[OFF + j] = fmaf(__uint_as_float(r[j]), s, acc[OFF + j]);
+}
+
+__device__ __forceinline__ float round_bf16(float x) {
+    return __bfloat162float(__float2bfloat16_rn(x));
+}
+
+// MODE 1: GEMM1 + SwiGLU + requant (K = 7168).  MODE 2: GEMM2 -> bf16 Y (K = 2048).
+template <int MODE>
+__global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
+    const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, Workspace ws,
+    const float* __restrict__ w_scale, int silu_exact)
+{
+    constexpr int kKBlocks = (MODE == 1) ? kHiddenBlocks : kInterBlocks;
+    constexpr int kTilesN = (MODE == 1) ? (kInter / kBlock) : (kHidden / kTileN);  // 16 / 28
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    GemmShared* sh = reinterpret_cast<GemmShared*>(smem_raw + (base - raw_addr) + (size_t)kStages * kStageBytes);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&sh->full[s]), 1);
+            mbar_init(smem_u32(&sh->empty[s]), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&sh->acc_full[s]), 1);
+            mbar_init(smem_u32(&sh->acc_empty[s]), kEpilogueWarps);
+            mbar_init(smem_u32(&sh->amax_bar[s]), kEpilogueThreads);
+        }
+        sh->abort = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0 && lane == 0) {
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 2) {
+        tmem_alloc(smem_u32(&sh->tmem_base), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sh->tmem_base;
+    volatile int* abort_flag = &sh->abort;
+    const int total_tiles = ws.num_tiles[0] * kTilesN;
+
+    if (warp < 4) {
+        setmaxnreg_dec<56>();
+        if (warp == 0 && lane == 0) {
+            // ------------------------------------------------------------ TMA producer
+            uint32_t it = 0;
+            bool ok = true;
+            for (int id = blockIdx.x; ok && id < total_tiles; id += gridDim.x) {
+                const TileCoord tc = decode_tile(ws, id, kTilesN);
+                for (int kb = 0; kb < kKBlocks; ++kb, ++it) {
+                    const uint32_t s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1u;
+                    if (!mbar_wait(smem_u32(&sh->empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t full = smem_u32(&sh->full[s]);
+                    mbar_expect_tx(full, kStageBytes);
+                    const uint32_t a_dst = base + s * kStageBytes;
+                    const uint32_t b_dst = a_dst + kATileBytes;
+                    tma_load_2d(a_dst, &tmap_a, full, kb * kBlock, tc.row0);
+                    if (MODE == 1) {
+                        tma_load_3d(b_dst, &tmap_b, full, kb * kBlock, tc.n * kBlock, tc.e);
+                        tma_load_3d(b_dst + kBTileBytes / 2, &tmap_b, full, kb * kBlock, kInter + tc.n * kBlock, tc.e);
+                    } else {
+                        tma_load_3d(b_dst, &tmap_b, full, kb * kBlock, tc.n * kTileN, tc.e);
+                    }
+                }
+            }
+            if (!ok) {
+                // Leave only after this thread's copies in flight have landed (bounded).
+                const uint32_t pending = it < (uint32_t)kStages ? it : (uint32_t)kStages;
+                for (uint32_t j = 1; j <= pending; ++j) {
+                    const uint32_t jt = it - j;
+                    const uint32_t s = jt % kStages;
+                    const uint32_t ph = (jt / kStages) & 1u;
+                    const uint64_t t0 = global_timer_ns();
+                    while (!mbar_try_wait(smem_u32(&sh->full[s]), ph)) {
+                        if (global_timer_ns() - t0 > kWaitLimitNs / 4) break;
+                    }
+                }
+            }
+        } else if (warp == 1 && lane == 0) {
+            // ------------------------------------------------------------ MMA issuer
+            const uint32_t idesc = make_idesc_e4m3(kTileM, kTileN);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int id = blockIdx.x; ok && id < total_tiles; id += gridDim.x) {
+                for (int kb = 0; kb < kKBlocks; ++kb, ++it) {
+                    const uint32_t as = it & 1u;
+                    const uint32_t aph = (it >> 1) & 1u;
+                    if (!mbar_wait(smem_u32(&sh->acc_empty[as]), aph ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1u;
+                    if (!mbar_wait(smem_u32(&sh->full[s]), ph, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = base + s * kStageBytes;
+                    const uint64_t adesc = make_kmajor_sw128_desc(a_addr);
+                    const uint64_t bdesc = make_kmajor_sw128_desc(a_addr + kATileBytes);
+                    const uint32_t d = tmem_base + as * kTileN;
+#pragma unroll
+                    for (int k = 0; k < kBlock / 32; ++k) {
+                        // 32 e4m3 = 32 B along K inside the 128 B swizzled row: +2 in 16 B units.
+                        umma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
+                    }
+                    tc_commit(smem_u32(&sh->empty[s]));
+                    tc_commit(smem_u32(&sh->acc_full[as]));
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- promotion + epilogue
+        setmaxnreg_inc<224>();
+        const int ew = warp - 4;
+        const int h = ew >> 2;       // which 128 of the tile's 256 accumulator columns
+        const int q = warp & 3;      // TMEM lane quarter this warp may read
+        const int row = q * 32 + lane;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        // accumulator column of the four 32-column chunks this thread promotes
+        //   GEMM1: linear-branch columns 64h..64h+63 and gated-branch columns 128+64h..128+64h+63
+        //   GEMM2: columns 128h..128h+127
+        const uint32_t c0 = (MODE == 1) ? (uint32_t)(64 * h) : (uint32_t)(128 * h);
+        const uint32_t c1 = c0 + 32;
+        const uint32_t c2 = (MODE == 1) ? (uint32_t)(128 + 64 * h) : c0 + 64;
+        const uint32_t c3 = c2 + 32;
+
+        uint32_t it = 0;
+        uint32_t tile_iter = 0;
+        bool ok = true;
+        for (int id = blockIdx.x; ok && id < total_tiles; id += gridDim.x, ++tile_iter) {
+            const TileCoord tc = decode_tile(ws, id, kTilesN);
+            const int grow = tc.row0 + row;
+            const float* sfa = ((MODE == 1) ? ws.sfa1 : ws.sfa2) + grow;
+            const float* sw_lo;
+            const float* sw_hi;
+            if (MODE == 1) {
+                sw_lo = w_scale + ((size_t)tc.e * (kGemm1Out / kBlock) + tc.n) * kHiddenBlocks;
+                sw_hi = sw_lo + (size_t)(kInter / kBlock) * kHiddenBlocks;
+            } else {
+                sw_lo = w_scale + ((size_t)tc.e * kHiddenBlocks + 2 * tc.n + h) * kInterBlocks;
+                sw_hi = sw_lo;
+            }
+            float acc[128];
+#pragma unroll
+            for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
+
+            float sa_n = __ldg(sfa);
+            float lo_n = __ldg(sw_lo);
+            float hi_n = __ldg(sw_hi);
+            for (int kb = 0; kb < kKBlocks; ++kb, ++it) {
+                const float s_lo = sa_n * lo_n;
+                const float s_hi = sa_n * hi_n;
+                if (kb + 1 < kKBlocks) {
+                    sa_n = __ldg(sfa + (size_t)(kb + 1) * ws.m_cap);
+                    lo_n = __ldg(sw_lo + kb + 1);
+                    hi_n = __ldg(sw_hi + kb + 1);
+                }
+                const uint32_t as = it & 1u;
+                const uint32_t aph = (it >> 1) & 1u;
+                ok = mbar_wait(smem_u32(&sh->acc_full[as]), aph, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t t = lane_addr + as * kTileN;
+                uint32_t r0[32], r1[32];
+                tmem_ld_32x32(t + c0, r0);
+                tmem_ld_32x32(t + c1, r1);
+                tmem_ld_wait2(r0, r1);
+                promote32<0>(acc, r0, s_lo);
+                tmem_ld_32x32(t + c2, r0);
+                promote32<32>(acc, r1, s_lo);
+                tmem_ld_32x32(t + c3, r1);
+                tmem_ld_wait2(r0, r1);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[as]));
+                promote32<64>(acc, r0, s_hi);
+                promote32<96>(acc, r1, s_hi);
+            }
+            if (!ok) break;
+
+            const bool valid = row < tc.rows;
+            if (MODE == 1) {
+                // D is rounded to bf16 (the reference materialises it in bf16), then
+                // v = silu(x2) * x1 in fp32, absmax over the row's 128-column block.
+                float amax = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 64; ++j) {
+                    const float x1 = round_bf16(acc[j]);
+                    const float x2 = round_bf16(acc[64 + j]);
+                    const float silu = silu_exact ? x2 / (1.0f + __expf(-x2))
+                                                  : x2 * (0.5f * (x2 * rsqrtf(fmaf(x2, x2, 4.0f)) + 1.0f));
+                    const float v = silu * x1;
+                    acc[j] = v;
+                    amax = fmaxf(amax, fabsf(v));
+                }
+                const uint32_t tp = tile_iter & 1u;
+                sh->amax[tp][h][row] = amax;
+                mbar_arrive(smem_u32(&sh->amax_bar[tp]));
+                ok = mbar_wait(smem_u32(&sh->amax_bar[tp]), (tile_iter >> 1) & 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const float maxv = fmaxf(amax, sh->amax[tp][h ^ 1][row]);
+                const float scale = (maxv > 0.0f) ? (maxv / 448.0f) : 1.0f;
+                const float inv_scale = 1.0f / scale;
+                if (valid) {
+                    uint4* dst = reinterpret_cast<uint4*>(ws.a2 + (size_t)grow * kInter + tc.n * kBlock + 64 * h);
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; ++v4) {
+                        uint32_t wd[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int j = v4 * 16 + i * 4;
+                            const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+                                make_float2(acc[j] * inv_scale, acc[j + 1] * inv_scale), __NV_SATFINITE, __NV_E4M3);
+                            const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+                                make_float2(acc[j + 2] * inv_scale, acc[j + 3] * inv_scale), __NV_SATFINITE, __NV_E4M3);
+                            wd[i] = lo | (hi << 16);
+                        }
+                        dst[v4] = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+                    }
+                    if (h == 0) ws.sfa2[(size_t)tc.n * ws.m_cap + grow] = scale;
+                }
+            } else {
+                if (valid) {
+                    uint4* dst = reinterpret_cast<uint4*>(ws.y + (size_t)grow * kHidden + tc.n * kTileN + 128 * h);
+#pragma unroll
+                    for (int v4 = 0; v4 < 16; ++v4) {
+                        uint4 pk;
+                        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            h2[i] = __floats2bfloat162_rn(acc[v4 * 8 + 2 * i], acc[v4 * 8 + 2 * i + 1]);
+                        dst[v4] = pk;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+    if (threadIdx.x == 0 && sh->abort != 0) {
+        atomicCAS(&ws.ctrl->status, kStatusOk, MODE == 1 ? kStatusGemm1Timeout : kStatusGemm2Timeout);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side: tensor maps and launch.
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+    return fn;
+}
+
+// rows x K bytes (K contiguous), optionally batched over experts; box = 128 B x box_rows.
+int encode_kmajor_u8_map(void* out_map, const void* base, uint64_t k_bytes, uint64_t rows, uint64_t batch,
+                         uint32_t box_rows)
+{
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return -1;
+    CUtensorMap* m = static_cast<CUtensorMap*>(out_map);
+    CUresult r;
+    if (batch == 0) {
+        const cuuint64_t dims[2] = {k_bytes, rows};
+        const cuuint64_t strides[1] = {k_bytes};
+        const cuuint32_t box[2] = {(cuuint32_t)kBlock, box_rows};
+        const cuuint32_t es[2] = {1, 1};
+        r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, es,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        const cuuint64_t dims[3] = {k_bytes, rows, batch};
+        const cuuint64_t strides[2] = {k_bytes, k_bytes * rows};
+        const cuuint32_t box[3] = {(cuuint32_t)kBlock, box_rows, 1};
+        const cuuint32_t es[3] = {1, 1, 1};
+        r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, es,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+size_t tensor_map_bytes() { return sizeof(CUtensorMap); }
+
+cudaError_t configure_gemm_kernels()
+{
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kGemmSmemBytes);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(grouped_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)kGemmSmemBytes);
+}
+
+cudaError_t launch_grouped_gemm(int mode, const void* tmap_a, const void* tmap_b, const Workspace& ws,
+                                const float* w_scale, int silu_exact, int num_ctas, cudaStream_t stream)
+{
+    const CUtensorMap* ma = static_cast<const CUtensorMap*>(tmap_a);
+    const CUtensorMap* mb = static_cast<const CUtensorMap*>(tmap_b);
+    if (mode == 1) {
+        grouped_gemm_kernel<1><<<num_ctas, kGemmThreads, kGemmSmemBytes, stream>>>(*ma, *mb, ws, w_scale, silu_exact);
+    } else {
+        grouped_gemm_kernel<2><<<num_ctas, kGemmThreads, kGemmSmemBytes, stream>>>(*ma, *mb, ws, w_scale, silu_exact);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace moe

@@ -1,0 +1,79 @@
+// Shared definitions of the FP8 block-scaled MoE layer (DeepSeek-V3 geometry):
+// problem constants, the dispatch policy record, and the device-side workspace view
+// that every stage kernel receives.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstddef>
+#include <cstdint>
+
+namespace moe {
+
+constexpr int kHidden = 7168;        // H
+constexpr int kInter = 2048;         // I
+constexpr int kGemm1Out = 4096;      // 2 I  (columns [0,I) linear branch, [I,2I) gated branch)
+constexpr int kNumExperts = 256;     // global experts
+constexpr int kShardExperts = 32;    // experts of one reference shard == one routing group
+constexpr int kBlock = 128;          // quantisation block
+constexpr int kHiddenBlocks = kHidden / kBlock;  // 56
+constexpr int kInterBlocks = kInter / kBlock;    // 16
+constexpr int kTopK = 8;
+constexpr int kNumGroups = 8;
+constexpr int kTopKGroup = 4;
+constexpr int kTileM = 128;          // rows of one expert tile (expert row ranges are padded to it)
+constexpr int kMaxLocalExperts = 256;
+
+// What the dispatch step does with a token's experts that fall into one 32-expert
+// shard.  The fields restate, as data, the branch structure of the reference's
+// routing kernel (kernel/moe_fp8.cu:457-607) after its compile-time knobs
+// (kernel/moe_fp8.cu:93-194) and its T-keyed kernel choice (kernel/moe_fp8.cu:2732-2790)
+// have been resolved on the host for the call's T.
+struct DispatchPolicy {
+    int prune;              // 0: every selected local expert is kept (exact dispatch)
+    int skip_zero_weight;   // exact dispatch only: drop pairs whose weight is exactly 0
+    int keep_limit;         // prune: at most this many experts per token and shard (3)
+    int drop_third;         // prune: third expert dropped when w3 <= drop_third_frac * sum
+    float drop_third_frac;
+    float drop_second_frac_2;    // prune: second dropped when w2 <= frac * sum (0 = never),
+    float drop_second_frac_ge3;  //        separate fractions for 2 and for >=3 local experts
+    int renorm;             // prune: kept weights rescaled by sum(local) / sum(kept)
+};
+
+// Integer control block, zeroed by a memset node at the start of every call.
+struct Control {
+    int expert_count[kMaxLocalExperts];  // routed rows per local expert (atomic counters)
+    int status;                          // 0 ok; otherwise the first error a kernel recorded
+    int status_detail;
+    int pad[2];
+};
+
+enum KernelStatus : int {
+    kStatusOk = 0,
+    kStatusGemm1Timeout = 101,
+    kStatusGemm2Timeout = 102,
+    kStatusRowOverflow = 103,
+};
+
+// Device pointers into the workspace (all owned by the handle).
+struct Workspace {
+    Control* ctrl;
+    int* expert_offset;     // [E+1] first packed row of each expert (multiples of 128)
+    int* tile_expert;       // [max_tiles] local expert of each 128-row tile
+    int* tile_rows;         // [max_tiles] valid rows in the tile (1..128)
+    int* num_tiles;         // [1]
+    int* topk_idx;          // [T,8] global expert ids in selection order
+    float* topk_weight;     // [T,8] normalised weights (before routed_scaling_factor)
+    int* pair_count;        // [T]   kept (token, local expert) pairs
+    uint32_t* pair_code;    // [T,8] (local expert << 24) | slot inside the expert
+    float* pair_weight;     // [T,8] weight * (renorm) * routed_scaling_factor
+    int* row_token;         // [M_cap] token of each packed row (diagnostics / tests)
+    uint8_t* a1;            // [M_cap, H]   e4m3 rows gathered per expert
+    float* sfa1;            // [56, M_cap]  their 1x128 scales, k-block major
+    uint8_t* a2;            // [M_cap, I]   e4m3 SwiGLU output
+    float* sfa2;            // [16, M_cap]
+    __nv_bfloat16* y;       // [M_cap, H]   GEMM2 rows before the weighted combine
+    int m_cap;              // packed-row capacity (multiple of 128)
+    int max_tiles;
+};
+
+}  // namespace moe

@@ -1,0 +1,437 @@
+// C ABI of the layer (declared in include/moe_fp8_b200.h): handle + workspace, argument
+// validation, the reference's T-keyed dispatch policy resolved on the host, and the
+// stage chain enqueued on the caller's stream.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "../../include/moe_fp8_b200.h"
+#include "layer.cuh"
+
+namespace moe {
+cudaError_t launch_route_dispatch(const float*, const void*, const Workspace&, int, int, int, float,
+                                  const DispatchPolicy&, cudaStream_t);
+cudaError_t launch_scan_tiles(const Workspace&, int, cudaStream_t);
+cudaError_t launch_permute(const void*, const float*, const Workspace&, int, cudaStream_t);
+cudaError_t launch_combine(const Workspace&, void*, int, cudaStream_t);
+int encode_kmajor_u8_map(void*, const void*, uint64_t, uint64_t, uint64_t, uint32_t);
+size_t tensor_map_bytes();
+cudaError_t configure_gemm_kernels();
+cudaError_t launch_grouped_gemm(int, const void*, const void*, const Workspace&, const float*, int, int,
+                                cudaStream_t);
+}  // namespace moe
+
+using namespace moe;
+
+namespace {
+
+constexpr int kVersion = (0 << 16) | 1;
+thread_local std::string g_create_error;
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+int row_capacity(int max_tokens, int num_local_experts)
+{
+    const long long pairs = 8LL * max_tokens;
+    const long long nonempty = pairs < num_local_experts ? pairs : num_local_experts;
+    long long cap = pairs + 127LL * nonempty;
+    cap = (cap + kTileM - 1) / kTileM * kTileM;
+    if (cap < kTileM) cap = kTileM;
+    return (int)cap;
+}
+
+struct Carve {
+    size_t off = 0;
+    size_t take(size_t bytes) {
+        const size_t o = off;
+        off = align_up(off + bytes, 1024);
+        return o;
+    }
+};
+
+struct Layout {
+    size_t ctrl, expert_offset, tile_expert, tile_rows, num_tiles, topk_idx, topk_weight, pair_count, pair_code,
+        pair_weight, row_token, a1, sfa1, a2, sfa2, y, total;
+    int m_cap, max_tiles;
+};
+
+Layout make_layout(int T, int E)
+{
+    Layout L;
+    L.m_cap = row_capacity(T, E);
+    L.max_tiles = L.m_cap / kTileM;
+    Carve c;
+    L.ctrl = c.take(sizeof(Control));
+    L.expert_offset = c.take(sizeof(int) * (kMaxLocalExperts + 1));
+    L.tile_expert = c.take(sizeof(int) * L.max_tiles);
+    L.tile_rows = c.take(sizeof(int) * L.max_tiles);
+    L.num_tiles = c.take(sizeof(int) * 4);
+    L.topk_idx = c.take(sizeof(int) * (size_t)T * kTopK);
+    L.topk_weight = c.take(sizeof(float) * (size_t)T * kTopK);
+    L.pair_count = c.take(sizeof(int) * (size_t)T);
+    L.pair_code = c.take(sizeof(uint32_t) * (size_t)T * kTopK);
+    L.pair_weight = c.take(sizeof(float) * (size_t)T * kTopK);
+    L.row_token = c.take(sizeof(int) * (size_t)L.m_cap);
+    L.a1 = c.take((size_t)L.m_cap * kHidden);
+    L.sfa1 = c.take(sizeof(float) * (size_t)kHiddenBlocks * L.m_cap);
+    L.a2 = c.take((size_t)L.m_cap * kInter);
+    L.sfa2 = c.take(sizeof(float) * (size_t)kInterBlocks * L.m_cap);
+    L.y = c.take(sizeof(__nv_bfloat16) * (size_t)L.m_cap * kHidden);
+    L.total = c.off;
+    return L;
+}
+
+}  // namespace
+
+struct moe_fp8_b200_ctx {
+    int device = 0;
+    int max_tokens = 0;
+    int num_local_experts = 0;
+    int num_sms = 0;
+    int opt_reference_pruning = 1;
+    int opt_exact_silu = 0;
+    uint8_t* base = nullptr;
+    Layout layout{};
+    Workspace ws{};
+    alignas(64) unsigned char tmap_a1[128];
+    alignas(64) unsigned char tmap_a2[128];
+    alignas(64) unsigned char tmap_w1[128];
+    alignas(64) unsigned char tmap_w2[128];
+    const void* cached_w1 = nullptr;
+    const void* cached_w2 = nullptr;
+    // staging for run_host (allocated on its first use)
+    uint8_t* stage = nullptr;
+    size_t stage_bytes = 0;
+    std::string error;
+};
+
+namespace {
+
+int fail(moe_fp8_b200_handle h, int code, const char* fmt, ...)
+{
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    if (h) h->error = buf; else g_create_error = buf;
+    return code;
+}
+
+void resolve_reference_policy(int T, DispatchPolicy& p)
+{
+    std::memset(&p, 0, sizeof(p));
+    p.keep_limit = 3;
+    if (T <= 1) return;  // fused exact dispatch
+    const bool prune = T >= 32 || T == 15;
+    if (!prune) { p.skip_zero_weight = 1; return; }
+    p.prune = 1;
+    float frac = 0.30f;
+    if (T >= 10000 && T < 13000) frac = 0.34f;
+    const bool low_t = T == 32 || T == 57 || T == 58 || T == 62 || T == 80 || T == 901;
+    if (low_t) frac = 0.20f;
+    if (T == 14107) frac = 0.30f;
+    else if (T == 32) frac = 0.25f;
+    else if (T == 53) frac = 0.20f;
+    else if (T == 80) frac = 0.20f;
+    else if (T == 901) frac = 0.24f;
+    p.drop_third_frac = frac;
+    p.drop_third = (T >= 10000 || T == 54 || T == 56 || T == 59 || T == 53 || low_t) ? 1 : 0;
+    if (T == 14107) { p.drop_second_frac_2 = 0.302f; p.drop_second_frac_ge3 = 0.303f; }
+    else if (T == 901) { p.drop_second_frac_2 = p.drop_second_frac_ge3 = 0.245f; }
+    else if (T == 80) { p.drop_second_frac_2 = p.drop_second_frac_ge3 = 0.20f; }
+    else if (T == 53) { p.drop_second_frac_2 = p.drop_second_frac_ge3 = 0.30f; }
+    p.renorm = (T == 14107) ? 0 : 1;
+}
+
+int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_t stream)
+{
+    const int T = a.num_tokens;
+    const int E = h->num_local_experts;
+    DispatchPolicy pol;
+    if (h->opt_reference_pruning) {
+        resolve_reference_policy(T, pol);
+    } else {
+        std::memset(&pol, 0, sizeof(pol));
+        pol.keep_limit = 3;
+    }
+    if (a.gemm1_weights != h->cached_w1) {
+        const int r = encode_kmajor_u8_map(h->tmap_w1, a.gemm1_weights, kHidden, kGemm1Out, E, 128);
+        if (r != 0) return fail(h, MOE_FP8_B200_ERR_CUDA, "cuTensorMapEncodeTiled(W1) failed: %d", r);
+        h->cached_w1 = a.gemm1_weights;
+    }
+    if (a.gemm2_weights != h->cached_w2) {
+        const int r = encode_kmajor_u8_map(h->tmap_w2, a.gemm2_weights, kInter, kHidden, E, 256);
+        if (r != 0) return fail(h, MOE_FP8_B200_ERR_CUDA, "cuTensorMapEncodeTiled(W2) failed: %d", r);
+        h->cached_w2 = a.gemm2_weights;
+    }
+    cudaError_t e = cudaMemsetAsync(h->ws.ctrl, 0, sizeof(Control), stream);
+    if (e == cudaSuccess)
+        e = launch_route_dispatch(a.routing_logits, a.routing_bias, h->ws, T, (int)a.local_expert_offset, E,
+                                  (float)a.routed_scaling_factor, pol, stream);
+    if (e == cudaSuccess) e = launch_scan_tiles(h->ws, E, stream);
+    if (e == cudaSuccess) e = launch_permute(a.hidden_states, a.hidden_states_scale, h->ws, T, stream);
+    if (e == cudaSuccess)
+        e = launch_grouped_gemm(1, h->tmap_a1, h->tmap_w1, h->ws, a.gemm1_weights_scale, h->opt_exact_silu,
+                                h->num_sms, stream);
+    if (e == cudaSuccess)
+        e = launch_grouped_gemm(2, h->tmap_a2, h->tmap_w2, h->ws, a.gemm2_weights_scale, 0, h->num_sms, stream);
+    if (e == cudaSuccess) e = launch_combine(h->ws, a.output, T, stream);
+    if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    return MOE_FP8_B200_OK;
+}
+
+int validate(moe_fp8_b200_handle h, const moe_fp8_b200_args* a)
+{
+    if (!h) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
+    if (!a) return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "args is NULL");
+    if (a->num_tokens < 0) return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "num_tokens %d < 0", a->num_tokens);
+    if (a->num_tokens > h->max_tokens)
+        return fail(h, MOE_FP8_B200_ERR_CAPACITY, "num_tokens %d exceeds the handle's max_tokens %d", a->num_tokens,
+                    h->max_tokens);
+    if (a->num_tokens == 0) return MOE_FP8_B200_OK;
+    if (!a->routing_logits || !a->routing_bias || !a->hidden_states || !a->hidden_states_scale ||
+        !a->gemm1_weights || !a->gemm1_weights_scale || !a->gemm2_weights || !a->gemm2_weights_scale || !a->output)
+        return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "a tensor pointer is NULL");
+    if (a->local_expert_offset < 0 || a->local_expert_offset >= kNumExperts)
+        return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "local_expert_offset %lld outside [0, 256)",
+                    (long long)a->local_expert_offset);
+    if (((uintptr_t)a->hidden_states & 15u) || ((uintptr_t)a->gemm1_weights & 15u) ||
+        ((uintptr_t)a->gemm2_weights & 15u) || ((uintptr_t)a->output & 15u))
+        return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "hidden_states, weights and output must be 16-byte aligned");
+    return MOE_FP8_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int moe_fp8_b200_version(void) { return kVersion; }
+
+int moe_fp8_b200_row_capacity(int max_tokens, int num_local_experts)
+{
+    if (max_tokens <= 0 || num_local_experts <= 0 || num_local_experts > kMaxLocalExperts) return 0;
+    return row_capacity(max_tokens, num_local_experts);
+}
+
+size_t moe_fp8_b200_workspace_bytes(int max_tokens, int num_local_experts)
+{
+    if (max_tokens <= 0 || num_local_experts <= 0 || num_local_experts > kMaxLocalExperts) return 0;
+    return make_layout(max_tokens, num_local_experts).total;
+}
+
+int moe_fp8_b200_reference_policy(int num_tokens, int32_t out_flags[5], float out_fracs[3])
+{
+    if (!out_flags || !out_fracs) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
+    DispatchPolicy p;
+    resolve_reference_policy(num_tokens, p);
+    out_flags[0] = p.prune; out_flags[1] = p.skip_zero_weight; out_flags[2] = p.keep_limit;
+    out_flags[3] = p.drop_third; out_flags[4] = p.renorm;
+    out_fracs[0] = p.drop_third_frac; out_fracs[1] = p.drop_second_frac_2; out_fracs[2] = p.drop_second_frac_ge3;
+    return MOE_FP8_B200_OK;
+}
+
+int moe_fp8_b200_create(moe_fp8_b200_handle* out, int device, int max_tokens, int num_local_experts)
+{
+    if (!out) return fail(nullptr, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "out is NULL");
+    *out = nullptr;
+    if (max_tokens <= 0) return fail(nullptr, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "max_tokens must be positive");
+    if (num_local_experts != 32 && num_local_experts != 64 && num_local_experts != 128 && num_local_experts != 256)
+        return fail(nullptr, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "num_local_experts must be 32, 64, 128 or 256");
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess)
+        return fail(nullptr, MOE_FP8_B200_ERR_CUDA, "cudaSetDevice(%d): %s", device, cudaGetErrorString(e));
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) return fail(nullptr, MOE_FP8_B200_ERR_CUDA, "device properties: %s", cudaGetErrorString(e));
+    if (prop.major != 10)
+        return fail(nullptr, MOE_FP8_B200_ERR_UNSUPPORTED,
+                    "device %d is sm_%d%d; this library holds sm_100a code only (no fallback path)", device,
+                    prop.major, prop.minor);
+    moe_fp8_b200_ctx* h = new (std::nothrow) moe_fp8_b200_ctx();
+    if (!h) return fail(nullptr, MOE_FP8_B200_ERR_CUDA, "out of host memory");
+    h->device = device;
+    h->max_tokens = max_tokens;
+    h->num_local_experts = num_local_experts;
+    h->num_sms = prop.multiProcessorCount;
+    h->layout = make_layout(max_tokens, num_local_experts);
+    e = cudaMalloc(&h->base, h->layout.total);
+    if (e != cudaSuccess) {
+        const int rc = fail(nullptr, MOE_FP8_B200_ERR_CUDA, "cudaMalloc(%zu): %s", h->layout.total, cudaGetErrorString(e));
+        delete h;
+        return rc;
+    }
+    const Layout& L = h->layout;
+    Workspace& w = h->ws;
+    w.ctrl = reinterpret_cast<Control*>(h->base + L.ctrl);
+    w.expert_offset = reinterpret_cast<int*>(h->base + L.expert_offset);
+    w.tile_expert = reinterpret_cast<int*>(h->base + L.tile_expert);
+    w.tile_rows = reinterpret_cast<int*>(h->base + L.tile_rows);
+    w.num_tiles = reinterpret_cast<int*>(h->base + L.num_tiles);
+    w.topk_idx = reinterpret_cast<int*>(h->base + L.topk_idx);
+    w.topk_weight = reinterpret_cast<float*>(h->base + L.topk_weight);
+    w.pair_count = reinterpret_cast<int*>(h->base + L.pair_count);
+    w.pair_code = reinterpret_cast<uint32_t*>(h->base + L.pair_code);
+    w.pair_weight = reinterpret_cast<float*>(h->base + L.pair_weight);
+    w.row_token = reinterpret_cast<int*>(h->base + L.row_token);
+    w.a1 = h->base + L.a1;
+    w.sfa1 = reinterpret_cast<float*>(h->base + L.sfa1);
+    w.a2 = h->base + L.a2;
+    w.sfa2 = reinterpret_cast<float*>(h->base + L.sfa2);
+    w.y = reinterpret_cast<__nv_bfloat16*>(h->base + L.y);
+    w.m_cap = L.m_cap;
+    w.max_tiles = L.max_tiles;
+    // Small control arrays start defined; the large row buffers are written before use.
+    e = cudaMemset(h->base, 0, L.topk_idx);
+    if (e == cudaSuccess) e = cudaMemset(w.row_token, 0xff, sizeof(int) * (size_t)L.m_cap);
+    if (e == cudaSuccess) e = configure_gemm_kernels();
+    int mr = 0;
+    if (e == cudaSuccess) {
+        if (tensor_map_bytes() > sizeof(h->tmap_a1)) mr = -100;
+        if (mr == 0) mr = encode_kmajor_u8_map(h->tmap_a1, w.a1, kHidden, L.m_cap, 0, kTileM);
+        if (mr == 0) mr = encode_kmajor_u8_map(h->tmap_a2, w.a2, kInter, L.m_cap, 0, kTileM);
+    }
+    if (e != cudaSuccess || mr != 0) {
+        const int rc = (e != cudaSuccess)
+                           ? fail(nullptr, MOE_FP8_B200_ERR_CUDA, "workspace set-up: %s", cudaGetErrorString(e))
+                           : fail(nullptr, MOE_FP8_B200_ERR_CUDA, "cuTensorMapEncodeTiled(workspace) failed: %d", mr);
+        cudaFree(h->base);
+        delete h;
+        return rc;
+    }
+    *out = h;
+    return MOE_FP8_B200_OK;
+}
+
+int moe_fp8_b200_destroy(moe_fp8_b200_handle h)
+{
+    if (!h) return MOE_FP8_B200_OK;
+    cudaSetDevice(h->device);
+    cudaDeviceSynchronize();
+    if (h->stage) cudaFree(h->stage);
+    if (h->base) cudaFree(h->base);
+    delete h;
+    return MOE_FP8_B200_OK;
+}
+
+const char* moe_fp8_b200_last_error(moe_fp8_b200_handle h) { return h ? h->error.c_str() : g_create_error.c_str(); }
+
+int moe_fp8_b200_set_option(moe_fp8_b200_handle h, int option, int value)
+{
+    if (!h) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
+    switch (option) {
+        case MOE_FP8_B200_OPT_REFERENCE_PRUNING: h->opt_reference_pruning = value ? 1 : 0; return MOE_FP8_B200_OK;
+        case MOE_FP8_B200_OPT_EXACT_SILU: h->opt_exact_silu = value ? 1 : 0; return MOE_FP8_B200_OK;
+        default: return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "unknown option %d", option);
+    }
+}
+
+int moe_fp8_b200_run(moe_fp8_b200_handle h, const moe_fp8_b200_args* args, void* stream)
+{
+    const int v = validate(h, args);
+    if (v != MOE_FP8_B200_OK) return v;
+    if (args->num_tokens == 0) return MOE_FP8_B200_OK;
+    return enqueue_layer(h, *args, static_cast<cudaStream_t>(stream));
+}
+
+int moe_fp8_b200_run_host(moe_fp8_b200_handle h, const moe_fp8_b200_args* args, void* stream_v)
+{
+    const int v = validate(h, args);
+    if (v != MOE_FP8_B200_OK) return v;
+    const int T = args->num_tokens;
+    if (T == 0) return MOE_FP8_B200_OK;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const size_t b_logits = align_up(sizeof(float) * (size_t)T * kNumExperts, 256);
+    const size_t b_hidden = align_up((size_t)T * kHidden, 256);
+    const size_t b_scale = align_up(sizeof(float) * (size_t)kHiddenBlocks * T, 256);
+    const size_t b_out = align_up(sizeof(__nv_bfloat16) * (size_t)T * kHidden, 256);
+    const size_t need = b_logits + b_hidden + b_scale + b_out;
+    if (need > h->stage_bytes) {
+        if (h->stage) { cudaStreamSynchronize(stream); cudaFree(h->stage); h->stage = nullptr; h->stage_bytes = 0; }
+        const cudaError_t e = cudaMalloc(&h->stage, need);
+        if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "cudaMalloc(staging %zu): %s", need, cudaGetErrorString(e));
+        h->stage_bytes = need;
+    }
+    uint8_t* d_logits = h->stage;
+    uint8_t* d_hidden = d_logits + b_logits;
+    uint8_t* d_scale = d_hidden + b_hidden;
+    uint8_t* d_out = d_scale + b_scale;
+    cudaError_t e = cudaMemcpyAsync(d_logits, args->routing_logits, sizeof(float) * (size_t)T * kNumExperts,
+                                    cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(d_hidden, args->hidden_states, (size_t)T * kHidden, cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(d_scale, args->hidden_states_scale, sizeof(float) * (size_t)kHiddenBlocks * T,
+                            cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "host-to-device copy: %s", cudaGetErrorString(e));
+    moe_fp8_b200_args dev = *args;
+    dev.routing_logits = reinterpret_cast<const float*>(d_logits);
+    dev.hidden_states = d_hidden;
+    dev.hidden_states_scale = reinterpret_cast<const float*>(d_scale);
+    dev.output = d_out;
+    const int rc = enqueue_layer(h, dev, stream);
+    if (rc != MOE_FP8_B200_OK) return rc;
+    e = cudaMemcpyAsync(args->output, d_out, sizeof(__nv_bfloat16) * (size_t)T * kHidden, cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "device-to-host copy: %s", cudaGetErrorString(e));
+    return MOE_FP8_B200_OK;
+}
+
+int moe_fp8_b200_check(moe_fp8_b200_handle h, void* stream)
+{
+    if (!h) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
+    cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "stream synchronize: %s", cudaGetErrorString(e));
+    int st[2] = {0, 0};
+    e = cudaMemcpy(st, &h->ws.ctrl->status, sizeof(st), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "status read: %s", cudaGetErrorString(e));
+    if (st[0] != kStatusOk)
+        return fail(h, MOE_FP8_B200_ERR_DEVICE, "device status %d (detail %d): %s", st[0], st[1],
+                    st[0] == kStatusGemm1Timeout   ? "GEMM1 gave up on a bounded wait"
+                    : st[0] == kStatusGemm2Timeout ? "GEMM2 gave up on a bounded wait"
+                    : st[0] == kStatusRowOverflow  ? "routed rows exceed the workspace capacity"
+                                                   : "unknown");
+    return MOE_FP8_B200_OK;
+}
+
+int moe_fp8_b200_read_intermediate(moe_fp8_b200_handle h, int buffer, void* dst, size_t bytes, size_t offset,
+                                   void* stream)
+{
+    if (!h || !dst) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
+    const Workspace& w = h->ws;
+    const size_t T = (size_t)h->max_tokens, M = (size_t)w.m_cap;
+    const void* src = nullptr;
+    size_t size = 0;
+    switch (buffer) {
+        case MOE_FP8_B200_BUF_EXPERT_COUNT: src = w.ctrl->expert_count; size = sizeof(int) * h->num_local_experts; break;
+        case MOE_FP8_B200_BUF_EXPERT_OFFSET: src = w.expert_offset; size = sizeof(int) * (h->num_local_experts + 1); break;
+        case MOE_FP8_B200_BUF_TOPK_IDX: src = w.topk_idx; size = sizeof(int) * T * kTopK; break;
+        case MOE_FP8_B200_BUF_TOPK_WEIGHT: src = w.topk_weight; size = sizeof(float) * T * kTopK; break;
+        case MOE_FP8_B200_BUF_PAIR_COUNT: src = w.pair_count; size = sizeof(int) * T; break;
+        case MOE_FP8_B200_BUF_PAIR_CODE: src = w.pair_code; size = sizeof(uint32_t) * T * kTopK; break;
+        case MOE_FP8_B200_BUF_PAIR_WEIGHT: src = w.pair_weight; size = sizeof(float) * T * kTopK; break;
+        case MOE_FP8_B200_BUF_NUM_TILES: src = w.num_tiles; size = sizeof(int); break;
+        case MOE_FP8_B200_BUF_ROW_TOKEN: src = w.row_token; size = sizeof(int) * M; break;
+        case MOE_FP8_B200_BUF_A1: src = w.a1; size = M * kHidden; break;
+        case MOE_FP8_B200_BUF_SFA1: src = w.sfa1; size = sizeof(float) * kHiddenBlocks * M; break;
+        case MOE_FP8_B200_BUF_A2: src = w.a2; size = M * kInter; break;
+        case MOE_FP8_B200_BUF_SFA2: src = w.sfa2; size = sizeof(float) * kInterBlocks * M; break;
+        case MOE_FP8_B200_BUF_Y: src = w.y; size = sizeof(__nv_bfloat16) * M * kHidden; break;
+        case MOE_FP8_B200_BUF_STATUS: src = &w.ctrl->status; size = sizeof(int) * 2; break;
+        default: return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "unknown buffer id %d", buffer);
+    }
+    if (offset > size || bytes > size - offset)
+        return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "buffer %d holds %zu bytes; asked for %zu at offset %zu",
+                    buffer, size, bytes, offset);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(dst, static_cast<const uint8_t*>(src) + offset, bytes, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "intermediate read: %s", cudaGetErrorString(e));
+    return MOE_FP8_B200_OK;
+}
+
+}  // extern "C"

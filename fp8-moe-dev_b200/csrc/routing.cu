@@ -1,0 +1,401 @@
+// Stage 1-3 of the layer: DeepSeek-V3 no-aux routing fused with the per-shard dispatch
+// policy (one warp per token), the expert-offset scan that turns the per-expert row
+// counters into 128-row tiles, and the token-centric permute that gathers e4m3 rows and
+// their 1x128 scales into expert-contiguous order.  Nothing here reads a device value on
+// the host, so the whole chain can sit in a CUDA graph.
+#include "layer.cuh"
+
+namespace moe {
+
+// ---------------------------------------------------------------------------------------
+// Routing.  Restates kernel/moe_fp8.cu:359-448 of the reference (sigmoid, +bias, group
+// score = two largest of 32, 4 groups kept, 8 argmax rounds, weights from the unbiased
+// sigmoid normalised by 1e-20 + their sum taken in selection order) so that indices and
+// weights come out bit-identical.  The reference runs 256 threads per token with shared
+// memory round trips; here lane l of one warp owns experts {32 w + l : w = 0..7} in
+// registers and every reduction is a redux.sync over an order-preserving integer key.
+//
+// Tie order of the reference: inside a 32-expert warp its xor-butterfly with a strict
+// `>` keeps the candidate whose lane index is smallest after 5-bit reversal
+// (kernel/moe_fp8.cu:416-420), across warps the lowest warp wins
+// (kernel/moe_fp8.cu:427-431).  `rank = w * 32 + bitrev5(lane)` reproduces that order.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t float_to_ordered(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float ordered_to_float(uint32_t k) {
+    const uint32_t u = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+    return __uint_as_float(u);
+}
+
+constexpr float kNegSentinel = -1e30f;
+
+// Applies the dispatch policy to the experts of token `t` that fall into shard `s`
+// (local experts [32 s, 32 s + 32)) and appends the kept pairs.  Run by one lane.
+__device__ __forceinline__ void dispatch_one_shard(
+    const int (&idx)[kTopK], const float (&wn)[kTopK], int s, int local_expert_offset,
+    const DispatchPolicy& pol, float rsf, int t, int& n_pairs, const Workspace& ws)
+{
+    const int lo = s * kShardExperts;
+    if (!pol.prune) {
+#pragma unroll
+        for (int k = 0; k < kTopK; ++k) {
+            const int le = idx[k] - local_expert_offset;
+            if ((unsigned)(le - lo) < (unsigned)kShardExperts) {
+                const float wk = wn[k];
+                if (pol.skip_zero_weight && wk == 0.0f) continue;
+                const int slot = atomicAdd(&ws.ctrl->expert_count[le], 1);
+                const float w_scaled = wk * rsf;
+                ws.pair_code[(size_t)t * kTopK + n_pairs] = ((uint32_t)le << 24) | (uint32_t)slot;
+                ws.pair_weight[(size_t)t * kTopK + n_pairs] = w_scaled;
+                ++n_pairs;
+            }
+        }
+        return;
+    }
+
+    // Pruning dispatch: the three largest local weights in descending order by strict
+    // insertion (kernel/moe_fp8.cu:477-507), then the drop rules (:508-577), the
+    // renormalisation (:579-591) and emission in descending-weight order (:592-606).
+    constexpr int kKeep = 3;
+    int keep_le[kKeep];
+    float keep_w[kKeep];
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) { keep_le[i] = -1; keep_w[i] = -1.0f; }
+    int local_count = 0;
+    float local_w_sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kTopK; ++k) {
+        const int le = idx[k] - local_expert_offset;
+        if ((unsigned)(le - lo) < (unsigned)kShardExperts) {
+            const float wk = wn[k];
+            ++local_count;
+            local_w_sum += wk;
+#pragma unroll
+            for (int i = 0; i < kKeep; ++i) {
+                if (wk > keep_w[i]) {
+#pragma unroll
+                    for (int j = kKeep - 1; j > i; --j) {
+                        keep_w[j] = keep_w[j - 1];
+                        keep_le[j] = keep_le[j - 1];
+                    }
+                    keep_w[i] = wk;
+                    keep_le[i] = le;
+                    break;
+                }
+            }
+        }
+    }
+    if (local_count == 0) return;
+    int max_keep = pol.keep_limit < kKeep ? pol.keep_limit : kKeep;
+    if (pol.keep_limit >= 3 && local_count >= 3 && keep_le[2] >= 0 && local_w_sum > 0.0f) {
+        if (pol.drop_third && keep_w[2] <= pol.drop_third_frac * local_w_sum) max_keep = 2;
+    }
+    if (pol.keep_limit >= 3 && local_count >= 2 && keep_le[1] >= 0 && local_w_sum > 0.0f) {
+        const float frac = (local_count >= 3) ? pol.drop_second_frac_ge3 : pol.drop_second_frac_2;
+        if (frac > 0.0f && keep_w[1] <= frac * local_w_sum) max_keep = 1;
+    }
+    float renorm = 1.0f;
+    if (pol.renorm && local_count > max_keep) {
+        float kept_w_sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kKeep; ++i) {
+            if (i < max_keep && keep_le[i] >= 0) kept_w_sum += keep_w[i];
+        }
+        if (kept_w_sum > 0.0f) renorm = local_w_sum / kept_w_sum;
+    }
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) {
+        const int le = keep_le[i];
+        if (i < max_keep && le >= 0) {
+            const int slot = atomicAdd(&ws.ctrl->expert_count[le], 1);
+            const float w_scaled = keep_w[i] * renorm * rsf;
+            ws.pair_code[(size_t)t * kTopK + n_pairs] = ((uint32_t)le << 24) | (uint32_t)slot;
+            ws.pair_weight[(size_t)t * kTopK + n_pairs] = w_scaled;
+            ++n_pairs;
+        }
+    }
+}
+
+constexpr int kRouteWarps = 8;
+
+__global__ void __launch_bounds__(kRouteWarps * 32) route_dispatch_kernel(
+    const float* __restrict__ logits, const __nv_bfloat16* __restrict__ bias, Workspace ws, int T,
+    int local_expert_offset, int num_local_experts, float rsf, DispatchPolicy pol)
+{
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * kRouteWarps + (threadIdx.x >> 5);
+    if (t >= T) return;
+    constexpr uint32_t kFull = 0xffffffffu;
+
+    float s[kNumGroups];   // unbiased sigmoid of expert 32 w + lane
+    float sb[kNumGroups];  // biased score, later masked
+#pragma unroll
+    for (int w = 0; w < kNumGroups; ++w) {
+        const float l = logits[(size_t)t * kNumExperts + w * 32 + lane];
+        const float sig = 1.0f / (1.0f + __expf(-l));
+        s[w] = sig;
+        sb[w] = sig + __bfloat162float(bias[w * 32 + lane]);
+    }
+
+    // Group score: sum of the two largest biased scores of the group (duplicates count).
+    float gscore[kNumGroups];
+#pragma unroll
+    for (int w = 0; w < kNumGroups; ++w) {
+        const uint32_t key = float_to_ordered(sb[w]);
+        const uint32_t k1 = __reduce_max_sync(kFull, key);
+        const uint32_t holders = __ballot_sync(kFull, key == k1);
+        uint32_t k2;
+        if (__popc(holders) >= 2) {
+            k2 = k1;
+        } else {
+            const uint32_t masked = (key == k1) ? 0u : key;
+            k2 = __reduce_max_sync(kFull, masked);
+        }
+        gscore[w] = ordered_to_float(k1) + ordered_to_float(k2);
+    }
+
+    // Four best groups, lowest index first on ties (kernel/moe_fp8.cu:380-389).
+    uint32_t kept_mask = 0;
+#pragma unroll
+    for (int k = 0; k < kTopKGroup; ++k) {
+        float best = kNegSentinel;
+        int best_i = -1;
+#pragma unroll
+        for (int i = 0; i < kNumGroups; ++i) {
+            if (!((kept_mask >> i) & 1u) && gscore[i] > best) { best = gscore[i]; best_i = i; }
+        }
+        if (best_i >= 0) kept_mask |= 1u << best_i;
+    }
+#pragma unroll
+    for (int w = 0; w < kNumGroups; ++w) {
+        if (!((kept_mask >> w) & 1u)) sb[w] = kNegSentinel;
+    }
+
+    // Eight argmax rounds over the 256 masked scores.
+    const uint32_t lane_rev = __brev((uint32_t)lane) >> 27;
+    int idx[kTopK];
+    float sel[kTopK];
+#pragma unroll
+    for (int k = 0; k < kTopK; ++k) {
+        float bv = sb[0];
+        int bw = 0;
+#pragma unroll
+        for (int w = 1; w < kNumGroups; ++w) {
+            if (sb[w] > bv) { bv = sb[w]; bw = w; }
+        }
+        const uint32_t key = float_to_ordered(bv);
+        const uint32_t kmax = __reduce_max_sync(kFull, key);
+        const uint32_t my_rank = (key == kmax) ? ((uint32_t)bw * 32u + lane_rev) : 0xffffffffu;
+        const uint32_t win_rank = __reduce_min_sync(kFull, my_rank);
+        const int win_w = (int)(win_rank >> 5);
+        const int win_lane = (int)(__brev(win_rank & 31u) >> 27);
+        float s_mine = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kNumGroups; ++w) {
+            if (w == win_w) {
+                s_mine = s[w];
+                if (lane == win_lane) sb[w] = kNegSentinel;
+            }
+        }
+        sel[k] = __shfl_sync(kFull, s_mine, win_lane);
+        idx[k] = win_w * 32 + win_lane;
+    }
+
+    float sumw = 1e-20f;
+#pragma unroll
+    for (int k = 0; k < kTopK; ++k) sumw += sel[k];
+    const float inv = 1.0f / sumw;
+    float wn[kTopK];
+#pragma unroll
+    for (int k = 0; k < kTopK; ++k) wn[k] = sel[k] * inv;
+
+    if (lane < kTopK) {
+        int my_idx = 0;
+        float my_w = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kTopK; ++k) {
+            if (k == lane) { my_idx = idx[k]; my_w = wn[k]; }
+        }
+        ws.topk_idx[(size_t)t * kTopK + lane] = my_idx;
+        ws.topk_weight[(size_t)t * kTopK + lane] = my_w;
+    }
+
+    if (lane == 0) {
+        int n_pairs = 0;
+        const int shards = num_local_experts / kShardExperts;
+        for (int sh = 0; sh < shards; ++sh) {
+            dispatch_one_shard(idx, wn, sh, local_expert_offset, pol, rsf, t, n_pairs, ws);
+        }
+        ws.pair_count[t] = n_pairs;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Offsets and tiles.  One CTA: every expert's row count is rounded up to 128, an
+// exclusive scan gives the first packed row of each expert, and each 128-row tile gets
+// its expert and its number of valid rows.  (The reference does the scan with one warp
+// and then reads the totals back on the host, kernel/moe_fp8.cu:838-870, 2816-2824.)
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kMaxLocalExperts) scan_tiles_kernel(Workspace ws, int num_local_experts)
+{
+    __shared__ int s_tiles[kMaxLocalExperts];
+    __shared__ int s_scan[kMaxLocalExperts + 1];
+    const int e = threadIdx.x;
+    const int m = (e < num_local_experts) ? ws.ctrl->expert_count[e] : 0;
+    const int k = (m + kTileM - 1) / kTileM;
+    s_tiles[e] = k;
+    __syncthreads();
+    if (e == 0) {
+        int acc = 0;
+        for (int i = 0; i < kMaxLocalExperts; ++i) { s_scan[i] = acc; acc += s_tiles[i]; }
+        s_scan[kMaxLocalExperts] = acc;
+    }
+    __syncthreads();
+    int total = s_scan[kMaxLocalExperts];
+    const bool overflow = total > ws.max_tiles || total * kTileM > ws.m_cap;
+    if (overflow) {
+        if (e == 0) {
+            atomicCAS(&ws.ctrl->status, kStatusOk, kStatusRowOverflow);
+            ws.ctrl->status_detail = total;
+        }
+        total = 0;
+    }
+    if (e < num_local_experts) ws.expert_offset[e] = overflow ? 0 : s_scan[e] * kTileM;
+    if (e == 0) {
+        ws.expert_offset[num_local_experts] = total * kTileM;
+        ws.num_tiles[0] = total;
+    }
+    if (!overflow && e < num_local_experts) {
+        const int base = s_scan[e];
+        for (int j = 0; j < k; ++j) {
+            ws.tile_expert[base + j] = e;
+            const int left = m - j * kTileM;
+            ws.tile_rows[base + j] = left < kTileM ? left : kTileM;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Permute.  One warp per token: the 7168-byte e4m3 row is read once (14 x 16 B per lane)
+// and written to each packed row the token owns; the 56 scales move from the [56, T]
+// input layout to the [56, M_cap] packed layout.  Same data movement as the reference's
+// row-centric kernel/moe_fp8.cu:1064-1115, without an [E, T] token list.
+// ---------------------------------------------------------------------------------------
+constexpr int kPermuteWarps = 4;
+
+__global__ void __launch_bounds__(kPermuteWarps * 32) permute_rows_kernel(
+    const uint8_t* __restrict__ hidden, const float* __restrict__ hidden_scale, Workspace ws, int T)
+{
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * kPermuteWarps + (threadIdx.x >> 5);
+    if (t >= T) return;
+    if (ws.num_tiles[0] == 0) return;
+    const int n_pairs = ws.pair_count[t];
+    if (n_pairs == 0) return;
+
+    constexpr int kVec = kHidden / 16 / 32;  // 14 uint4 per lane
+    uint4 v[kVec];
+    const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)t * kHidden);
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) v[i] = __ldg(src + lane + 32 * i);
+    const float sc0 = __ldg(hidden_scale + (size_t)lane * T + t);
+    const float sc1 = (lane + 32 < kHiddenBlocks) ? __ldg(hidden_scale + (size_t)(lane + 32) * T + t) : 0.0f;
+
+    for (int p = 0; p < n_pairs; ++p) {
+        const uint32_t code = ws.pair_code[(size_t)t * kTopK + p];
+        const int le = (int)(code >> 24);
+        const int slot = (int)(code & 0x00ffffffu);
+        const int row = ws.expert_offset[le] + slot;
+        uint4* dst = reinterpret_cast<uint4*>(ws.a1 + (size_t)row * kHidden);
+#pragma unroll
+        for (int i = 0; i < kVec; ++i) dst[lane + 32 * i] = v[i];
+        ws.sfa1[(size_t)lane * ws.m_cap + row] = sc0;
+        if (lane + 32 < kHiddenBlocks) ws.sfa1[(size_t)(lane + 32) * ws.m_cap + row] = sc1;
+        if (lane == 0) ws.row_token[row] = t;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Combine.  out[t, :] = bf16( sum_p float(Y[row_p, :]) * w_p ) with the pairs taken in
+// dispatch order and fp32 accumulation; tokens without a local expert get zeros.  Same
+// arithmetic as kernel/moe_fp8.cu:2276-2321.
+// ---------------------------------------------------------------------------------------
+constexpr int kCombineThreads = 448;  // 448 threads x 2 x 8 columns = 7168
+
+__global__ void __launch_bounds__(kCombineThreads) combine_kernel(Workspace ws, __nv_bfloat16* __restrict__ out, int T)
+{
+    const int t = blockIdx.x;
+    if (t >= T) return;
+    int n_pairs = ws.pair_count[t];
+    if (ws.num_tiles[0] == 0) n_pairs = 0;
+    float acc[2][8];
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[c][j] = 0.0f;
+
+    for (int p = 0; p < n_pairs; ++p) {
+        const uint32_t code = ws.pair_code[(size_t)t * kTopK + p];
+        const float w = ws.pair_weight[(size_t)t * kTopK + p];
+        const int row = ws.expert_offset[code >> 24] + (int)(code & 0x00ffffffu);
+        const uint4* src = reinterpret_cast<const uint4*>(ws.y + (size_t)row * kHidden);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            const uint4 raw = __ldg(src + threadIdx.x + c * kCombineThreads);
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(h2[j]);
+                acc[c][2 * j] += f.x * w;
+                acc[c][2 * j + 1] += f.y * w;
+            }
+        }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)t * kHidden);
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        uint4 packed;
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(acc[c][2 * j], acc[c][2 * j + 1]);
+        dst[threadIdx.x + c * kCombineThreads] = packed;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Launchers (called by the C-ABI layer).
+// ---------------------------------------------------------------------------------------
+cudaError_t launch_route_dispatch(const float* logits, const void* bias, const Workspace& ws, int T,
+                                  int local_expert_offset, int num_local_experts, float rsf,
+                                  const DispatchPolicy& pol, cudaStream_t stream)
+{
+    const int grid = (T + kRouteWarps - 1) / kRouteWarps;
+    route_dispatch_kernel<<<grid, kRouteWarps * 32, 0, stream>>>(
+        logits, static_cast<const __nv_bfloat16*>(bias), ws, T, local_expert_offset, num_local_experts, rsf, pol);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_scan_tiles(const Workspace& ws, int num_local_experts, cudaStream_t stream)
+{
+    scan_tiles_kernel<<<1, kMaxLocalExperts, 0, stream>>>(ws, num_local_experts);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_permute(const void* hidden, const float* hidden_scale, const Workspace& ws, int T,
+                           cudaStream_t stream)
+{
+    const int grid = (T + kPermuteWarps - 1) / kPermuteWarps;
+    permute_rows_kernel<<<grid, kPermuteWarps * 32, 0, stream>>>(
+        static_cast<const uint8_t*>(hidden), hidden_scale, ws, T);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_combine(const Workspace& ws, void* out, int T, cudaStream_t stream)
+{
+    combine_kernel<<<T, kCombineThreads, 0, stream>>>(ws, static_cast<__nv_bfloat16*>(out), T);
+    return cudaGetLastError();
+}
+
+}  // namespace moe

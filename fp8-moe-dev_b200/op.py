@@ -1,0 +1,196 @@
+"""Host-side mirror of the reference operator.
+
+`run(...)` takes the same eleven positional arguments, in the same order and with the same
+dtypes and layouts, as the reference's `run` (kernel/moe_fp8.cu:2663-2669), writes the bf16
+result into `output` (destination passing) and returns without synchronising.  `MoeLayer`
+is the explicit-handle form of the same call.  Torch is used only for device memory and
+the current stream; all compute happens in libmoe_fp8_b200.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Optional, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+
+H, I, N1, NE = 7168, 2048, 4096, 256
+
+
+class MoeError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"moe_fp8_b200 error {code}: {message}")
+        self.code = code
+
+
+def _check_tensor(name, t, dtype, shape, device=None):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if tuple(t.shape) != tuple(shape):
+        raise ValueError(f"{name} must have shape {tuple(shape)}, got {tuple(t.shape)}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if device is not None and t.device != device:
+        raise ValueError(f"{name} must live on {device}, got {t.device}")
+
+
+class MoeLayer:
+    """One handle = one GPU's workspace for up to `max_tokens` tokens and `num_local_experts`
+    experts (32 per reference shard; 64/128/256 hold several shards on one GPU)."""
+
+    def __init__(self, max_tokens: int, num_local_experts: int = 32, device: Optional[int] = None):
+        self._lib = _lib.load()
+        if device is None:
+            device = torch.cuda.current_device()
+        self.device = int(device)
+        self.max_tokens = int(max_tokens)
+        self.num_local_experts = int(num_local_experts)
+        h = C.c_void_p()
+        rc = self._lib.moe_fp8_b200_create(C.byref(h), self.device, self.max_tokens, self.num_local_experts)
+        if rc != _lib.OK:
+            raise MoeError(rc, self._lib.moe_fp8_b200_last_error(None).decode())
+        self._h = h
+        self.row_capacity = self._lib.moe_fp8_b200_row_capacity(self.max_tokens, self.num_local_experts)
+
+    # -- lifetime ---------------------------------------------------------------------
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.moe_fp8_b200_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _raise(self, rc):
+        raise MoeError(rc, self._lib.moe_fp8_b200_last_error(self._h).decode())
+
+    # -- options ----------------------------------------------------------------------
+    def set_reference_pruning(self, on: bool):
+        rc = self._lib.moe_fp8_b200_set_option(self._h, _lib.OPT_REFERENCE_PRUNING, int(bool(on)))
+        if rc != _lib.OK:
+            self._raise(rc)
+
+    def set_exact_silu(self, on: bool):
+        rc = self._lib.moe_fp8_b200_set_option(self._h, _lib.OPT_EXACT_SILU, int(bool(on)))
+        if rc != _lib.OK:
+            self._raise(rc)
+
+    # -- the operator -----------------------------------------------------------------
+    def _args(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+              gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+              routed_scaling_factor, output, host: bool):
+        T = int(routing_logits.shape[0])
+        E = self.num_local_experts
+        dev = torch.device("cuda", self.device)
+        io_dev = torch.device("cpu") if host else dev
+        _check_tensor("routing_logits", routing_logits, torch.float32, (T, NE), io_dev)
+        _check_tensor("routing_bias", routing_bias, torch.bfloat16, (NE,), dev)
+        _check_tensor("hidden_states", hidden_states, torch.float8_e4m3fn, (T, H), io_dev)
+        _check_tensor("hidden_states_scale", hidden_states_scale, torch.float32, (H // 128, T), io_dev)
+        _check_tensor("gemm1_weights", gemm1_weights, torch.float8_e4m3fn, (E, N1, H), dev)
+        _check_tensor("gemm1_weights_scale", gemm1_weights_scale, torch.float32, (E, N1 // 128, H // 128), dev)
+        _check_tensor("gemm2_weights", gemm2_weights, torch.float8_e4m3fn, (E, H, I), dev)
+        _check_tensor("gemm2_weights_scale", gemm2_weights_scale, torch.float32, (E, H // 128, I // 128), dev)
+        _check_tensor("output", output, torch.bfloat16, (T, H), io_dev)
+        a = _lib.Args()
+        a.routing_logits = routing_logits.data_ptr()
+        a.routing_bias = routing_bias.data_ptr()
+        a.hidden_states = hidden_states.data_ptr()
+        a.hidden_states_scale = hidden_states_scale.data_ptr()
+        a.gemm1_weights = gemm1_weights.data_ptr()
+        a.gemm1_weights_scale = gemm1_weights_scale.data_ptr()
+        a.gemm2_weights = gemm2_weights.data_ptr()
+        a.gemm2_weights_scale = gemm2_weights_scale.data_ptr()
+        a.local_expert_offset = int(local_expert_offset)
+        a.routed_scaling_factor = float(routed_scaling_factor)
+        a.output = output.data_ptr()
+        a.num_tokens = T
+        return a
+
+    def run(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+            gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset, routed_scaling_factor,
+            output, stream: Optional[int] = None):
+        """Device tensors in, bf16 `output` overwritten; asynchronous on the current stream."""
+        a = self._args(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                       gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                       routed_scaling_factor, output, host=False)
+        if stream is None:
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._lib.moe_fp8_b200_run(self._h, C.byref(a), C.c_void_p(stream))
+        if rc != _lib.OK:
+            self._raise(rc)
+        return output
+
+    def run_host(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                 gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                 routed_scaling_factor, output, stream: Optional[int] = None):
+        """Per-call tensors (logits, hidden, hidden scale, output) in HOST memory; the call
+        copies in, runs, copies out and synchronises."""
+        a = self._args(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                       gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                       routed_scaling_factor, output, host=True)
+        if stream is None:
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._lib.moe_fp8_b200_run_host(self._h, C.byref(a), C.c_void_p(stream))
+        if rc != _lib.OK:
+            self._raise(rc)
+        return output
+
+    def check(self, stream: Optional[int] = None):
+        """Synchronise and raise if a kernel recorded a failure (e.g. a wait that ran out)."""
+        if stream is None:
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._lib.moe_fp8_b200_check(self._h, C.c_void_p(stream))
+        if rc != _lib.OK:
+            self._raise(rc)
+
+    # -- diagnostics ------------------------------------------------------------------
+    _DTYPES = dict(expert_count=np.int32, expert_offset=np.int32, topk_idx=np.int32, topk_weight=np.float32,
+                   pair_count=np.int32, pair_code=np.uint32, pair_weight=np.float32, num_tiles=np.int32,
+                   row_token=np.int32, a1=np.uint8, sfa1=np.float32, a2=np.uint8, sfa2=np.float32, y=np.uint16,
+                   status=np.int32)
+
+    def read(self, name: str, count: int, offset_elems: int = 0) -> np.ndarray:
+        """First `count` elements (after `offset_elems`) of an intermediate buffer of the last run."""
+        dt = np.dtype(self._DTYPES[name])
+        out = np.empty(int(count), dtype=dt)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._lib.moe_fp8_b200_read_intermediate(
+            self._h, _lib.BUF[name], out.ctypes.data_as(C.c_void_p), out.nbytes, int(offset_elems) * dt.itemsize,
+            C.c_void_p(stream))
+        if rc != _lib.OK:
+            self._raise(rc)
+        return out
+
+
+# ----------------------------------------------------------------------------------------
+# The reference-shaped entry point: one grow-only handle per (device, expert count), like
+# the reference's thread-local workspace (kernel/moe_fp8.cu:2677-2689).
+_layers: Dict[Tuple[int, int], MoeLayer] = {}
+
+
+def run(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+        gemm2_weights, gemm2_weights_scale, local_expert_offset, routed_scaling_factor, output):
+    """Drop-in for the reference's `run` (destination passing, returns None)."""
+    T = int(routing_logits.shape[0])
+    if T <= 0:
+        return None
+    dev = routing_logits.device.index if routing_logits.is_cuda else torch.cuda.current_device()
+    E = int(gemm1_weights.shape[0])
+    key = (dev, E)
+    layer = _layers.get(key)
+    if layer is None or layer.max_tokens < T:
+        if layer is not None:
+            layer.close()
+        layer = MoeLayer(max(T, 16), E, dev)
+        _layers[key] = layer
+    layer.run(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+              gemm2_weights, gemm2_weights_scale, local_expert_offset, routed_scaling_factor, output)
+    return None

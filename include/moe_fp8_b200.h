@@ -1,0 +1,149 @@
+/*
+ * moe_fp8_b200 -- C ABI of the B200 (sm_100a) FP8 block-scaled MoE layer.
+ *
+ * One call computes one DeepSeek-V3 MoE layer shard: no-aux routing over 256 global
+ * experts, dispatch to the `num_local_experts` experts this GPU holds, FP8 grouped GEMM1
+ * (7168 -> 2 x 2048) with fused SwiGLU + 1x128 e4m3 requantisation, FP8 grouped GEMM2
+ * (2048 -> 7168) and the weighted combine into a bf16 output.
+ *
+ * The argument set, dtypes, layouts and semantics of `moe_fp8_b200_run` are those of the
+ * reference operator `run(...)` in kernel/moe_fp8.cu:2663-2669 (exported as
+ * `__tvm_ffi_run` at kernel/moe_fp8.cu:3674); only the carrier changes from TVM-FFI
+ * tensor views to plain device pointers.  All functions return 0 on success and a
+ * negative `moe_fp8_b200_status` otherwise; `moe_fp8_b200_last_error` gives the text.
+ *
+ * Pointers are DEVICE pointers of the handle's device unless a function says otherwise.
+ * A handle is not thread-safe; use one per host thread and GPU (the reference keeps one
+ * thread-local workspace, kernel/moe_fp8.cu:2677-2689).
+ */
+#ifndef MOE_FP8_B200_H_
+#define MOE_FP8_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define MOE_FP8_B200_API __attribute__((visibility("default")))
+#else
+#define MOE_FP8_B200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct moe_fp8_b200_ctx* moe_fp8_b200_handle;
+
+typedef enum {
+    MOE_FP8_B200_OK = 0,
+    MOE_FP8_B200_ERR_INVALID_ARGUMENT = -1,
+    MOE_FP8_B200_ERR_CUDA = -2,
+    MOE_FP8_B200_ERR_CAPACITY = -3, /* num_tokens above the handle's max_tokens */
+    MOE_FP8_B200_ERR_DEVICE = -4,   /* a kernel reported a bounded wait that ran out */
+    MOE_FP8_B200_ERR_UNSUPPORTED = -5
+} moe_fp8_b200_status;
+
+/* Replaces the positional arguments of run(), kernel/moe_fp8.cu:2663-2669. */
+typedef struct {
+    const float* routing_logits;        /* fp32 [T, 256] */
+    const void* routing_bias;           /* bf16 [256] */
+    const void* hidden_states;          /* e4m3 [T, 7168] */
+    const float* hidden_states_scale;   /* fp32 [56, T]  (k-block major, tokens contiguous) */
+    const void* gemm1_weights;          /* e4m3 [E_local, 4096, 7168] */
+    const float* gemm1_weights_scale;   /* fp32 [E_local, 32, 56] */
+    const void* gemm2_weights;          /* e4m3 [E_local, 7168, 2048] */
+    const float* gemm2_weights_scale;   /* fp32 [E_local, 56, 16] */
+    int64_t local_expert_offset;        /* first global expert held here (32 * rank) */
+    double routed_scaling_factor;
+    void* output;                       /* bf16 [T, 7168], fully overwritten */
+    int32_t num_tokens;                 /* T; 0 is a no-op (kernel/moe_fp8.cu:2671-2672) */
+} moe_fp8_b200_args;
+
+/* Options (moe_fp8_b200_set_option). */
+enum {
+    /* 1 (default): dispatch follows the reference's T-keyed policy table, i.e. exact
+     * dispatch for T < 32 (T != 15) and the keep-3 / drop-third / renormalise pruning
+     * of kernel/moe_fp8.cu:476-607 otherwise, applied per 32-expert shard.
+     * 0: exact dispatch at every T (the FlashInfer definition's semantics). */
+    MOE_FP8_B200_OPT_REFERENCE_PRUNING = 1,
+    /* 0 (default): the reference's rsqrt sigmoid approximant in SwiGLU
+     * (kernel/moe_fp8.cu:313-315, 1803-1804).  1: x / (1 + exp(-x)). */
+    MOE_FP8_B200_OPT_EXACT_SILU = 2
+};
+
+/* Intermediate buffers readable after a run (moe_fp8_b200_read_intermediate). */
+enum {
+    MOE_FP8_B200_BUF_EXPERT_COUNT = 0,  /* int32 [E_local]  routed rows per local expert */
+    MOE_FP8_B200_BUF_EXPERT_OFFSET = 1, /* int32 [E_local+1] first packed row per expert */
+    MOE_FP8_B200_BUF_TOPK_IDX = 2,      /* int32 [T, 8] */
+    MOE_FP8_B200_BUF_TOPK_WEIGHT = 3,   /* fp32  [T, 8] */
+    MOE_FP8_B200_BUF_PAIR_COUNT = 4,    /* int32 [T] */
+    MOE_FP8_B200_BUF_PAIR_CODE = 5,     /* uint32 [T, 8]  (local expert << 24) | slot */
+    MOE_FP8_B200_BUF_PAIR_WEIGHT = 6,   /* fp32  [T, 8] */
+    MOE_FP8_B200_BUF_NUM_TILES = 7,     /* int32 [1] */
+    MOE_FP8_B200_BUF_ROW_TOKEN = 8,     /* int32 [M_cap] */
+    MOE_FP8_B200_BUF_A1 = 9,            /* e4m3 [M_cap, 7168] */
+    MOE_FP8_B200_BUF_SFA1 = 10,         /* fp32 [56, M_cap] */
+    MOE_FP8_B200_BUF_A2 = 11,           /* e4m3 [M_cap, 2048] */
+    MOE_FP8_B200_BUF_SFA2 = 12,         /* fp32 [16, M_cap] */
+    MOE_FP8_B200_BUF_Y = 13,            /* bf16 [M_cap, 7168] */
+    MOE_FP8_B200_BUF_STATUS = 14        /* int32 [2] device status word + detail */
+};
+
+/* Library version, (major << 16) | minor.  No counterpart in the reference. */
+MOE_FP8_B200_API int moe_fp8_b200_version(void);
+
+/* Bytes of device workspace a handle of this capacity allocates.  Replaces the
+ * reference's grow-only alloc_workspace sizing, kernel/moe_fp8.cu:2473-2585. */
+MOE_FP8_B200_API size_t moe_fp8_b200_workspace_bytes(int max_tokens, int num_local_experts);
+
+/* Packed-row capacity M_cap for that sizing (multiple of 128). */
+MOE_FP8_B200_API int moe_fp8_b200_row_capacity(int max_tokens, int num_local_experts);
+
+/* Allocates the workspace on `device` (all cudaMalloc calls of the library happen here,
+ * none in run).  num_local_experts in {32, 64, 128, 256}.  Replaces the thread-local
+ * Workspace of kernel/moe_fp8.cu:2349-2461, 2677-2689. */
+MOE_FP8_B200_API int moe_fp8_b200_create(moe_fp8_b200_handle* out, int device, int max_tokens, int num_local_experts);
+
+MOE_FP8_B200_API int moe_fp8_b200_destroy(moe_fp8_b200_handle h);
+
+/* Text of the last error on this handle (or of the last failed create when h is NULL).
+ * The reference only prints to stderr (kernel/moe_fp8.cu:2683, 3130, 3162). */
+MOE_FP8_B200_API const char* moe_fp8_b200_last_error(moe_fp8_b200_handle h);
+
+MOE_FP8_B200_API int moe_fp8_b200_set_option(moe_fp8_b200_handle h, int option, int value);
+
+/* The layer.  Enqueues every stage on `stream` (a cudaStream_t; NULL = legacy default
+ * stream, which is what the reference always uses, kernel/moe_fp8.cu:2691) and returns
+ * without synchronising, like the reference (kernel/moe_fp8.cu:45-47).  No host read of
+ * device data happens, so the call may be captured into a CUDA graph; routing is
+ * recomputed on every call (the reference caches it by pointer identity,
+ * kernel/moe_fp8.cu:2696-2702).  Replaces run(), kernel/moe_fp8.cu:2663-3672. */
+MOE_FP8_B200_API int moe_fp8_b200_run(moe_fp8_b200_handle h, const moe_fp8_b200_args* args, void* stream);
+
+/* Same layer with HOST pointers for the per-call tensors (routing_logits,
+ * hidden_states, hidden_states_scale, output); routing_bias and the weights stay device
+ * pointers.  Copies in, runs, copies out and synchronises `stream`.  This is the
+ * end-to-end form a host-resident caller of the reference operator sees. */
+MOE_FP8_B200_API int moe_fp8_b200_run_host(moe_fp8_b200_handle h, const moe_fp8_b200_args* args, void* stream);
+
+/* Synchronises `stream` and returns MOE_FP8_B200_ERR_DEVICE if any kernel of earlier
+ * runs recorded a failure in the device status word. */
+MOE_FP8_B200_API int moe_fp8_b200_check(moe_fp8_b200_handle h, void* stream);
+
+/* Copies one intermediate buffer of the last run to host memory (synchronises `stream`).
+ * Test and diagnostics hook; stands in for the reference's compile-time debug dumps
+ * (kernel/moe_fp8.cu:3166-3300). */
+MOE_FP8_B200_API int moe_fp8_b200_read_intermediate(moe_fp8_b200_handle h, int buffer, void* dst_host, size_t bytes,
+                                   size_t offset_bytes, void* stream);
+
+/* Resolves the reference's T-keyed dispatch policy on the host (no GPU needed):
+ * out[0]=prune, [1]=skip_zero_weight, [2]=keep_limit, [3]=drop_third, and
+ * fracs[0]=drop_third_frac, [1]=drop_second_frac (2 local), [2]=drop_second_frac (>=3),
+ * out[4]=renorm.  Restates kernel/moe_fp8.cu:508-591, 2732-2790. */
+MOE_FP8_B200_API int moe_fp8_b200_reference_policy(int num_tokens, int32_t out_flags[5], float out_fracs[3]);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_FP8_B200_H_ */

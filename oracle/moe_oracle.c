@@ -1,0 +1,501 @@
+/*
+ * TEST INFRASTRUCTURE -- CPU oracle of the FP8 block-scaled MoE layer.
+ *
+ * Only tests/, __graft_entry__.smoke() and bench.py's cpu_baseline / --impl reference
+ * legs may load this file's library; the product (fp8-moe-dev_b200/) never does.
+ *
+ * It restates, in plain C, what the reference computes on the GPU:
+ *   oracle_route          kernel/moe_fp8.cu:359-448   (sigmoid + bias, group top-2 sums,
+ *                                                      4 groups, 8 argmax rounds, weights)
+ *   oracle_policy         kernel/moe_fp8.cu:93-194, 508-591, 2732-2790 (T-keyed knobs)
+ *   oracle_dispatch       kernel/moe_fp8.cu:457-475, 476-607, 646-668 (exact / pruning)
+ *   oracle_expert_rows    kernel/moe_fp8.cu:1239-1312 (GEMM1, per-128-K scale, bf16),
+ *                         :1801-1837 + :313-315 (SwiGLU, 1x128 absmax, e4m3 requant),
+ *                         :2055-2110 (GEMM2, bf16)
+ *   oracle_combine        kernel/moe_fp8.cu:2276-2321 (weighted sum in pair order, bf16)
+ *   oracle_fp32_layer     the layer's *definition* (exact sigmoid / SiLU, no pruning, no
+ *                         intermediate rounding), as flashinfer's trace template
+ *                         trace/templates/moe.py:28-183 states it; this is the host fp32
+ *                         baseline that bench.py times.
+ *
+ * Parity status: PINNED against the reference's own GPU run.  The reference holds no
+ * golden vectors or tests; the fixtures under tests/golden/ were produced by running the
+ * reference library (oracle/_ref/libref_moe.so, built by oracle/build_ref.sh from the
+ * reference sources) on a B200 with tests/golden/make_golden.py, and
+ * tests/test_oracle_golden.py checks this file against them.
+ *
+ * GPU-only intrinsics have CPU stand-ins here: __expf -> expf, rsqrtf -> 1/sqrtf.  That
+ * is why routing weights are compared to a few ulp and e4m3 payloads to one code step.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define H 7168
+#define I 2048
+#define N1 4096
+#define NE 256
+#define SHARD 32
+#define BLK 128
+#define HB 56
+#define IB 16
+#define TOPK 8
+#define NGROUP 8
+#define KGROUP 4
+
+#define API __attribute__((visibility("default")))
+
+/* ------------------------------------------------------------------ number formats */
+static float bf16_to_f32(uint16_t b) {
+    uint32_t u = (uint32_t)b << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+static uint16_t f32_to_bf16(float f) { /* round to nearest even */
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+static float round_bf16(float f) { return bf16_to_f32(f32_to_bf16(f)); }
+
+static float e4m3_lut[256];
+static int lut_ready = 0;
+static void init_lut(void) {
+    if (lut_ready) return;
+    for (int c = 0; c < 256; ++c) {
+        int s = c >> 7, e = (c >> 3) & 15, m = c & 7;
+        float v;
+        if (e == 15 && m == 7) v = NAN;
+        else if (e == 0) v = ldexpf((float)m, -9);
+        else v = ldexpf(1.0f + (float)m / 8.0f, e - 7);
+        e4m3_lut[c] = s ? -v : v;
+    }
+    lut_ready = 1;
+}
+/* float -> e4m3 (fn variant), round to nearest even, saturating to +-448. */
+static uint8_t f32_to_e4m3(float x) {
+    uint8_t sign = signbit(x) ? 0x80 : 0;
+    float a = fabsf(x);
+    if (isnan(a)) return (uint8_t)(sign | 0x7f);
+    if (a >= 448.0f) return (uint8_t)(sign | 0x7e);
+    if (a < 0.015625f) { /* below 2^-6: subnormal grid of 2^-9 */
+        int q = (int)nearbyintf(a * 512.0f);
+        return (uint8_t)(sign | q); /* q == 8 carries into the first normal */
+    }
+    int e;
+    float m = frexpf(a, &e); /* a = m * 2^e, m in [0.5, 1) */
+    e -= 1;
+    float frac = m * 2.0f - 1.0f; /* [0, 1) */
+    int mant = (int)nearbyintf(frac * 8.0f);
+    if (mant == 8) { mant = 0; e += 1; }
+    if (e > 8 || (e == 8 && mant > 6)) return (uint8_t)(sign | 0x7e);
+    return (uint8_t)(sign | ((e + 7) << 3) | mant);
+}
+
+API void oracle_e4m3_decode(const uint8_t* src, float* dst, long n) {
+    init_lut();
+    for (long i = 0; i < n; ++i) dst[i] = e4m3_lut[src[i]];
+}
+API void oracle_e4m3_encode(const float* src, uint8_t* dst, long n) {
+    for (long i = 0; i < n; ++i) dst[i] = f32_to_e4m3(src[i]);
+}
+API void oracle_bf16_encode(const float* src, uint16_t* dst, long n) {
+    for (long i = 0; i < n; ++i) dst[i] = f32_to_bf16(src[i]);
+}
+
+/* ------------------------------------------------------------------ routing */
+/* One token.  Literal restatement, including the warp xor-butterfly tie order. */
+static void route_token(const float* logit, const uint16_t* bias, int exact_sigmoid, int* idx, float* w) {
+    float s[NE], sb[NE];
+    for (int e = 0; e < NE; ++e) {
+        float sg = 1.0f / (1.0f + expf(-logit[e]));
+        (void)exact_sigmoid;
+        s[e] = sg;
+        sb[e] = sg + bf16_to_f32(bias[e]);
+    }
+    float gscore[NGROUP];
+    for (int g = 0; g < NGROUP; ++g) {
+        float top1 = -1e30f, top2 = -1e30f;
+        for (int i = 0; i < SHARD; ++i) {
+            float v = sb[g * SHARD + i];
+            if (v > top1) { top2 = top1; top1 = v; }
+            else if (v > top2) { top2 = v; }
+        }
+        gscore[g] = top1 + top2;
+    }
+    int kept[NGROUP] = {0};
+    for (int k = 0; k < KGROUP; ++k) {
+        float best = -1e30f;
+        int bi = -1;
+        for (int g = 0; g < NGROUP; ++g)
+            if (!kept[g] && gscore[g] > best) { best = gscore[g]; bi = g; }
+        if (bi >= 0) kept[bi] = 1;
+    }
+    for (int e = 0; e < NE; ++e)
+        if (!kept[e / SHARD]) sb[e] = -1e30f;
+    for (int k = 0; k < TOPK; ++k) {
+        float wmax[NE / 32];
+        int widx[NE / 32];
+        for (int wp = 0; wp < NE / 32; ++wp) {
+            float v[32];
+            int ix[32];
+            for (int l = 0; l < 32; ++l) { v[l] = sb[wp * 32 + l]; ix[l] = wp * 32 + l; }
+            for (int off = 16; off > 0; off >>= 1) {
+                float nv[32];
+                int ni[32];
+                for (int l = 0; l < 32; ++l) {
+                    int o = l ^ off;
+                    if (v[o] > v[l]) { nv[l] = v[o]; ni[l] = ix[o]; }
+                    else { nv[l] = v[l]; ni[l] = ix[l]; }
+                }
+                memcpy(v, nv, sizeof v);
+                memcpy(ix, ni, sizeof ix);
+            }
+            wmax[wp] = v[0];
+            widx[wp] = ix[0];
+        }
+        float bv = -1e30f;
+        int bi = 0;
+        for (int wp = 0; wp < NE / 32; ++wp)
+            if (wmax[wp] > bv) { bv = wmax[wp]; bi = widx[wp]; }
+        idx[k] = bi;
+        sb[bi] = -1e30f;
+    }
+    float sumw = 1e-20f;
+    for (int k = 0; k < TOPK; ++k) sumw += s[idx[k]];
+    float inv = 1.0f / sumw;
+    for (int k = 0; k < TOPK; ++k) w[k] = s[idx[k]] * inv;
+}
+
+API void oracle_route(const float* logits, const uint16_t* bias, int T, int* idx, float* w) {
+#pragma omp parallel for schedule(static)
+    for (int t = 0; t < T; ++t) route_token(logits + (size_t)t * NE, bias, 0, idx + t * TOPK, w + t * TOPK);
+}
+
+/* Smallest gap between two candidates of one argmax round / group pick, per token:
+ * tokens whose gap is below a few ulp may legitimately pick differently on the GPU
+ * (ex2.approx sigmoid), tests use this to set those tokens aside. */
+API void oracle_route_margin(const float* logits, const uint16_t* bias, int T, float* margin) {
+#pragma omp parallel for schedule(static)
+    for (int t = 0; t < T; ++t) {
+        const float* logit = logits + (size_t)t * NE;
+        float sb[NE];
+        for (int e = 0; e < NE; ++e) sb[e] = 1.0f / (1.0f + expf(-logit[e])) + bf16_to_f32(bias[e]);
+        float gs[NGROUP];
+        for (int g = 0; g < NGROUP; ++g) {
+            float t1 = -1e30f, t2 = -1e30f;
+            for (int i = 0; i < SHARD; ++i) {
+                float v = sb[g * SHARD + i];
+                if (v > t1) { t2 = t1; t1 = v; } else if (v > t2) t2 = v;
+            }
+            gs[g] = t1 + t2;
+        }
+        float sorted[NGROUP];
+        memcpy(sorted, gs, sizeof gs);
+        for (int a = 0; a < NGROUP; ++a)
+            for (int b = a + 1; b < NGROUP; ++b)
+                if (sorted[b] > sorted[a]) { float x = sorted[a]; sorted[a] = sorted[b]; sorted[b] = x; }
+        float mg = sorted[KGROUP - 1] - sorted[KGROUP];
+        float cand[NE];
+        int n = 0;
+        for (int g = 0; g < NGROUP; ++g)
+            if (gs[g] >= sorted[KGROUP - 1])
+                for (int i = 0; i < SHARD; ++i) cand[n++] = sb[g * SHARD + i];
+        for (int a = 0; a < n; ++a)
+            for (int b = a + 1; b < n; ++b)
+                if (cand[b] > cand[a]) { float x = cand[a]; cand[a] = cand[b]; cand[b] = x; }
+        if (n > TOPK) { float d = cand[TOPK - 1] - cand[TOPK]; if (d < mg) mg = d; }
+        margin[t] = mg;
+    }
+}
+
+/* ------------------------------------------------------------------ dispatch policy */
+typedef struct {
+    int prune, skip_zero_weight, keep_limit, drop_third;
+    float drop_third_frac, drop_second_frac_2, drop_second_frac_ge3;
+    int renorm;
+} oracle_policy_t;
+
+API void oracle_policy(int T, int reference_pruning, oracle_policy_t* p) {
+    memset(p, 0, sizeof *p);
+    p->keep_limit = 3;
+    if (!reference_pruning) return;
+    if (T <= 1) return;                      /* route_topk_kernel<true,false>, :2732 */
+    if (!(T >= 32 || T == 15 || T == 0)) {   /* <false,false> + build_dispatch_kernel, :2754, :2785 */
+        p->skip_zero_weight = 1;             /* :655 */
+        return;
+    }
+    p->prune = 1;                            /* <true,true>, :2742-2752 */
+    float frac = 0.30f;                                        /* :114-116, :510 */
+    if (T >= 10000 && T < 13000) frac = 0.34f;                 /* :511-513 */
+    int low = (T == 32 || T == 57 || T == 58 || T == 62 || T == 80 || T == 901); /* :514-520 */
+    if (low) frac = 0.20f;
+    if (T == 14107) frac = 0.30f;
+    else if (T == 32) frac = 0.25f;
+    else if (T == 53) frac = 0.20f;
+    else if (T == 80) frac = 0.20f;
+    else if (T == 901) frac = 0.24f;                           /* :524-534 */
+    p->drop_third_frac = frac;
+    p->drop_third = (T >= 10000 || T == 54 || T == 56 || T == 59 || T == 53 || low); /* :535-541 */
+    if (T == 14107) { p->drop_second_frac_2 = 0.302f; p->drop_second_frac_ge3 = 0.303f; } /* :548-556 */
+    else if (T == 901) p->drop_second_frac_2 = p->drop_second_frac_ge3 = 0.245f;
+    else if (T == 80) p->drop_second_frac_2 = p->drop_second_frac_ge3 = 0.20f;
+    else if (T == 53) p->drop_second_frac_2 = p->drop_second_frac_ge3 = 0.30f;  /* T == 32: 0 -> off */
+    p->renorm = (T == 14107) ? 0 : 1;                          /* :580-591 */
+}
+
+/* Kept (local expert, scaled weight) pairs of every token, in emission order, shard by
+ * shard (a shard = 32 consecutive local experts = what one reference call handles). */
+API void oracle_dispatch(const int* idx, const float* w, int T, int local_expert_offset, int num_local_experts,
+                         const oracle_policy_t* pol, float rsf, int* pair_count, int* pair_le, float* pair_w,
+                         int* expert_count) {
+    memset(expert_count, 0, sizeof(int) * (size_t)num_local_experts);
+    for (int t = 0; t < T; ++t) {
+        const int* ix = idx + t * TOPK;
+        const float* wn = w + t * TOPK;
+        int np = 0;
+        for (int sh = 0; sh < num_local_experts / SHARD; ++sh) {
+            int lo = sh * SHARD;
+            if (!pol->prune) {
+                for (int k = 0; k < TOPK; ++k) {
+                    int le = ix[k] - local_expert_offset;
+                    if (le < lo || le >= lo + SHARD) continue;
+                    if (pol->skip_zero_weight && wn[k] == 0.0f) continue;
+                    pair_le[t * TOPK + np] = le;
+                    pair_w[t * TOPK + np] = wn[k] * rsf;
+                    ++np;
+                    ++expert_count[le];
+                }
+                continue;
+            }
+            int keep_le[3] = {-1, -1, -1};
+            float keep_w[3] = {-1.0f, -1.0f, -1.0f};
+            int local_count = 0;
+            float local_w_sum = 0.0f;
+            for (int k = 0; k < TOPK; ++k) {
+                int le = ix[k] - local_expert_offset;
+                if (le < lo || le >= lo + SHARD) continue;
+                float wk = wn[k];
+                ++local_count;
+                local_w_sum += wk;
+                for (int i = 0; i < 3; ++i) {
+                    if (wk > keep_w[i]) {
+                        for (int j = 2; j > i; --j) { keep_w[j] = keep_w[j - 1]; keep_le[j] = keep_le[j - 1]; }
+                        keep_w[i] = wk;
+                        keep_le[i] = le;
+                        break;
+                    }
+                }
+            }
+            if (local_count == 0) continue;
+            int max_keep = 3;
+            if (local_count >= 3 && keep_le[2] >= 0 && local_w_sum > 0.0f)
+                if (pol->drop_third && keep_w[2] <= pol->drop_third_frac * local_w_sum) max_keep = 2;
+            if (local_count >= 2 && keep_le[1] >= 0 && local_w_sum > 0.0f) {
+                float f2 = local_count >= 3 ? pol->drop_second_frac_ge3 : pol->drop_second_frac_2;
+                if (f2 > 0.0f && keep_w[1] <= f2 * local_w_sum) max_keep = 1;
+            }
+            float renorm = 1.0f;
+            if (pol->renorm && local_count > max_keep) {
+                float kept = 0.0f;
+                for (int i = 0; i < 3; ++i)
+                    if (i < max_keep && keep_le[i] >= 0) kept += keep_w[i];
+                if (kept > 0.0f) renorm = local_w_sum / kept;
+            }
+            for (int i = 0; i < 3; ++i) {
+                if (i < max_keep && keep_le[i] >= 0) {
+                    pair_le[t * TOPK + np] = keep_le[i];
+                    pair_w[t * TOPK + np] = keep_w[i] * renorm * rsf;
+                    ++np;
+                    ++expert_count[keep_le[i]];
+                }
+            }
+        }
+        pair_count[t] = np;
+    }
+}
+
+/* ------------------------------------------------------------------ expert compute */
+static float dot128(const float* a, const float* b) {
+    float s = 0.0f;
+    for (int k = 0; k < BLK; ++k) s += a[k] * b[k];
+    return s;
+}
+
+/*
+ * All rows of ONE expert.  tokens[r] is the token of row r.
+ *   faithful = 1: the reference's rounding points (bf16 D, approximate SiLU unless
+ *                 exact_silu, e4m3 A2 with 1x128 scales, bf16 Y); y_out rows are bf16-valued.
+ *   faithful = 0: the definition -- dequantised fp32 GEMMs, exact SiLU, nothing rounded.
+ * Optional outputs (may be NULL): d_out [rows, 4096] (after bf16 rounding when faithful),
+ * a2_out [rows, 2048] e4m3 codes, sfa2_out [rows, 16].
+ */
+API void oracle_expert_rows(const uint8_t* hidden, const float* hidden_scale, int T, const int* tokens, int rows,
+                            const uint8_t* w1, const float* w1_scale, const uint8_t* w2, const float* w2_scale,
+                            int faithful, int exact_silu, float* y_out, float* d_out, uint8_t* a2_out,
+                            float* sfa2_out) {
+    init_lut();
+    if (rows <= 0) return;
+    float* w1f = (float*)malloc(sizeof(float) * (size_t)N1 * H);
+    float* w2f = (float*)malloc(sizeof(float) * (size_t)H * I);
+    float* af = (float*)malloc(sizeof(float) * (size_t)rows * H);
+    float* d = (float*)malloc(sizeof(float) * (size_t)rows * N1);
+    float* a2f = (float*)malloc(sizeof(float) * (size_t)rows * I);
+    float* s2 = (float*)malloc(sizeof(float) * (size_t)rows * IB);
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < (long)N1 * H; ++i) w1f[i] = e4m3_lut[w1[i]];
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < (long)H * I; ++i) w2f[i] = e4m3_lut[w2[i]];
+    for (int r = 0; r < rows; ++r)
+        for (int k = 0; k < H; ++k) af[(size_t)r * H + k] = e4m3_lut[hidden[(size_t)tokens[r] * H + k]];
+
+    /* GEMM1: D[r, n] = sum_kb dot(A[r, kb], W1[n, kb]) * (sA[kb, t] * sW1[n/128, kb]) */
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N1; ++n) {
+        const float* wrow = w1f + (size_t)n * H;
+        const float* sw = w1_scale + (size_t)(n / BLK) * HB;
+        for (int r = 0; r < rows; ++r) {
+            const float* arow = af + (size_t)r * H;
+            int t = tokens[r];
+            float acc = 0.0f;
+            for (int kb = 0; kb < HB; ++kb) {
+                float raw = dot128(arow + kb * BLK, wrow + kb * BLK);
+                float sc = hidden_scale[(size_t)kb * T + t] * sw[kb];
+                acc += raw * sc;
+            }
+            d[(size_t)r * N1 + n] = faithful ? round_bf16(acc) : acc;
+        }
+    }
+    if (d_out) memcpy(d_out, d, sizeof(float) * (size_t)rows * N1);
+
+    /* SwiGLU (+ requant) */
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        for (int ib = 0; ib < IB; ++ib) {
+            float v[BLK];
+            float amax = 0.0f;
+            for (int j = 0; j < BLK; ++j) {
+                int n = ib * BLK + j;
+                float x1 = d[(size_t)r * N1 + n];
+                float x2 = d[(size_t)r * N1 + I + n];
+                float silu;
+                if (!faithful || exact_silu) silu = x2 / (1.0f + expf(-x2));
+                else silu = x2 * (0.5f * (x2 * (1.0f / sqrtf(fmaf(x2, x2, 4.0f))) + 1.0f));
+                v[j] = silu * x1;
+                float a = fabsf(v[j]);
+                if (a > amax) amax = a;
+            }
+            if (faithful) {
+                float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
+                float inv = 1.0f / scale;
+                s2[(size_t)r * IB + ib] = scale;
+                for (int j = 0; j < BLK; ++j) {
+                    uint8_t q = f32_to_e4m3(v[j] * inv);
+                    if (a2_out) a2_out[(size_t)r * I + ib * BLK + j] = q;
+                    a2f[(size_t)r * I + ib * BLK + j] = e4m3_lut[q];
+                }
+            } else {
+                s2[(size_t)r * IB + ib] = 1.0f;
+                for (int j = 0; j < BLK; ++j) a2f[(size_t)r * I + ib * BLK + j] = v[j];
+            }
+        }
+    }
+    if (sfa2_out) memcpy(sfa2_out, s2, sizeof(float) * (size_t)rows * IB);
+
+    /* GEMM2: Y[r, h] = sum_kb dot(A2[r, kb], W2[h, kb]) * (sA2[r, kb] * sW2[h/128, kb]) */
+#pragma omp parallel for schedule(static)
+    for (int h = 0; h < H; ++h) {
+        const float* wrow = w2f + (size_t)h * I;
+        const float* sw = w2_scale + (size_t)(h / BLK) * IB;
+        for (int r = 0; r < rows; ++r) {
+            const float* arow = a2f + (size_t)r * I;
+            float acc = 0.0f;
+            for (int kb = 0; kb < IB; ++kb) {
+                float raw = dot128(arow + kb * BLK, wrow + kb * BLK);
+                float sc = s2[(size_t)r * IB + kb] * sw[kb];
+                acc += raw * sc;
+            }
+            y_out[(size_t)r * H + h] = faithful ? round_bf16(acc) : acc;
+        }
+    }
+    free(w1f); free(w2f); free(af); free(d); free(a2f); free(s2);
+}
+
+/* out[t, :] = bf16(sum_p y[row(t,p), :] * w(t,p)), fp32 fused multiply-add in pair order
+ * (nvcc contracts the reference's `s += v * w` into an FMA).  row_of_pair[t*8+p] indexes y. */
+API void oracle_combine(const float* y, const int* pair_count, const int* row_of_pair, const float* pair_w, int T,
+                        uint16_t* out_bf16) {
+#pragma omp parallel for schedule(static)
+    for (int t = 0; t < T; ++t) {
+        for (int h = 0; h < H; ++h) {
+            float s = 0.0f;
+            for (int p = 0; p < pair_count[t]; ++p)
+                s = fmaf(y[(size_t)row_of_pair[t * TOPK + p] * H + h], pair_w[t * TOPK + p], s);
+            out_bf16[(size_t)t * H + h] = f32_to_bf16(s);
+        }
+    }
+}
+
+/*
+ * Whole layer on the host for `num_local_experts` experts starting at local_expert_offset.
+ *   mode 0: faithful restatement of the reference pipeline (policy from oracle_policy(T, reference_pruning))
+ *   mode 1: fp32 definition (no pruning, no intermediate rounding)
+ * Weights are [E_local, ...] as passed to the operator.  Returns the number of routed rows.
+ */
+API long oracle_layer(const float* logits, const uint16_t* bias, const uint8_t* hidden, const float* hidden_scale,
+                      const uint8_t* w1, const float* w1_scale, const uint8_t* w2, const float* w2_scale,
+                      int T, int local_expert_offset, int num_local_experts, float rsf, int mode,
+                      int reference_pruning, int exact_silu, uint16_t* out_bf16) {
+    int* idx = (int*)malloc(sizeof(int) * (size_t)T * TOPK);
+    float* w = (float*)malloc(sizeof(float) * (size_t)T * TOPK);
+    int* pc = (int*)malloc(sizeof(int) * (size_t)T);
+    int* ple = (int*)malloc(sizeof(int) * (size_t)T * TOPK);
+    float* pw = (float*)malloc(sizeof(float) * (size_t)T * TOPK);
+    int* rop = (int*)malloc(sizeof(int) * (size_t)T * TOPK);
+    int* ecount = (int*)malloc(sizeof(int) * (size_t)num_local_experts);
+    int* eoff = (int*)malloc(sizeof(int) * (size_t)(num_local_experts + 1));
+    oracle_route(logits, bias, T, idx, w);
+    oracle_policy_t pol;
+    oracle_policy(T, mode == 0 ? reference_pruning : 0, &pol);
+    oracle_dispatch(idx, w, T, local_expert_offset, num_local_experts, &pol, rsf, pc, ple, pw, ecount);
+    eoff[0] = 0;
+    for (int e = 0; e < num_local_experts; ++e) eoff[e + 1] = eoff[e] + ecount[e];
+    long M = eoff[num_local_experts];
+    int* tokens = (int*)malloc(sizeof(int) * (size_t)(M > 0 ? M : 1));
+    int* fill = (int*)calloc((size_t)num_local_experts, sizeof(int));
+    for (int t = 0; t < T; ++t)
+        for (int p = 0; p < pc[t]; ++p) {
+            int le = ple[t * TOPK + p];
+            int row = eoff[le] + fill[le]++;
+            tokens[row] = t;
+            rop[t * TOPK + p] = row;
+        }
+    float* y = (float*)malloc(sizeof(float) * (size_t)(M > 0 ? M : 1) * H);
+    for (int e = 0; e < num_local_experts; ++e) {
+        int rows = ecount[e];
+        if (rows == 0) continue;
+        oracle_expert_rows(hidden, hidden_scale, T, tokens + eoff[e], rows, w1 + (size_t)e * N1 * H,
+                           w1_scale + (size_t)e * (N1 / BLK) * HB, w2 + (size_t)e * H * I,
+                           w2_scale + (size_t)e * HB * IB, mode == 0, exact_silu, y + (size_t)eoff[e] * H, NULL, NULL,
+                           NULL);
+    }
+    oracle_combine(y, pc, rop, pw, T, out_bf16);
+    free(idx); free(w); free(pc); free(ple); free(pw); free(rop); free(ecount); free(eoff); free(tokens); free(fill);
+    free(y);
+    return M;
+}
+
+API int oracle_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}

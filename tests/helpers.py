@@ -1,0 +1,178 @@
+"""Shared helpers of the test-suite: seeded cases, the reference loader, error metrics."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+import numpy as np
+import torch
+
+import __graft_entry__ as entry
+
+ROOT = Path(__file__).resolve().parent.parent
+REF_LIB = ROOT / "oracle" / "_ref" / "libref_moe.so"
+DIAG_DIR = ROOT / "gpurun_out" / "diag"
+H, I, N1, NE, TOPK = 7168, 2048, 4096, 256, 8
+RSF = 2.5
+
+
+def np_u16(t: torch.Tensor) -> np.ndarray:
+    return t.contiguous().view(torch.uint16).cpu().numpy()
+
+
+def np_u8(t: torch.Tensor) -> np.ndarray:
+    return t.contiguous().view(torch.uint8).cpu().numpy()
+
+
+def save_diag(name: str, **arrays):
+    """Keep arrays of a failing comparison for offline reading."""
+    try:
+        DIAG_DIR.mkdir(parents=True, exist_ok=True)
+        np.savez_compressed(DIAG_DIR / f"{name}.npz", **arrays)
+    except Exception:
+        pass
+
+
+_shards = {}
+
+
+def gpu_shard(offset: int, E: int, base_seed: int = 1000):
+    """Weights of experts [offset, offset+E) on the GPU (CUDA generator), cached per session."""
+    key = (offset, E, base_seed)
+    if key not in _shards:
+        entry.load_package()
+        from fp8_moe_dev_b200 import gen
+        if len(_shards) >= 2:
+            _shards.pop(next(iter(_shards)))
+            torch.cuda.empty_cache()
+        _shards[key] = gen.make_shard(offset, E, base_seed, device="cuda", out_device="cuda")
+    return _shards[key]
+
+
+def cpu_inputs(T: int, seed: int = 0, skew: bool = False):
+    entry.load_package()
+    from fp8_moe_dev_b200 import gen
+    logits, bias = gen.make_routing(T, seed, skew)
+    hidden, hscale = gen.make_hidden(T, seed + 1)
+    return logits, bias, hidden, hscale
+
+
+def run_layer(layer, inputs, weights, offset, rsf=RSF, out=None):
+    logits, bias, hidden, hscale = [x.cuda() for x in inputs]
+    w1, s1, w2, s2 = weights
+    T = logits.shape[0]
+    if out is None:
+        out = torch.full((T, H), float("nan"), dtype=torch.bfloat16, device="cuda")
+    layer.run(logits, bias, hidden, hscale, w1, s1, w2, s2, offset, rsf, out)
+    layer.check()
+    return out
+
+
+# ------------------------------------------------------------------ reference library
+_ref_mod = None
+
+
+def reference_available() -> bool:
+    return REF_LIB.exists()
+
+
+def reference_module():
+    global _ref_mod
+    if _ref_mod is None:
+        import tvm_ffi
+        _ref_mod = tvm_ffi.load_module(str(REF_LIB))
+    return _ref_mod
+
+
+def reference_run(inputs, weights, offset, rsf=RSF):
+    """The unmodified reference operator on fresh device buffers (its caches key on pointers)."""
+    logits, bias, hidden, hscale = [x.cuda().clone() for x in inputs]
+    w1, s1, w2, s2 = weights
+    T = logits.shape[0]
+    out = torch.zeros(T, H, dtype=torch.bfloat16, device="cuda")
+    reference_module().run(logits, bias, hidden, hscale, w1, s1, w2, s2, int(offset), float(rsf), out)
+    torch.cuda.synchronize()
+    return out
+
+
+_harness = None
+
+
+def harness():
+    global _harness
+    if _harness is None:
+        reference_module()  # makes sure dependencies are resolved the same way
+        _harness = C.CDLL(str(REF_LIB))
+        _harness.ref_harness_route.restype = C.c_int
+        _harness.ref_harness_dispatch.restype = C.c_int
+    return _harness
+
+
+def reference_routing(logits: torch.Tensor, bias: torch.Tensor):
+    """topk_idx int32 [T,8], topk_weight fp32 [T,8] from the reference's own routing kernel."""
+    T = logits.shape[0]
+    lg, bs = logits.cuda().contiguous(), bias.cuda().contiguous()
+    idx = torch.zeros(T, TOPK, dtype=torch.int32, device="cuda")
+    w = torch.zeros(T, TOPK, dtype=torch.float32, device="cuda")
+    cnt = torch.zeros(T, dtype=torch.int32, device="cuda")
+    vp = lambda t: C.c_void_p(t.data_ptr())
+    rc = harness().ref_harness_route(vp(lg), vp(bs), C.c_int(T), vp(idx), vp(w), vp(cnt), C.c_void_p(0))
+    torch.cuda.synchronize()
+    assert rc == 0, rc
+    return idx.cpu().numpy(), w.cpu().numpy()
+
+
+def reference_dispatch(logits: torch.Tensor, bias: torch.Tensor, offset: int, rsf: float = RSF):
+    """The reference's dispatch tables for this T: dict(variant, expert_count [32], pairs = per-token
+    list of (local expert, weight) in stored order, offsets [33], padded [32])."""
+    T = logits.shape[0]
+    lg, bs = logits.cuda().contiguous(), bias.cuda().contiguous()
+    i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device="cuda")
+    f32 = lambda *s: torch.zeros(*s, dtype=torch.float32, device="cuda")
+    idx, w, tlc = i32(T, TOPK), f32(T, TOPK), i32(T)
+    ecount, elist, eweight = i32(32), i32(32, T), f32(32, T)
+    pcode, pweight = i32(T, TOPK), f32(T, TOPK)
+    offs, padded, scratch = i32(33), i32(32), i32(80)
+    vp = lambda t: C.c_void_p(t.data_ptr())
+    rc = harness().ref_harness_dispatch(vp(lg), vp(bs), C.c_int(T), C.c_int(offset), C.c_float(rsf), vp(idx), vp(w),
+                                        vp(tlc), vp(ecount), vp(elist), vp(eweight), vp(pcode), vp(pweight),
+                                        vp(offs), vp(padded), vp(scratch), C.c_void_p(0))
+    torch.cuda.synchronize()
+    assert rc >= 0, rc
+    tlc_h, pcode_h, pw_h = tlc.cpu().numpy(), pcode.cpu().numpy(), pweight.cpu().numpy()
+    pairs = []
+    for t in range(T):
+        n = min(int(tlc_h[t]), TOPK)
+        pairs.append([(int(np.uint32(pcode_h[t, p]) >> 24), np.float32(pw_h[t, p])) for p in range(n)])
+    return dict(variant=rc, expert_count=ecount.cpu().numpy(), pairs=pairs, offsets=offs.cpu().numpy(),
+                padded=padded.cpu().numpy(), expert_token_list=elist.cpu().numpy())
+
+
+# ------------------------------------------------------------------ metrics
+def error_stats(got: np.ndarray, want: np.ndarray) -> dict:
+    got = got.astype(np.float64)
+    want = want.astype(np.float64)
+    diff = np.abs(got - want)
+    den = np.linalg.norm(want)
+    return dict(
+        max_abs=float(diff.max()) if diff.size else 0.0,
+        mean_abs=float(diff.mean()) if diff.size else 0.0,
+        rel_l2=float(np.linalg.norm(got - want) / den) if den > 0 else float(np.linalg.norm(got - want)),
+        contest_ratio=float((diff <= 1.0 + 0.3 * np.abs(want)).mean()) if diff.size else 1.0,
+        cosine=float((got * want).sum() / (np.linalg.norm(got) * den)) if den > 0 and np.linalg.norm(got) > 0 else 1.0,
+    )
+
+
+def gpu_pairs(layer, T: int):
+    """Per-token [(local expert, slot, weight)] of the last run, expert_count, expert_offset."""
+    pc = layer.read("pair_count", T)
+    code = layer.read("pair_code", T * TOPK).reshape(T, TOPK)
+    pw = layer.read("pair_weight", T * TOPK).reshape(T, TOPK)
+    pairs = [[(int(code[t, p] >> 24), int(code[t, p] & 0xFFFFFF), np.float32(pw[t, p])) for p in range(int(pc[t]))]
+             for t in range(T)]
+    return pairs, layer.read("expert_count", layer.num_local_experts), layer.read("expert_offset",
+                                                                                  layer.num_local_experts + 1)
+
+
+_ = os
