@@ -1,0 +1,410 @@
+#!/usr/bin/env python
+"""Benchmark of the FP8 block-scaled MoE layer on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" = one pass of the whole layer (routing, dispatch, permute, GEMM1+SwiGLU+requant,
+GEMM2, combine, and for N > 1 the NCCL sum of the partial outputs) over one synthetic batch.
+The default workload is the large-prefill configuration: T = 12288 tokens, all 256 experts,
+split evenly over the N GPUs (N = 1 holds all 256 on one GPU).  Rank 0 prints ONE JSON line.
+
+Timed on the device with CUDA events after W warm-up steps, max over ranks; the weights
+(11.3 GB over all ranks) and activations are far larger than the 126 MB L2, so no explicit
+flush is needed between iterations.  Seeded synthetic inputs stand in for recorded traces.
+
+--impl reference runs the UNMODIFIED reference operator (oracle/_ref/libref_moe.so, built
+from the reference's own sources by oracle/build_ref.sh) on the same GPU(s), workload and
+metric: 32 experts per call, so (256/N)/32 sequential calls per rank whose bf16 outputs are
+added, then the same NCCL sum.  If that library cannot be loaded, the CPU oracle port of the
+layer is timed on the host cores instead and the line says so.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+import __graft_entry__ as entry  # noqa: E402
+
+H, I, N1, NE = 7168, 2048, 4096, 256
+RSF = 2.5
+FLOPS_PER_ROW = 2 * (H * N1 + I * H)          # 88,080,384
+GEMM1_FLOPS_PER_ROW = 2 * H * N1              # 58,720,256
+GEMM2_FLOPS_PER_ROW = 2 * I * H               # 29,360,128
+FP8_NOMINAL_TFLOPS = 4500.0
+
+WORKLOADS = {
+    # name: (T, skew, description)
+    "t12288_e256": (12288, False, "T=12288 prefill, 256 experts split over the GPUs, uniform routing"),
+    "t16384_e256_skew": (16384, True, "T=16384, 256 experts split over the GPUs, Zipf-like skewed routing"),
+    "t1024_e256": (1024, False, "T=1024 prefill, 256 experts split over the GPUs"),
+}
+
+# DRAM bytes per launch of the dominant kernel (GEMM1) from an ncu capture, keyed by workload;
+# None until a capture of that workload exists (see profiles/).
+NCU_DRAM_BYTES_PER_LAUNCH = {}
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"],
+                    bf16_tflops_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+
+    REASONS = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+               0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.dev = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.dev, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.dev, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.dev)
+                for bit, name in self.REASONS.items():
+                    if mask & bit and name != "gpu_idle":
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.01)
+
+    def __enter__(self):
+        if self.nv:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    if world != n_gpus:
+        raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    return rank, world, local
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x: float, world: int) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(x: float, world: int) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def make_workload(name: str, rank: int, world: int):
+    entry.load_package()
+    from fp8_moe_dev_b200 import gen
+    from fp8_moe_dev_b200.dist import expert_range
+    T, skew, _ = WORKLOADS[name]
+    offset, E = expert_range(rank, world)
+    logits, bias = gen.make_routing(T, seed=0, skew=skew)           # CPU streams: identical on every rank
+    hidden, hscale = gen.make_hidden(T, seed=1)
+    weights = gen.make_shard(offset, E, base_seed=1000, device="cuda", out_device="cuda")
+    return T, offset, E, (logits, bias, hidden, hscale), weights
+
+
+def time_steps(step, steps, warmup, world):
+    for _ in range(warmup):
+        step()
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    barrier(world)
+    return max_over_ranks(e0.elapsed_time(e1), world) / steps  # ms per step
+
+
+def small_config_latencies(pkg, weights, bias_dev):
+    """Latency of the small single-shard configurations (rank 0, N = 1): T = 1 as the median of
+    1000 CUDA-graph replays, T = 16 and T = 1024 event-timed; 32 experts at offset 0."""
+    from fp8_moe_dev_b200 import gen
+    w1, s1, w2, s2 = [x[:32] for x in weights]
+    out = []
+    for T in (1, 16, 1024):
+        logits, _ = gen.make_routing(T, seed=0)
+        hidden, hscale = gen.make_hidden(T, seed=1)
+        dev = [logits.cuda(), bias_dev, hidden.cuda(), hscale.cuda()]
+        layer = pkg.MoeLayer(T, 32, 0)
+        o = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+        run = lambda: layer.run(*dev, w1, s1, w2, s2, 0, RSF, o)  # noqa: E731
+        for _ in range(5):
+            run()
+        layer.check()
+        rows = int(layer.read("pair_count", T).sum())
+        if T == 1:
+            g = torch.cuda.CUDAGraph()
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                with torch.cuda.graph(g, stream=s):
+                    run()
+            torch.cuda.current_stream().wait_stream(s)
+            times = []
+            for _ in range(1000):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                g.replay()
+                b.record()
+                b.synchronize()
+                times.append(a.elapsed_time(b) * 1e3)
+            lat = statistics.median(times)
+            how = "median of 1000 CUDA-graph replays"
+        else:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n = 50
+            a.record()
+            for _ in range(n):
+                run()
+            b.record()
+            b.synchronize()
+            lat = a.elapsed_time(b) * 1e3 / n
+            how = f"mean of {n} back-to-back runs"
+        out.append({"workload": f"T={T}, 32 experts, offset 0", "latency_us": round(lat, 2),
+                    "tokens_per_s": round(T / lat * 1e6, 1), "routed_rows": rows, "how": how})
+        layer.close()
+    return out
+
+
+def cpu_baseline(inputs, weights, sample_tokens=64):
+    """Host fp32 dequantise-and-compute baseline (the layer's definition, oracle port), timed on
+    a bounded sample: the first `sample_tokens` tokens against the first 32-expert shard."""
+    orc = entry.load_oracle()
+    logits, bias, hidden, hscale = inputs
+    S = min(sample_tokens, logits.shape[0])
+    w1, s1, w2, s2 = [x[:32] for x in weights]
+    args = (logits[:S].numpy(), bias.view(torch.uint16).numpy(), hidden[:S].view(torch.uint8).numpy(),
+            hscale[:, :S].contiguous().numpy(), w1.view(torch.uint8).cpu().numpy(), s1.cpu().numpy(),
+            w2.view(torch.uint8).cpu().numpy(), s2.cpu().numpy(), 0, RSF)
+    t0 = time.perf_counter()
+    _, rows = orc.layer(*args, mode="fp32")
+    dt = time.perf_counter() - t0
+    rows_per_s = rows / dt if dt > 0 else 0.0
+    return {"value": round(rows_per_s / 8.0, 3), "unit": "tokens/s", "cores": orc.num_threads(), "kind": "port",
+            "sample": f"fp32 definition of the layer on the host: first {S} tokens x experts 0..31 "
+                      f"({rows} routed rows, {dt:.2f} s incl. dequantising the touched experts); "
+                      "tokens/s = rows/s / 8 rows per token"}
+
+
+def run_ours(args, rank, world, local):
+    pkg = entry.load_package()
+    from fp8_moe_dev_b200.dist import combine_partials
+    T, offset, E, inputs, weights = make_workload(args.workload, rank, world)
+    dev = [x.cuda() for x in inputs]
+    w1, s1, w2, s2 = weights
+    layer = pkg.MoeLayer(T, E, local)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+
+    def step():
+        layer.run(*dev, w1, s1, w2, s2, offset, RSF, out)
+        combine_partials(out, "all_reduce")
+
+    step()
+    layer.check()
+    rows_local = int(layer.read("pair_count", T).sum())
+    rows_total = int(sum_over_ranks(rows_local, world))
+    rows_max = int(max_over_ranks(rows_local, world))
+
+    layer.set_stage_timing(True)
+    with ClockSampler(local) as clk:
+        ms = time_steps(step, args.steps, args.warmup, world)
+    stages, timed_runs = layer.stage_times()
+    layer.set_stage_timing(False)
+    layer.check()
+
+    # end to end: per-step inputs start in pinned host memory, the result ends in host memory
+    pin = [x.pin_memory() for x in (inputs[0], inputs[2], inputs[3])]
+    host_out = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+    if world == 1:
+        def e2e_step():
+            layer.run_host(pin[0], dev[1], pin[1], pin[2], w1, s1, w2, s2, offset, RSF, host_out)
+    else:
+        def e2e_step():
+            dev[0].copy_(pin[0], non_blocking=True)
+            dev[2].copy_(pin[1], non_blocking=True)
+            dev[3].copy_(pin[2], non_blocking=True)
+            layer.run(*dev, w1, s1, w2, s2, offset, RSF, out)
+            combine_partials(out, "all_reduce")
+            host_out.copy_(out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+    e2e_ms = time_steps(e2e_step, max(3, args.steps // 2), 3, world)
+    h2d = sum(x.numel() * x.element_size() for x in pin)
+    d2h = host_out.numel() * host_out.element_size()
+
+    pk = peaks()
+    g1_ms = max_over_ranks(stages["gemm1"], world)
+    g1_flops = rows_max * GEMM1_FLOPS_PER_ROW  # the slowest rank's launch
+    achieved = g1_flops / (g1_ms * 1e-3) / 1e12 if g1_ms > 0 else 0.0
+    fp8_peak = 2.0 * pk["bf16_tflops_sustained"]
+    line = {
+        "metric": "moe_layer_tokens_per_s", "value": round(T / ms * 1e3, 1), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+        "latency_us": round(ms * 1e3, 1), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "e4m3 x e4m3 -> f32 accumulate, bf16 out", "data": "synthetic",
+        "config": {"workload": args.workload, "description": WORKLOADS[args.workload][2], "tokens": T,
+                   "experts_total": NE, "experts_per_gpu": E, "routed_rows_total": rows_total,
+                   "routed_rows_max_rank": rows_max, "reference_pruning": True,
+                   "l2": "inputs larger than L2 (weights 11.3 GB total), no flush",
+                   "ideal_scaling_bound": round(rows_total / rows_max, 3) if rows_max else None},
+        "clocks": clk.summary(),
+        "e2e": {"value": round(T / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "path": "moe_fp8_b200_run_host (C ABI, host buffers)" if world == 1
+                        else "pinned H2D + moe_fp8_b200_run + NCCL all-reduce + D2H"},
+        "gpu_launches": 6 * args.steps * world,
+        "stage_ms": {k: round(max_over_ranks(v, world), 4) for k, v in stages.items()},
+        "layer_tflops": round(rows_max * FLOPS_PER_ROW / (ms * 1e-3) / 1e12, 1),
+        "roofline": {"kernel": "grouped_gemm_kernel<1> (GEMM1 + SwiGLU + requant)", "bound": "tensor",
+                     "achieved": round(achieved, 1), "peak": round(fp8_peak, 1), "unit": "TFLOP/s",
+                     "frac": round(achieved / fp8_peak, 4) if fp8_peak else None,
+                     "peak_note": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({pk['source']}); "
+                                  f"nominal dense fp8 {FP8_NOMINAL_TFLOPS:.0f}",
+                     "frac_of_nominal": round(achieved / FP8_NOMINAL_TFLOPS, 4),
+                     "flops_per_launch": g1_flops, "avg_launch_ms": round(g1_ms, 4), "timed_launches": timed_runs,
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload)},
+    }
+    if rank == 0 and world == 1:
+        if not args.skip_small:
+            line["configs"] = small_config_latencies(pkg, weights, dev[1])
+        if not args.skip_cpu:
+            line["cpu_baseline"] = cpu_baseline(inputs, weights)
+    layer.close()
+    return line
+
+
+def run_reference(args, rank, world, local):
+    sys.path.insert(0, str(ROOT / "tests"))
+    from fp8_moe_dev_b200.dist import combine_partials
+    import helpers as hp
+    T, offset, E, inputs, weights = make_workload(args.workload, rank, world)
+    try:
+        mod = hp.reference_module()
+    except Exception as ex:  # library missing or not loadable: time the CPU port instead
+        if rank != 0:
+            return None
+        cb = cpu_baseline(inputs, weights)
+        return {"impl": "reference", "metric": "moe_layer_tokens_per_s", "value": cb["value"], "unit": "tokens/s",
+                "n_gpus": world, "steps": 1, "warmup": 0, "ms_per_step": None, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": args.workload, "note": f"reference GPU library unavailable ({ex}); CPU port timed"},
+                "cpu_baseline": cb,
+                "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    dev = [x.cuda() for x in inputs]
+    w1, s1, w2, s2 = weights
+    shards = E // 32
+    parts = [torch.zeros(T, H, dtype=torch.bfloat16, device="cuda") for _ in range(shards)]
+    out = torch.zeros(T, H, dtype=torch.bfloat16, device="cuda")
+
+    def step():
+        for s in range(shards):
+            sl = slice(32 * s, 32 * s + 32)
+            mod.run(dev[0], dev[1], dev[2], dev[3], w1[sl], s1[sl], w2[sl], s2[sl], offset + 32 * s, RSF, parts[s])
+        torch.sum(torch.stack(parts).float(), dim=0, out=None).to(torch.bfloat16, copy=False) if False else None
+        out.copy_(parts[0])
+        for s in range(1, shards):
+            out.add_(parts[s])
+        combine_partials(out, "all_reduce")
+
+    with ClockSampler(local) as clk:
+        ms = time_steps(step, args.steps, args.warmup, world)
+    val = round(T / ms * 1e3, 1)
+    return {"impl": "reference", "metric": "moe_layer_tokens_per_s", "value": val, "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+            "latency_us": round(ms * 1e3, 1), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "e4m3 x e4m3 -> f32 accumulate, bf16 out", "data": "synthetic",
+            "config": {"workload": args.workload, "description": WORKLOADS[args.workload][2], "tokens": T,
+                       "experts_total": NE, "experts_per_gpu": E,
+                       "how": f"{shards} sequential reference calls of 32 experts per rank on identical pointers "
+                              "(its pointer-keyed caches may hit), bf16 adds, same NCCL all-reduce"},
+            "clocks": clk.summary(),
+            "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": 0, "kind": "reference",
+                             "sample": "the reference's own GPU build (oracle/_ref/libref_moe.so) on the same "
+                                       "B200(s), full workload; the reference has no CPU implementation"},
+            "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="t12288_e256")
+    ap.add_argument("--skip-small", action="store_true", help="skip the T=1/16/1024 single-shard latencies")
+    ap.add_argument("--skip-cpu", action="store_true", help="skip the host fp32 baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank, world, local = dist_setup(args.gpus)
+    line = run_ours(args, rank, world, local) if args.impl == "ours" else run_reference(args, rank, world, local)
+    if rank == 0 and line is not None:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -13,7 +13,7 @@ LIB_PATH = HERE / "libmoe_fp8_b200.so"
 
 OK = 0
 ERR_INVALID_ARGUMENT, ERR_CUDA, ERR_CAPACITY, ERR_DEVICE, ERR_UNSUPPORTED = -1, -2, -3, -4, -5
-OPT_REFERENCE_PRUNING, OPT_EXACT_SILU = 1, 2
+OPT_REFERENCE_PRUNING, OPT_EXACT_SILU, OPT_STAGE_TIMING = 1, 2, 3
 
 BUF = dict(
     expert_count=0, expert_offset=1, topk_idx=2, topk_weight=3, pair_count=4, pair_code=5, pair_weight=6,
@@ -24,7 +24,7 @@ EXPORTS = [
     "moe_fp8_b200_version", "moe_fp8_b200_workspace_bytes", "moe_fp8_b200_row_capacity",
     "moe_fp8_b200_create", "moe_fp8_b200_destroy", "moe_fp8_b200_last_error", "moe_fp8_b200_set_option",
     "moe_fp8_b200_run", "moe_fp8_b200_run_host", "moe_fp8_b200_check", "moe_fp8_b200_read_intermediate",
-    "moe_fp8_b200_reference_policy",
+    "moe_fp8_b200_reference_policy", "moe_fp8_b200_stage_times",
 ]
 
 
@@ -72,6 +72,8 @@ def load() -> C.CDLL:
     lib.moe_fp8_b200_check.argtypes = [H, C.c_void_p]
     lib.moe_fp8_b200_read_intermediate.restype = C.c_int
     lib.moe_fp8_b200_read_intermediate.argtypes = [H, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]
+    lib.moe_fp8_b200_stage_times.restype = C.c_int
+    lib.moe_fp8_b200_stage_times.argtypes = [H, C.POINTER(C.c_float), C.POINTER(C.c_int)]
     lib.moe_fp8_b200_reference_policy.restype = C.c_int
     lib.moe_fp8_b200_reference_policy.argtypes = [C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_float)]
     _lib = lib

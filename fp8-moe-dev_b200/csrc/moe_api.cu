@@ -103,6 +103,13 @@ struct moe_fp8_b200_ctx {
     alignas(64) unsigned char tmap_w2[128];
     const void* cached_w1 = nullptr;
     const void* cached_w2 = nullptr;
+    // optional per-stage timing: events around each stage of the last kTimedRuns runs
+    int opt_stage_timing = 0;
+    static constexpr int kTimedRuns = 64;
+    static constexpr int kStageEvents = 7;
+    cudaEvent_t events[kTimedRuns][kStageEvents] = {};
+    bool events_created = false;
+    int timed_runs = 0;
     // staging for run_host (allocated on its first use)
     uint8_t* stage = nullptr;
     size_t stage_bytes = 0;
@@ -169,18 +176,37 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
         if (r != 0) return fail(h, MOE_FP8_B200_ERR_CUDA, "cuTensorMapEncodeTiled(W2) failed: %d", r);
         h->cached_w2 = a.gemm2_weights;
     }
+    cudaEvent_t* ev = nullptr;
+    if (h->opt_stage_timing) {
+        if (!h->events_created) {
+            for (auto& run : h->events)
+                for (auto& x : run)
+                    if (cudaEventCreate(&x) != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "cudaEventCreate failed");
+            h->events_created = true;
+        }
+        ev = h->events[h->timed_runs % moe_fp8_b200_ctx::kTimedRuns];
+        ++h->timed_runs;
+    }
+    auto mark = [&](int i) { if (ev) cudaEventRecord(ev[i], stream); };
     cudaError_t e = cudaMemsetAsync(h->ws.ctrl, 0, sizeof(Control), stream);
+    mark(0);
     if (e == cudaSuccess)
         e = launch_route_dispatch(a.routing_logits, a.routing_bias, h->ws, T, (int)a.local_expert_offset, E,
                                   (float)a.routed_scaling_factor, pol, stream);
+    mark(1);
     if (e == cudaSuccess) e = launch_scan_tiles(h->ws, E, stream);
+    mark(2);
     if (e == cudaSuccess) e = launch_permute(a.hidden_states, a.hidden_states_scale, h->ws, T, stream);
+    mark(3);
     if (e == cudaSuccess)
         e = launch_grouped_gemm(1, h->tmap_a1, h->tmap_w1, h->ws, a.gemm1_weights_scale, h->opt_exact_silu,
                                 h->num_sms, stream);
+    mark(4);
     if (e == cudaSuccess)
         e = launch_grouped_gemm(2, h->tmap_a2, h->tmap_w2, h->ws, a.gemm2_weights_scale, 0, h->num_sms, stream);
+    mark(5);
     if (e == cudaSuccess) e = launch_combine(h->ws, a.output, T, stream);
+    mark(6);
     if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
     return MOE_FP8_B200_OK;
 }
@@ -312,6 +338,9 @@ int moe_fp8_b200_destroy(moe_fp8_b200_handle h)
     if (!h) return MOE_FP8_B200_OK;
     cudaSetDevice(h->device);
     cudaDeviceSynchronize();
+    if (h->events_created)
+        for (auto& run : h->events)
+            for (auto& x : run) cudaEventDestroy(x);
     if (h->stage) cudaFree(h->stage);
     if (h->base) cudaFree(h->base);
     delete h;
@@ -326,6 +355,10 @@ int moe_fp8_b200_set_option(moe_fp8_b200_handle h, int option, int value)
     switch (option) {
         case MOE_FP8_B200_OPT_REFERENCE_PRUNING: h->opt_reference_pruning = value ? 1 : 0; return MOE_FP8_B200_OK;
         case MOE_FP8_B200_OPT_EXACT_SILU: h->opt_exact_silu = value ? 1 : 0; return MOE_FP8_B200_OK;
+        case MOE_FP8_B200_OPT_STAGE_TIMING:
+            h->opt_stage_timing = value ? 1 : 0;
+            h->timed_runs = 0;
+            return MOE_FP8_B200_OK;
         default: return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "unknown option %d", option);
     }
 }
@@ -395,6 +428,26 @@ int moe_fp8_b200_check(moe_fp8_b200_handle h, void* stream)
                     : st[0] == kStatusGemm2Timeout ? "GEMM2 gave up on a bounded wait"
                     : st[0] == kStatusRowOverflow  ? "routed rows exceed the workspace capacity"
                                                    : "unknown");
+    return MOE_FP8_B200_OK;
+}
+
+int moe_fp8_b200_stage_times(moe_fp8_b200_handle h, float out_ms[6], int* out_runs)
+{
+    if (!h || !out_ms) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
+    for (int i = 0; i < 6; ++i) out_ms[i] = 0.0f;
+    const int n = h->timed_runs < moe_fp8_b200_ctx::kTimedRuns ? h->timed_runs : moe_fp8_b200_ctx::kTimedRuns;
+    if (out_runs) *out_runs = n;
+    if (n == 0) return MOE_FP8_B200_OK;
+    for (int r = 0; r < n; ++r) {
+        cudaError_t e = cudaEventSynchronize(h->events[r][6]);
+        for (int i = 0; i < 6 && e == cudaSuccess; ++i) {
+            float ms = 0.0f;
+            e = cudaEventElapsedTime(&ms, h->events[r][i], h->events[r][i + 1]);
+            out_ms[i] += ms / n;
+        }
+        if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "stage timing: %s", cudaGetErrorString(e));
+    }
+    h->timed_runs = 0;
     return MOE_FP8_B200_OK;
 }
 

@@ -82,6 +82,22 @@ class MoeLayer:
         if rc != _lib.OK:
             self._raise(rc)
 
+    STAGES = ("route_dispatch", "scan", "permute", "gemm1", "gemm2", "combine")
+
+    def set_stage_timing(self, on: bool):
+        rc = self._lib.moe_fp8_b200_set_option(self._h, _lib.OPT_STAGE_TIMING, int(bool(on)))
+        if rc != _lib.OK:
+            self._raise(rc)
+
+    def stage_times(self):
+        """({stage: mean ms}, runs) over the runs since stage timing was switched on."""
+        ms = (C.c_float * 6)()
+        n = C.c_int(0)
+        rc = self._lib.moe_fp8_b200_stage_times(self._h, ms, C.byref(n))
+        if rc != _lib.OK:
+            self._raise(rc)
+        return dict(zip(self.STAGES, [float(x) for x in ms])), int(n.value)
+
     # -- the operator -----------------------------------------------------------------
     def _args(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
               gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,

@@ -68,7 +68,10 @@ enum {
     MOE_FP8_B200_OPT_REFERENCE_PRUNING = 1,
     /* 0 (default): the reference's rsqrt sigmoid approximant in SwiGLU
      * (kernel/moe_fp8.cu:313-315, 1803-1804).  1: x / (1 + exp(-x)). */
-    MOE_FP8_B200_OPT_EXACT_SILU = 2
+    MOE_FP8_B200_OPT_EXACT_SILU = 2,
+    /* 1: record CUDA events around every stage of each run (not capturable into a graph
+     * while on); read them with moe_fp8_b200_stage_times.  Setting it restarts the count. */
+    MOE_FP8_B200_OPT_STAGE_TIMING = 3
 };
 
 /* Intermediate buffers readable after a run (moe_fp8_b200_read_intermediate). */
@@ -100,8 +103,8 @@ MOE_FP8_B200_API size_t moe_fp8_b200_workspace_bytes(int max_tokens, int num_loc
 /* Packed-row capacity M_cap for that sizing (multiple of 128). */
 MOE_FP8_B200_API int moe_fp8_b200_row_capacity(int max_tokens, int num_local_experts);
 
-/* Allocates the workspace on `device` (all cudaMalloc calls of the library happen here,
- * none in run).  num_local_experts in {32, 64, 128, 256}.  Replaces the thread-local
+/* Allocates the workspace on `device` (every cudaMalloc of the library happens here,
+ * except the staging buffers of run_host, which its first call allocates).  num_local_experts in {32, 64, 128, 256}.  Replaces the thread-local
  * Workspace of kernel/moe_fp8.cu:2349-2461, 2677-2689. */
 MOE_FP8_B200_API int moe_fp8_b200_create(moe_fp8_b200_handle* out, int device, int max_tokens, int num_local_experts);
 
@@ -130,6 +133,13 @@ MOE_FP8_B200_API int moe_fp8_b200_run_host(moe_fp8_b200_handle h, const moe_fp8_
 /* Synchronises `stream` and returns MOE_FP8_B200_ERR_DEVICE if any kernel of earlier
  * runs recorded a failure in the device status word. */
 MOE_FP8_B200_API int moe_fp8_b200_check(moe_fp8_b200_handle h, void* stream);
+
+/* Mean device time in ms of the six stages (routing+dispatch, offset scan, permute, GEMM1,
+ * GEMM2, combine) over the runs recorded since stage timing was switched on (at most the
+ * last 64), measured with CUDA events on the runs' stream; waits for those runs to
+ * finish and restarts the count.  Stands in for the per-stage numbers the reference never
+ * reports (it has no profiling hooks). */
+MOE_FP8_B200_API int moe_fp8_b200_stage_times(moe_fp8_b200_handle h, float out_ms[6], int* out_runs);
 
 /* Copies one intermediate buffer of the last run to host memory (synchronises `stream`).
  * Test and diagnostics hook; stands in for the reference's compile-time debug dumps

@@ -38,7 +38,13 @@ if [ ! -f "$OUT/trtllm_runner.o" ] || [ "$K/trtllm_batched_gemm_runner.cu" -nt "
 fi
 # moe_fp8.cu is compiled through ref_harness.cu, which includes it unchanged and appends
 # test entry points for the reference's routing / dispatch kernels.
-( $NVCC $COMMON -I "$K" -I "$TVM/include" -I "$TVM/3rdparty/dlpack/include" -c "$HERE/ref_harness.cu" -o "$OUT/moe_fp8.o" ) & pids+=($!)
+# MOE_TRTLLM_BMM_CONFIG is one of the reference's own #ifndef knobs (kernel/moe_fp8.cu:87-89).  Its
+# default, 364, is a position in the kernel table generated for flashinfer 0.6.8.post1; in this
+# image's flashinfer_cubin table position 364 is an e4m3-output, 8-token-tile kernel, and running
+# it with the reference's bf16 / 64-token-tile arguments made an illegal memory access.  -1 makes
+# the adapter ask the runner for its default valid configuration (kernel/trtllm_fp8_bmm.cu:88-98).
+REF_KNOBS="${REF_KNOBS:--DMOE_TRTLLM_BMM_CONFIG=-1}"
+( $NVCC $COMMON $REF_KNOBS -I "$K" -I "$TVM/include" -I "$TVM/3rdparty/dlpack/include" -c "$HERE/ref_harness.cu" -o "$OUT/moe_fp8.o" ) & pids+=($!)
 ( $NVCC $COMMON $TLLM_DEFS $TLLM_INC -c "$K/trtllm_fp8_bmm.cu" -o "$OUT/trtllm_fp8_bmm.o" ) & pids+=($!)
 for f in envUtils logger stringUtils tllmException; do
   ( g++ -std=c++17 -O2 -fPIC -w $TLLM_DEFS $TLLM_INC -I /usr/local/cuda/include \
