@@ -24,8 +24,9 @@ EXPORTS = [
     "moe_fp8_b200_version", "moe_fp8_b200_workspace_bytes", "moe_fp8_b200_row_capacity",
     "moe_fp8_b200_create", "moe_fp8_b200_destroy", "moe_fp8_b200_last_error", "moe_fp8_b200_set_option",
     "moe_fp8_b200_run", "moe_fp8_b200_run_host", "moe_fp8_b200_check", "moe_fp8_b200_read_intermediate",
-    "moe_fp8_b200_reference_policy", "moe_fp8_b200_stage_times",
+    "moe_fp8_b200_reference_policy", "moe_fp8_b200_stage_times", "moe_fp8_b200_route_noalloc",
 ]
+NOALLOC_MAX_TOKENS = 4096
 
 
 class Args(C.Structure):
@@ -72,6 +73,10 @@ def load() -> C.CDLL:
     lib.moe_fp8_b200_check.argtypes = [H, C.c_void_p]
     lib.moe_fp8_b200_read_intermediate.restype = C.c_int
     lib.moe_fp8_b200_read_intermediate.argtypes = [H, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]
+    lib.moe_fp8_b200_route_noalloc.restype = C.c_int
+    lib.moe_fp8_b200_route_noalloc.argtypes = [
+        C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_double, C.c_int32, C.c_void_p, C.c_void_p,
+        C.c_void_p, C.c_void_p, C.c_char_p, C.c_size_t]
     lib.moe_fp8_b200_stage_times.restype = C.c_int
     lib.moe_fp8_b200_stage_times.argtypes = [H, C.POINTER(C.c_float), C.POINTER(C.c_int)]
     lib.moe_fp8_b200_reference_policy.restype = C.c_int

@@ -153,6 +153,41 @@ MOE_FP8_B200_API int moe_fp8_b200_read_intermediate(moe_fp8_b200_handle h, int b
  * out[4]=renorm.  Restates kernel/moe_fp8.cu:508-591, 2732-2790. */
 MOE_FP8_B200_API int moe_fp8_b200_reference_policy(int num_tokens, int32_t out_flags[5], float out_fracs[3]);
 
+/* Largest batch the allocation-free routing entry point accepts; its built-in scratch is
+ * sized for it (about 270 KB of device memory per GPU, held until the process exits). */
+#define MOE_FP8_B200_NOALLOC_MAX_TOKENS 4096
+
+/* Routing + dispatch without any allocation.  This entry point has no counterpart in the
+ * reference.  It exists for callers that cannot call cudaMalloc where they need the routing
+ * result: code running under a frozen memory pool, inside a latency-critical serving loop,
+ * or in a host runtime that forbids allocations by libraries.  It needs no handle: the
+ * scratch the stage works in (per-expert row counters, per-token pair tables) is a fixed
+ * device array inside the library, so the call performs no cudaMalloc / cudaFree and calls
+ * no allocating routine.
+ *
+ * Inputs: routing_logits fp32 [T,256], routing_bias bf16 [256] (device pointers).
+ * Outputs (device pointers, caller-owned): topk_idx_out int32 [T,8], topk_weight_out fp32
+ * [T,8] -- the same values moe_fp8_b200_run leaves in MOE_FP8_B200_BUF_TOPK_IDX / _WEIGHT --
+ * and expert_count_out int32 [num_local_experts], the routed rows per local expert under
+ * the chosen dispatch policy (reference_pruning as in MOE_FP8_B200_OPT_REFERENCE_PRUNING).
+ * Work is enqueued on `stream` and the call returns without synchronising.
+ *
+ * Limits and rules:
+ *  - num_tokens above MOE_FP8_B200_NOALLOC_MAX_TOKENS is refused with
+ *    MOE_FP8_B200_ERR_CAPACITY (err, if given, receives the text).
+ *  - The first call on each GPU looks up the scratch array's device address; make that
+ *    first call with the GPU current and before any stream capture begins.
+ *  - Every call on a GPU uses the same scratch and the scratch keeps the last call's
+ *    contents (the counters are cleared at the start of each call).  Calls that overlap
+ *    on one GPU race on it: serialise them (one stream, or events between streams).
+ * err / err_len: optional buffer for an error message (may be NULL / 0). */
+MOE_FP8_B200_API int moe_fp8_b200_route_noalloc(const float* routing_logits, const void* routing_bias,
+                                                int32_t num_tokens, int64_t local_expert_offset,
+                                                int32_t num_local_experts, double routed_scaling_factor,
+                                                int32_t reference_pruning, int32_t* topk_idx_out,
+                                                float* topk_weight_out, int32_t* expert_count_out, void* stream,
+                                                char* err, size_t err_len);
+
 #ifdef __cplusplus
 }
 #endif
