@@ -43,10 +43,15 @@ GEMM2_FLOPS_PER_ROW = 2 * I * H               # 29,360,128
 FP8_NOMINAL_TFLOPS = 4500.0
 
 WORKLOADS = {
-    # name: (T, skew, description)
-    "t12288_e256": (12288, False, "T=12288 prefill, 256 experts split over the GPUs, uniform routing"),
-    "t16384_e256_skew": (16384, True, "T=16384, 256 experts split over the GPUs, Zipf-like skewed routing"),
-    "t1024_e256": (1024, False, "T=1024 prefill, 256 experts split over the GPUs"),
+    # name: (T, skew, experts in the layer, description)
+    "t12288_e256": (12288, False, 256, "T=12288 prefill, 256 experts split over the GPUs, uniform routing"),
+    "t16384_e256_skew": (16384, True, 256, "T=16384, 256 experts split over the GPUs, Zipf-like skewed routing"),
+    "t1024_e256": (1024, False, 256, "T=1024 prefill, 256 experts split over the GPUs"),
+    # single 32-expert shard (offset 0) on one GPU: the reference's native shape; also the small
+    # cases used for ncu captures (1.4 GB of weights, well above the 126 MB L2)
+    "t12288_e32": (12288, False, 32, "T=12288, one 32-expert shard (offset 0), 1 GPU"),
+    "t1024_e32": (1024, False, 32, "T=1024, one 32-expert shard (offset 0), 1 GPU"),
+    "t16_e32": (16, False, 32, "T=16, one 32-expert shard (offset 0), 1 GPU"),
 }
 
 # DRAM bytes per launch of the dominant kernel (GEMM1) from an ncu capture, keyed by workload;
@@ -157,8 +162,13 @@ def make_workload(name: str, rank: int, world: int):
     entry.load_package()
     from fp8_moe_dev_b200 import gen
     from fp8_moe_dev_b200.dist import expert_range
-    T, skew, _ = WORKLOADS[name]
-    offset, E = expert_range(rank, world)
+    T, skew, experts_total, _ = WORKLOADS[name]
+    if experts_total == NE:
+        offset, E = expert_range(rank, world)
+    else:
+        if world != 1:
+            raise SystemExit(f"workload {name} is a single-shard case: run it with --gpus 1")
+        offset, E = 0, experts_total
     logits, bias = gen.make_routing(T, seed=0, skew=skew)           # CPU streams: identical on every rank
     hidden, hscale = gen.make_hidden(T, seed=1)
     weights = gen.make_shard(offset, E, base_seed=1000, device="cuda", out_device="cuda")
@@ -178,9 +188,26 @@ def time_steps(step, steps, warmup, world):
     return max_over_ranks(e0.elapsed_time(e1), world) / steps  # ms per step
 
 
-def small_config_latencies(pkg, weights, bias_dev):
-    """Latency of the small single-shard configurations (rank 0, N = 1): T = 1 as the median of
-    1000 CUDA-graph replays, T = 16 and T = 1024 event-timed; 32 experts at offset 0."""
+def _event_times_us(fn, n):
+    """Per-call device time of n calls of fn, each bracketed by its own pair of events."""
+    times = []
+    for _ in range(n):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        times.append(a.elapsed_time(b) * 1e3)
+    return times
+
+
+def small_config_latencies(pkg, weights, bias_dev, reference_mod=None):
+    """Latency of the small single-shard configurations (rank 0, N = 1; 32 experts, offset 0) at
+    T = 1, 16, 1024.  Ours: the whole layer (routing included) captured once into a CUDA graph,
+    median of 1000 (T = 1) / 200 replays, plus the mean of back-to-back eager calls.  Reference:
+    median of the same number of calls on identical pointers, i.e. its own steady state, in
+    which it replays an internal CUDA graph and skips routing (kernel/moe_fp8.cu:2696-2702,
+    2881-2916)."""
     from fp8_moe_dev_b200 import gen
     w1, s1, w2, s2 = [x[:32] for x in weights]
     out = []
@@ -188,43 +215,43 @@ def small_config_latencies(pkg, weights, bias_dev):
         logits, _ = gen.make_routing(T, seed=0)
         hidden, hscale = gen.make_hidden(T, seed=1)
         dev = [logits.cuda(), bias_dev, hidden.cuda(), hscale.cuda()]
+        o = torch.zeros(T, H, dtype=torch.bfloat16, device="cuda")
+        reps = 1000 if T == 1 else 200
+        if reference_mod is not None:
+            run = lambda: reference_mod.run(*dev, w1, s1, w2, s2, 0, RSF, o)  # noqa: E731
+            for _ in range(5):
+                run()
+            torch.cuda.synchronize()
+            lat = statistics.median(_event_times_us(run, reps))
+            out.append({"workload": f"T={T}, 32 experts, offset 0", "latency_us": round(lat, 2),
+                        "tokens_per_s": round(T / lat * 1e6, 1),
+                        "how": f"median of {reps} calls on identical pointers (reference steady state)"})
+            continue
         layer = pkg.MoeLayer(T, 32, 0)
-        o = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
         run = lambda: layer.run(*dev, w1, s1, w2, s2, 0, RSF, o)  # noqa: E731
         for _ in range(5):
             run()
         layer.check()
         rows = int(layer.read("pair_count", T).sum())
-        if T == 1:
-            g = torch.cuda.CUDAGraph()
-            s = torch.cuda.Stream()
-            s.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(s):
-                with torch.cuda.graph(g, stream=s):
-                    run()
-            torch.cuda.current_stream().wait_stream(s)
-            times = []
-            for _ in range(1000):
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                g.replay()
-                b.record()
-                b.synchronize()
-                times.append(a.elapsed_time(b) * 1e3)
-            lat = statistics.median(times)
-            how = "median of 1000 CUDA-graph replays"
-        else:
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            n = 50
-            a.record()
-            for _ in range(n):
+        g = torch.cuda.CUDAGraph()
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            with torch.cuda.graph(g, stream=s):
                 run()
-            b.record()
-            b.synchronize()
-            lat = a.elapsed_time(b) * 1e3 / n
-            how = f"mean of {n} back-to-back runs"
+        torch.cuda.current_stream().wait_stream(s)
+        lat = statistics.median(_event_times_us(g.replay, reps))
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(50):
+            run()
+        b.record()
+        b.synchronize()
+        eager = a.elapsed_time(b) * 1e3 / 50
         out.append({"workload": f"T={T}, 32 experts, offset 0", "latency_us": round(lat, 2),
-                    "tokens_per_s": round(T / lat * 1e6, 1), "routed_rows": rows, "how": how})
+                    "tokens_per_s": round(T / lat * 1e6, 1), "routed_rows": rows,
+                    "eager_latency_us": round(eager, 2),
+                    "how": f"median of {reps} CUDA-graph replays of the whole layer (routing included)"})
         layer.close()
     return out
 
@@ -290,7 +317,7 @@ def run_ours(args, rank, world, local):
             combine_partials(out, "all_reduce")
             host_out.copy_(out, non_blocking=True)
             torch.cuda.current_stream().synchronize()
-    e2e_ms = time_steps(e2e_step, max(3, args.steps // 2), 3, world)
+    e2e_ms = time_steps(e2e_step, max(3, args.steps // 2), 3, world) if not args.skip_e2e else float("nan")
     h2d = sum(x.numel() * x.element_size() for x in pin)
     d2h = host_out.numel() * host_out.element_size()
 
@@ -304,13 +331,13 @@ def run_ours(args, rank, world, local):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
         "latency_us": round(ms * 1e3, 1), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "e4m3 x e4m3 -> f32 accumulate, bf16 out", "data": "synthetic",
-        "config": {"workload": args.workload, "description": WORKLOADS[args.workload][2], "tokens": T,
-                   "experts_total": NE, "experts_per_gpu": E, "routed_rows_total": rows_total,
+        "config": {"workload": args.workload, "description": WORKLOADS[args.workload][3], "tokens": T,
+                   "experts_total": WORKLOADS[args.workload][2], "experts_per_gpu": E, "routed_rows_total": rows_total,
                    "routed_rows_max_rank": rows_max, "reference_pruning": True,
-                   "l2": "inputs larger than L2 (weights 11.3 GB total), no flush",
+                   "l2": f"inputs larger than L2 (weights {E * 44.04e-3:.1f} GB on this GPU), no flush",
                    "ideal_scaling_bound": round(rows_total / rows_max, 3) if rows_max else None},
         "clocks": clk.summary(),
-        "e2e": {"value": round(T / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+        "e2e": None if args.skip_e2e else {"value": round(T / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "path": "moe_fp8_b200_run_host (C ABI, host buffers)" if world == 1
                         else "pinned H2D + moe_fp8_b200_run + NCCL all-reduce + D2H"},
@@ -337,6 +364,7 @@ def run_ours(args, rank, world, local):
 
 def run_reference(args, rank, world, local):
     sys.path.insert(0, str(ROOT / "tests"))
+    entry.load_package()
     from fp8_moe_dev_b200.dist import combine_partials
     import helpers as hp
     T, offset, E, inputs, weights = make_workload(args.workload, rank, world)
@@ -362,7 +390,6 @@ def run_reference(args, rank, world, local):
         for s in range(shards):
             sl = slice(32 * s, 32 * s + 32)
             mod.run(dev[0], dev[1], dev[2], dev[3], w1[sl], s1[sl], w2[sl], s2[sl], offset + 32 * s, RSF, parts[s])
-        torch.sum(torch.stack(parts).float(), dim=0, out=None).to(torch.bfloat16, copy=False) if False else None
         out.copy_(parts[0])
         for s in range(1, shards):
             out.add_(parts[s])
@@ -371,12 +398,15 @@ def run_reference(args, rank, world, local):
     with ClockSampler(local) as clk:
         ms = time_steps(step, args.steps, args.warmup, world)
     val = round(T / ms * 1e3, 1)
-    return {"impl": "reference", "metric": "moe_layer_tokens_per_s", "value": val, "unit": "tokens/s",
+    small = None
+    if rank == 0 and world == 1 and not args.skip_small:
+        small = small_config_latencies(None, weights, dev[1], reference_mod=mod)
+    return {"impl": "reference", "configs": small, "metric": "moe_layer_tokens_per_s", "value": val, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
             "latency_us": round(ms * 1e3, 1), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "e4m3 x e4m3 -> f32 accumulate, bf16 out", "data": "synthetic",
-            "config": {"workload": args.workload, "description": WORKLOADS[args.workload][2], "tokens": T,
-                       "experts_total": NE, "experts_per_gpu": E,
+            "config": {"workload": args.workload, "description": WORKLOADS[args.workload][3], "tokens": T,
+                       "experts_total": WORKLOADS[args.workload][2], "experts_per_gpu": E,
                        "how": f"{shards} sequential reference calls of 32 experts per rank on identical pointers "
                               "(its pointer-keyed caches may hit), bf16 adds, same NCCL all-reduce"},
             "clocks": clk.summary(),
@@ -395,8 +425,10 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="t12288_e256")
     ap.add_argument("--skip-small", action="store_true", help="skip the T=1/16/1024 single-shard latencies")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the host fp32 baseline")
+    ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3)
+    if not args.skip_e2e:
+        args.warmup = max(args.warmup, 3)
     rank, world, local = dist_setup(args.gpus)
     line = run_ours(args, rank, world, local) if args.impl == "ours" else run_reference(args, rank, world, local)
     if rank == 0 and line is not None:

