@@ -223,9 +223,31 @@ def small_config_latencies(pkg, weights, bias_dev, reference_mod=None):
                 run()
             torch.cuda.synchronize()
             lat = statistics.median(_event_times_us(run, reps))
+            # fresh inputs: the same values in three rotating buffer sets, so that the
+            # reference's pointer-keyed caches miss and it runs routing, its host read-back
+            # and its descriptor set-up, as it must whenever the activations change
+            sets = [[x.clone() for x in (dev[0], dev[2], dev[3])] + [torch.zeros_like(o)] for _ in range(3)]
+            state = {"i": 0}
+
+            def run_fresh():
+                lg, hd, hs, oo = sets[state["i"] % 3]
+                state["i"] += 1
+                reference_mod.run(lg, dev[1], hd, hs, w1, s1, w2, s2, 0, RSF, oo)
+            for _ in range(6):
+                run_fresh()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            n_fresh = 100
+            for _ in range(n_fresh):
+                run_fresh()
+            torch.cuda.synchronize()
+            fresh = (time.perf_counter() - t0) / n_fresh * 1e6
             out.append({"workload": f"T={T}, 32 experts, offset 0", "latency_us": round(lat, 2),
                         "tokens_per_s": round(T / lat * 1e6, 1),
-                        "how": f"median of {reps} calls on identical pointers (reference steady state)"})
+                        "fresh_inputs_latency_us": round(fresh, 2),
+                        "how": f"median of {reps} calls on identical pointers (reference steady state: cached "
+                               "routing, internal graph replay); fresh_inputs = mean wall time per call over "
+                               f"{n_fresh} calls rotating three input buffer sets (its caches miss)"})
             continue
         layer = pkg.MoeLayer(T, 32, 0)
         run = lambda: layer.run(*dev, w1, s1, w2, s2, 0, RSF, o)  # noqa: E731
@@ -248,7 +270,14 @@ def small_config_latencies(pkg, weights, bias_dev, reference_mod=None):
         b.record()
         b.synchronize()
         eager = a.elapsed_time(b) * 1e3 / 50
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(100):
+            run()
+        torch.cuda.synchronize()
+        wall = (time.perf_counter() - t0) / 100 * 1e6
         out.append({"workload": f"T={T}, 32 experts, offset 0", "latency_us": round(lat, 2),
+                    "eager_wall_us_per_call": round(wall, 2),
                     "tokens_per_s": round(T / lat * 1e6, 1), "routed_rows": rows,
                     "eager_latency_us": round(eager, 2),
                     "how": f"median of {reps} CUDA-graph replays of the whole layer (routing included)"})

@@ -123,6 +123,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
+    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&sh->full[s]), 1);
@@ -140,6 +141,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
     }
+    // Everything above is independent of earlier kernels; from here on their results are read.
+    pdl_wait();
+    const int total_tiles = ws.num_tiles[0] * kTilesN;
+    if ((int)blockIdx.x >= total_tiles) return;  // nothing for this CTA: leave before touching TMEM
     if (warp == 2) {
         tmem_alloc(smem_u32(&sh->tmem_base), kTmemCols);
         tmem_relinquish();
@@ -149,7 +154,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
     tc_fence_after();
     const uint32_t tmem_base = sh->tmem_base;
     volatile int* abort_flag = &sh->abort;
-    const int total_tiles = ws.num_tiles[0] * kTilesN;
 
     if (warp < 4) {
         setmaxnreg_dec<56>();
@@ -416,17 +420,25 @@ cudaError_t configure_gemm_kernels()
                                 (int)kGemmSmemBytes);
 }
 
+int gemm_tiles_n(int mode) { return mode == 1 ? kInter / kBlock : kHidden / kTileN; }
+
 cudaError_t launch_grouped_gemm(int mode, const void* tmap_a, const void* tmap_b, const Workspace& ws,
                                 const float* w_scale, int silu_exact, int num_ctas, cudaStream_t stream)
 {
     const CUtensorMap* ma = static_cast<const CUtensorMap*>(tmap_a);
     const CUtensorMap* mb = static_cast<const CUtensorMap*>(tmap_b);
-    if (mode == 1) {
-        grouped_gemm_kernel<1><<<num_ctas, kGemmThreads, kGemmSmemBytes, stream>>>(*ma, *mb, ws, w_scale, silu_exact);
-    } else {
-        grouped_gemm_kernel<2><<<num_ctas, kGemmThreads, kGemmSmemBytes, stream>>>(*ma, *mb, ws, w_scale, silu_exact);
-    }
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(num_ctas < 1 ? 1 : num_ctas);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = kGemmSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (mode == 1) return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<1>, *ma, *mb, ws, w_scale, silu_exact);
+    return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<2>, *ma, *mb, ws, w_scale, silu_exact);
 }
 
 }  // namespace moe

@@ -39,12 +39,16 @@ struct DispatchPolicy {
     int renorm;             // prune: kept weights rescaled by sum(local) / sum(kept)
 };
 
-// Integer control block, zeroed by a memset node at the start of every call.
+// Integer control block.  Zeroed when the handle is created; after that the last CTA of the
+// routing kernel turns the counters into offsets and tiles and puts them back to zero for
+// the next call, so a call needs no memset node.
 struct Control {
     int expert_count[kMaxLocalExperts];  // routed rows per local expert (atomic counters)
     int status;                          // 0 ok; otherwise the first error a kernel recorded
     int status_detail;
-    int pad[2];
+    int blocks_done;                     // routing CTAs finished (ticket for the last-CTA scan)
+    int pad;
+    int expert_rows[kMaxLocalExperts];   // copy of the counters of the last call (diagnostics)
 };
 
 enum KernelStatus : int {

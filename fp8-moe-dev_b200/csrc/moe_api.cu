@@ -14,8 +14,7 @@
 
 namespace moe {
 cudaError_t launch_route_dispatch(const float*, const void*, const Workspace&, int, int, int, float,
-                                  const DispatchPolicy&, cudaStream_t);
-cudaError_t launch_scan_tiles(const Workspace&, int, cudaStream_t);
+                                  const DispatchPolicy&, int, cudaStream_t);
 cudaError_t launch_permute(const void*, const float*, const Workspace&, int, cudaStream_t);
 cudaError_t launch_combine(const Workspace&, void*, int, cudaStream_t);
 int encode_kmajor_u8_map(void*, const void*, uint64_t, uint64_t, uint64_t, uint32_t);
@@ -23,6 +22,7 @@ size_t tensor_map_bytes();
 cudaError_t configure_gemm_kernels();
 cudaError_t launch_grouped_gemm(int, const void*, const void*, const Workspace&, const float*, int, int,
                                 cudaStream_t);
+int gemm_tiles_n(int mode);
 }  // namespace moe
 
 using namespace moe;
@@ -94,6 +94,7 @@ struct moe_fp8_b200_ctx {
     int num_sms = 0;
     int opt_reference_pruning = 1;
     int opt_exact_silu = 0;
+    bool counters_dirty = false;
     uint8_t* base = nullptr;
     Layout layout{};
     Workspace ws{};
@@ -188,26 +189,43 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
         ++h->timed_runs;
     }
     auto mark = [&](int i) { if (ev) cudaEventRecord(ev[i], stream); };
-    cudaError_t e = cudaMemsetAsync(h->ws.ctrl, 0, sizeof(Control), stream);
+    // The routing kernel's last CTA leaves the counters at zero for the next call; only after
+    // a failed launch (chain cut short) are they cleared explicitly.
+    cudaError_t e = cudaSuccess;
+    if (h->counters_dirty) {
+        e = cudaMemsetAsync(h->ws.ctrl, 0, sizeof(Control), stream);
+        h->counters_dirty = false;
+    }
     mark(0);
     if (e == cudaSuccess)
         e = launch_route_dispatch(a.routing_logits, a.routing_bias, h->ws, T, (int)a.local_expert_offset, E,
-                                  (float)a.routed_scaling_factor, pol, stream);
+                                  (float)a.routed_scaling_factor, pol, /*do_scan=*/1, stream);
     mark(1);
-    if (e == cudaSuccess) e = launch_scan_tiles(h->ws, E, stream);
     mark(2);
+    // most 128-row tiles this batch can produce: one per (token, expert) pair, and no more
+    // than the rows / 128 plus one partial tile per local expert
+    const long long pairs = 8LL * T;
+    long long m_tiles = pairs / kTileM + E;
+    if (m_tiles > pairs) m_tiles = pairs;
+    auto ctas = [&](int mode) {
+        const long long t = m_tiles * gemm_tiles_n(mode);
+        return (int)(t < h->num_sms ? t : h->num_sms);
+    };
     if (e == cudaSuccess) e = launch_permute(a.hidden_states, a.hidden_states_scale, h->ws, T, stream);
     mark(3);
     if (e == cudaSuccess)
         e = launch_grouped_gemm(1, h->tmap_a1, h->tmap_w1, h->ws, a.gemm1_weights_scale, h->opt_exact_silu,
-                                h->num_sms, stream);
+                                ctas(1), stream);
     mark(4);
     if (e == cudaSuccess)
-        e = launch_grouped_gemm(2, h->tmap_a2, h->tmap_w2, h->ws, a.gemm2_weights_scale, 0, h->num_sms, stream);
+        e = launch_grouped_gemm(2, h->tmap_a2, h->tmap_w2, h->ws, a.gemm2_weights_scale, 0, ctas(2), stream);
     mark(5);
     if (e == cudaSuccess) e = launch_combine(h->ws, a.output, T, stream);
     mark(6);
-    if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    if (e != cudaSuccess) {
+        h->counters_dirty = true;
+        return fail(h, MOE_FP8_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    }
     return MOE_FP8_B200_OK;
 }
 
@@ -460,7 +478,7 @@ int moe_fp8_b200_read_intermediate(moe_fp8_b200_handle h, int buffer, void* dst,
     const void* src = nullptr;
     size_t size = 0;
     switch (buffer) {
-        case MOE_FP8_B200_BUF_EXPERT_COUNT: src = w.ctrl->expert_count; size = sizeof(int) * h->num_local_experts; break;
+        case MOE_FP8_B200_BUF_EXPERT_COUNT: src = w.ctrl->expert_rows; size = sizeof(int) * h->num_local_experts; break;
         case MOE_FP8_B200_BUF_EXPERT_OFFSET: src = w.expert_offset; size = sizeof(int) * (h->num_local_experts + 1); break;
         case MOE_FP8_B200_BUF_TOPK_IDX: src = w.topk_idx; size = sizeof(int) * T * kTopK; break;
         case MOE_FP8_B200_BUF_TOPK_WEIGHT: src = w.topk_weight; size = sizeof(float) * T * kTopK; break;

@@ -24,7 +24,7 @@
 
 namespace moe {
 cudaError_t launch_route_dispatch(const float*, const void*, const Workspace&, int, int, int, float,
-                                  const DispatchPolicy&, cudaStream_t);
+                                  const DispatchPolicy&, int, cudaStream_t);
 }
 using namespace moe;
 
@@ -123,7 +123,7 @@ extern "C" int moe_fp8_b200_route_noalloc(const float* routing_logits, const voi
     e = cudaMemsetAsync(ws.ctrl, 0, sizeof(Control), stream);
     if (e == cudaSuccess)
         e = launch_route_dispatch(routing_logits, routing_bias, ws, num_tokens, (int)local_expert_offset,
-                                  num_local_experts, (float)routed_scaling_factor, pol, stream);
+                                  num_local_experts, (float)routed_scaling_factor, pol, /*do_scan=*/0, stream);
     if (e == cudaSuccess)
         e = cudaMemcpyAsync(expert_count_out, ws.ctrl->expert_count, sizeof(int) * (size_t)num_local_experts,
                             cudaMemcpyDeviceToDevice, stream);

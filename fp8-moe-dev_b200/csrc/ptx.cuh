@@ -171,6 +171,14 @@ __host__ __device__ constexpr uint32_t make_idesc_e4m3(int m, int n) {
            | (static_cast<uint32_t>(m >> 4) << 24);   // M / 16
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// Every kernel of the layer is launched with the programmatic-stream-serialization attribute:
+// it may start while its predecessor drains, runs its set-up, and calls pdl_wait() before it
+// touches anything the predecessor wrote (the wait returns once all earlier grids have
+// completed and their memory is visible).  pdl_launch_dependents() lets the successor start.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- misc
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");

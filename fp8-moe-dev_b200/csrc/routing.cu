@@ -4,6 +4,7 @@
 // their 1x128 scales into expert-contiguous order.  Nothing here reads a device value on
 // the host, so the whole chain can sit in a CUDA graph.
 #include "layer.cuh"
+#include "ptx.cuh"
 
 namespace moe {
 
@@ -118,16 +119,78 @@ __device__ __forceinline__ void dispatch_one_shard(
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Offsets and tiles, run by the LAST routing CTA to finish (256 threads).  Every expert's
+// row count is rounded up to 128, an exclusive scan gives the first packed row of each
+// expert, and each 128-row tile gets its expert and its number of valid rows; the counters
+// are then cleared for the next call.  (The reference does the scan in a separate one-warp
+// kernel and then reads the totals back on the host, kernel/moe_fp8.cu:838-870, 2816-2824.)
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void scan_tiles_block(const Workspace& ws, int num_local_experts)
+{
+    __shared__ int s_warp_total[kMaxLocalExperts / 32];
+    const int e = threadIdx.x;
+    const int lane = e & 31, warp = e >> 5;
+    // the counters were written by other CTAs' atomics: read them past the L1
+    const int m = (e < num_local_experts) ? __ldcg(&ws.ctrl->expert_count[e]) : 0;
+    const int k = (m + kTileM - 1) / kTileM;
+    int incl = k;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += y;
+    }
+    if (lane == 31) s_warp_total[warp] = incl;
+    __syncthreads();
+    int warp_base = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < kMaxLocalExperts / 32; ++w) {
+        const int t = s_warp_total[w];
+        if (w < warp) warp_base += t;
+        total += t;
+    }
+    const int base = warp_base + incl - k;  // exclusive prefix, in tiles
+    const bool overflow = total > ws.max_tiles || total * kTileM > ws.m_cap;
+    if (overflow) total = 0;
+    if (e < num_local_experts) {
+        ws.expert_offset[e] = overflow ? 0 : base * kTileM;
+        ws.ctrl->expert_rows[e] = m;
+        ws.ctrl->expert_count[e] = 0;
+    }
+    if (e == 0) {
+        ws.expert_offset[num_local_experts] = total * kTileM;
+        ws.num_tiles[0] = total;
+        ws.ctrl->blocks_done = 0;
+        if (overflow) {
+            ws.ctrl->status = kStatusRowOverflow;
+            ws.ctrl->status_detail = warp_base + incl;
+        }
+    }
+    if (!overflow && e < num_local_experts) {
+        for (int j = 0; j < k; ++j) {
+            ws.tile_expert[base + j] = e;
+            const int left = m - j * kTileM;
+            ws.tile_rows[base + j] = left < kTileM ? left : kTileM;
+        }
+    }
+}
+
 constexpr int kRouteWarps = 8;
 
 __global__ void __launch_bounds__(kRouteWarps * 32) route_dispatch_kernel(
     const float* __restrict__ logits, const __nv_bfloat16* __restrict__ bias, Workspace ws, int T,
-    int local_expert_offset, int num_local_experts, float rsf, DispatchPolicy pol)
+    int local_expert_offset, int num_local_experts, float rsf, DispatchPolicy pol, int do_scan)
 {
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * kRouteWarps + (threadIdx.x >> 5);
-    if (t >= T) return;
     constexpr uint32_t kFull = 0xffffffffu;
+    pdl_launch_dependents();
+    pdl_wait();  // the previous call's kernels still read the pair tables and offsets
+    if (do_scan && blockIdx.x == 0 && threadIdx.x == 0) {
+        ws.ctrl->status = kStatusOk;
+        ws.ctrl->status_detail = 0;
+    }
+    if (t < T) {
 
     float s[kNumGroups];   // unbiased sigmoid of expert 32 w + lane
     float sb[kNumGroups];  // biased score, later masked
@@ -230,50 +293,21 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_dispatch_kernel(
         }
         ws.pair_count[t] = n_pairs;
     }
-}
+    }  // t < T
 
-// ---------------------------------------------------------------------------------------
-// Offsets and tiles.  One CTA: every expert's row count is rounded up to 128, an
-// exclusive scan gives the first packed row of each expert, and each 128-row tile gets
-// its expert and its number of valid rows.  (The reference does the scan with one warp
-// and then reads the totals back on the host, kernel/moe_fp8.cu:838-870, 2816-2824.)
-// ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kMaxLocalExperts) scan_tiles_kernel(Workspace ws, int num_local_experts)
-{
-    __shared__ int s_tiles[kMaxLocalExperts];
-    __shared__ int s_scan[kMaxLocalExperts + 1];
-    const int e = threadIdx.x;
-    const int m = (e < num_local_experts) ? ws.ctrl->expert_count[e] : 0;
-    const int k = (m + kTileM - 1) / kTileM;
-    s_tiles[e] = k;
+    if (!do_scan) return;
+    // Last CTA to get here turns the counters into offsets and tiles.
+    __shared__ int s_is_last;
     __syncthreads();
-    if (e == 0) {
-        int acc = 0;
-        for (int i = 0; i < kMaxLocalExperts; ++i) { s_scan[i] = acc; acc += s_tiles[i]; }
-        s_scan[kMaxLocalExperts] = acc;
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const int ticket = atomicAdd(&ws.ctrl->blocks_done, 1);
+        s_is_last = (ticket == (int)gridDim.x - 1) ? 1 : 0;
     }
     __syncthreads();
-    int total = s_scan[kMaxLocalExperts];
-    const bool overflow = total > ws.max_tiles || total * kTileM > ws.m_cap;
-    if (overflow) {
-        if (e == 0) {
-            atomicCAS(&ws.ctrl->status, kStatusOk, kStatusRowOverflow);
-            ws.ctrl->status_detail = total;
-        }
-        total = 0;
-    }
-    if (e < num_local_experts) ws.expert_offset[e] = overflow ? 0 : s_scan[e] * kTileM;
-    if (e == 0) {
-        ws.expert_offset[num_local_experts] = total * kTileM;
-        ws.num_tiles[0] = total;
-    }
-    if (!overflow && e < num_local_experts) {
-        const int base = s_scan[e];
-        for (int j = 0; j < k; ++j) {
-            ws.tile_expert[base + j] = e;
-            const int left = m - j * kTileM;
-            ws.tile_rows[base + j] = left < kTileM ? left : kTileM;
-        }
+    if (s_is_last) {
+        __threadfence();
+        scan_tiles_block(ws, num_local_experts);
     }
 }
 
@@ -290,6 +324,8 @@ __global__ void __launch_bounds__(kPermuteWarps * 32) permute_rows_kernel(
 {
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * kPermuteWarps + (threadIdx.x >> 5);
+    pdl_launch_dependents();
+    pdl_wait();
     if (t >= T) return;
     if (ws.num_tiles[0] == 0) return;
     const int n_pairs = ws.pair_count[t];
@@ -327,6 +363,8 @@ constexpr int kCombineThreads = 448;  // 448 threads x 2 x 8 columns = 7168
 __global__ void __launch_bounds__(kCombineThreads) combine_kernel(Workspace ws, __nv_bfloat16* __restrict__ out, int T)
 {
     const int t = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     if (t >= T) return;
     int n_pairs = ws.pair_count[t];
     if (ws.num_tiles[0] == 0) n_pairs = 0;
@@ -365,37 +403,48 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(Workspace ws, 
 }
 
 // ---------------------------------------------------------------------------------------
-// Launchers (called by the C-ABI layer).
+// Launchers (called by the C-ABI layer).  All launches carry the programmatic stream
+// serialization attribute (see ptx.cuh).
 // ---------------------------------------------------------------------------------------
-cudaError_t launch_route_dispatch(const float* logits, const void* bias, const Workspace& ws, int T,
-                                  int local_expert_offset, int num_local_experts, float rsf,
-                                  const DispatchPolicy& pol, cudaStream_t stream)
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args)
 {
-    const int grid = (T + kRouteWarps - 1) / kRouteWarps;
-    route_dispatch_kernel<<<grid, kRouteWarps * 32, 0, stream>>>(
-        logits, static_cast<const __nv_bfloat16*>(bias), ws, T, local_expert_offset, num_local_experts, rsf, pol);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
-cudaError_t launch_scan_tiles(const Workspace& ws, int num_local_experts, cudaStream_t stream)
+cudaError_t launch_route_dispatch(const float* logits, const void* bias, const Workspace& ws, int T,
+                                  int local_expert_offset, int num_local_experts, float rsf,
+                                  const DispatchPolicy& pol, int do_scan, cudaStream_t stream)
 {
-    scan_tiles_kernel<<<1, kMaxLocalExperts, 0, stream>>>(ws, num_local_experts);
-    return cudaGetLastError();
+    const int grid = (T + kRouteWarps - 1) / kRouteWarps;
+    return launch_pdl(route_dispatch_kernel, dim3(grid), dim3(kRouteWarps * 32), 0, stream, logits,
+                      static_cast<const __nv_bfloat16*>(bias), ws, T, local_expert_offset, num_local_experts, rsf, pol,
+                      do_scan);
 }
 
 cudaError_t launch_permute(const void* hidden, const float* hidden_scale, const Workspace& ws, int T,
                            cudaStream_t stream)
 {
     const int grid = (T + kPermuteWarps - 1) / kPermuteWarps;
-    permute_rows_kernel<<<grid, kPermuteWarps * 32, 0, stream>>>(
-        static_cast<const uint8_t*>(hidden), hidden_scale, ws, T);
-    return cudaGetLastError();
+    return launch_pdl(permute_rows_kernel, dim3(grid), dim3(kPermuteWarps * 32), 0, stream,
+                      static_cast<const uint8_t*>(hidden), hidden_scale, ws, T);
 }
 
 cudaError_t launch_combine(const Workspace& ws, void* out, int T, cudaStream_t stream)
 {
-    combine_kernel<<<T, kCombineThreads, 0, stream>>>(ws, static_cast<__nv_bfloat16*>(out), T);
-    return cudaGetLastError();
+    return launch_pdl(combine_kernel, dim3(T), dim3(kCombineThreads), 0, stream, ws, static_cast<__nv_bfloat16*>(out),
+                      T);
 }
 
 }  // namespace moe
