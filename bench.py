@@ -4,7 +4,8 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 One "step" = one pass of the whole layer (routing, dispatch, permute, GEMM1+SwiGLU+requant,
-GEMM2, combine, and for N > 1 the NCCL sum of the partial outputs) over one synthetic batch.
+GEMM2, combine, and for N > 1 the NCCL sum of the partial outputs: reduce-scatter by default,
+--collective all_reduce for replicated outputs) over one synthetic batch.
 The default workload is the large-prefill configuration: T = 12288 tokens, all 256 experts,
 split evenly over the N GPUs (N = 1 holds all 256 on one GPU).  Rank 0 prints ONE JSON line.
 
@@ -314,9 +315,12 @@ def run_ours(args, rank, world, local):
     layer = pkg.MoeLayer(T, E, local)
     out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
 
-    def step():
+    per = (T + world - 1) // world
+    scat = torch.empty(per, H, dtype=torch.bfloat16, device="cuda")
+
+    def step(mode=args.collective):
         layer.run(*dev, w1, s1, w2, s2, offset, RSF, out)
-        combine_partials(out, "all_reduce")
+        combine_partials(out, mode, scatter_out=scat)
 
     step()
     layer.check()
@@ -343,12 +347,16 @@ def run_ours(args, rank, world, local):
             dev[2].copy_(pin[1], non_blocking=True)
             dev[3].copy_(pin[2], non_blocking=True)
             layer.run(*dev, w1, s1, w2, s2, offset, RSF, out)
-            combine_partials(out, "all_reduce")
-            host_out.copy_(out, non_blocking=True)
+            res = combine_partials(out, args.collective, scatter_out=scat)
+            host_out[:res.shape[0]].copy_(res, non_blocking=True)
             torch.cuda.current_stream().synchronize()
     e2e_ms = time_steps(e2e_step, max(3, args.steps // 2), 3, world) if not args.skip_e2e else float("nan")
     h2d = sum(x.numel() * x.element_size() for x in pin)
-    d2h = host_out.numel() * host_out.element_size()
+    d2h = (host_out if (world == 1 or args.collective == "all_reduce") else scat).numel() * 2
+    other_ms = None
+    if world > 1:
+        other = "all_reduce" if args.collective == "reduce_scatter" else "reduce_scatter"
+        other_ms = time_steps(lambda: step(other), max(5, args.steps // 2), 3, world)
 
     pk = peaks()
     g1_ms = max_over_ranks(stages["gemm1"], world)
@@ -364,12 +372,14 @@ def run_ours(args, rank, world, local):
                    "experts_total": WORKLOADS[args.workload][2], "experts_per_gpu": E, "routed_rows_total": rows_total,
                    "routed_rows_max_rank": rows_max, "reference_pruning": True,
                    "l2": f"inputs larger than L2 (weights {E * 44.04e-3:.1f} GB on this GPU), no flush",
-                   "ideal_scaling_bound": round(rows_total / rows_max, 3) if rows_max else None},
+                   "ideal_scaling_bound": round(rows_total / rows_max, 3) if rows_max else None,
+                   "collective": None if world == 1 else args.collective,
+                   "other_collective_ms_per_step": None if other_ms is None else round(other_ms, 4)},
         "clocks": clk.summary(),
         "e2e": None if args.skip_e2e else {"value": round(T / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "path": "moe_fp8_b200_run_host (C ABI, host buffers)" if world == 1
-                        else "pinned H2D + moe_fp8_b200_run + NCCL all-reduce + D2H"},
+                        else f"pinned H2D + moe_fp8_b200_run + NCCL {args.collective} + D2H"},
         "gpu_launches": 6 * args.steps * world,
         "stage_ms": {k: round(max_over_ranks(v, world), 4) for k, v in stages.items()},
         "layer_tflops": round(rows_max * FLOPS_PER_ROW / (ms * 1e-3) / 1e12, 1),
@@ -413,6 +423,7 @@ def run_reference(args, rank, world, local):
     w1, s1, w2, s2 = weights
     shards = E // 32
     parts = [torch.zeros(T, H, dtype=torch.bfloat16, device="cuda") for _ in range(shards)]
+    scat = torch.empty((T + world - 1) // world, H, dtype=torch.bfloat16, device="cuda")
     out = torch.zeros(T, H, dtype=torch.bfloat16, device="cuda")
 
     def step():
@@ -422,7 +433,7 @@ def run_reference(args, rank, world, local):
         out.copy_(parts[0])
         for s in range(1, shards):
             out.add_(parts[s])
-        combine_partials(out, "all_reduce")
+        combine_partials(out, args.collective, scatter_out=scat)
 
     with ClockSampler(local) as clk:
         ms = time_steps(step, args.steps, args.warmup, world)
@@ -452,6 +463,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="t12288_e256")
+    ap.add_argument("--collective", choices=["reduce_scatter", "all_reduce"], default="reduce_scatter",
+                    help="how the ranks' bf16 partial outputs are summed for N > 1: reduce_scatter leaves rank r "
+                         "with tokens [r*T/N, (r+1)*T/N) (the inverse of the all-gather that replicated the "
+                         "inputs); all_reduce leaves every rank with all T tokens")
     ap.add_argument("--skip-small", action="store_true", help="skip the T=1/16/1024 single-shard latencies")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the host fp32 baseline")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")

@@ -102,6 +102,14 @@ __device__ __forceinline__ void promote32(float (&acc)[128], const uint32_t (&r)
     for (int j = 0; j < 32; ++j) acc[OFF + j] = fmaf(__uint_as_float(r[j]), s, acc[OFF + j]);
 }
 
+// Scale load that the compiler cannot sink towards its use: issued (as volatile asm) one
+// K block ahead, so that its L2 latency is covered by the whole block's promotion work.
+__device__ __forceinline__ float ld_scale_early(const float* p) {
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
 __device__ __forceinline__ float round_bf16(float x) {
     return __bfloat162float(__float2bfloat16_rn(x));
 }
@@ -257,16 +265,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
 #pragma unroll
             for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
 
-            float sa_n = __ldg(sfa);
-            float lo_n = __ldg(sw_lo);
-            float hi_n = __ldg(sw_hi);
+            float sa_n = ld_scale_early(sfa);
+            float lo_n = ld_scale_early(sw_lo);
+            float hi_n = ld_scale_early(sw_hi);
             for (int kb = 0; kb < kKBlocks; ++kb, ++it) {
                 const float s_lo = sa_n * lo_n;
                 const float s_hi = sa_n * hi_n;
                 if (kb + 1 < kKBlocks) {
-                    sa_n = __ldg(sfa + (size_t)(kb + 1) * ws.m_cap);
-                    lo_n = __ldg(sw_lo + kb + 1);
-                    hi_n = __ldg(sw_hi + kb + 1);
+                    sa_n = ld_scale_early(sfa + (size_t)(kb + 1) * ws.m_cap);
+                    lo_n = ld_scale_early(sw_lo + kb + 1);
+                    hi_n = ld_scale_early(sw_hi + kb + 1);
                 }
                 const uint32_t as = it & 1u;
                 const uint32_t aph = (it >> 1) & 1u;

@@ -1,0 +1,80 @@
+"""Expert-parallel path on two GPUs: every rank routes all tokens, computes its half of the
+256 experts, NCCL sums the bf16 partial outputs.  Skipped on boxes with fewer than two GPUs
+(the CPU form of the same plan runs in tests/test_dist_cpu.py over gloo)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, T, q):
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    sys.path.insert(0, str(root))
+    sys.path.insert(0, str(root / "tests"))
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    entry.load_package()
+    from fp8_moe_dev_b200 import gen
+    from fp8_moe_dev_b200.dist import ShardedMoe, token_range
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        logits, bias = gen.make_routing(T, seed=11)
+        hidden, hscale = gen.make_hidden(T, seed=12)
+        dev = [x.cuda() for x in (logits, bias, hidden, hscale)]
+        moe = ShardedMoe(T)
+        E = moe.num_local_experts
+        w = gen.make_shard(moe.local_expert_offset, E, device="cuda", out_device="cuda")
+        out = torch.empty(T, 7168, dtype=torch.bfloat16, device="cuda")
+        partial = torch.empty_like(out)
+        moe.layer.run(*dev, *w, moe.local_expert_offset, 2.5, partial)
+        moe.layer.check()
+        full = moe.run(*dev, *w, 2.5, out, mode="all_reduce").clone()
+        moe.layer.check()
+        # the same sum done by hand: gather the partial outputs and add them in rank order
+        parts = [torch.empty_like(partial) for _ in range(world)]
+        dist.all_gather(parts, partial)
+        want = parts[0].clone()
+        for p in parts[1:]:
+            want += p
+        ok_sum = torch.equal(full, want)
+        scat = moe.run(*dev, *w, 2.5, out, mode="reduce_scatter")
+        lo, hi = token_range(rank, world, T)
+        ok_scatter = torch.equal(scat[:hi - lo], want[lo:hi])
+        nonzero = bool(full.float().abs().sum() > 0)
+        q.put((rank, ok_sum, ok_scatter, nonzero))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_expert_parallel_sum():
+    world, T = 2, 96
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, T, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(600)
+        assert p.exitcode == 0
+    res = sorted(q.get(timeout=10) for _ in range(world))
+    assert res == [(0, True, True, True), (1, True, True, True)], res
