@@ -48,8 +48,10 @@ struct GemmShared {
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint64_t amax_bar[2];
+    uint64_t splitk_bar;
     uint32_t tmem_base;
     int abort;
+    int splitk_last;
     float amax[2][2][kTileM];
 };
 
@@ -62,21 +64,43 @@ struct TileCoord {
 // Tile id -> (expert, n tile, first packed row, valid rows).  Tiles of one expert are
 // numbered n-major / m-minor so that CTAs working on neighbouring ids share a weight tile.
 __device__ __forceinline__ TileCoord decode_tile(const Workspace& ws, int id, int n_tiles_n) {
-    const int mt = id / n_tiles_n;
-    const int e = ws.tile_expert[mt];
-    const int off0 = ws.expert_offset[e];
-    const int off1 = ws.expert_offset[e + 1];
-    const int mt0 = off0 / kTileM;
-    const int k = (off1 - off0) / kTileM;
-    const int local = id - mt0 * n_tiles_n;
-    const int n = local / k;
-    const int m_tile = mt0 + (local - n * k);
+    // one 16-byte record per tile: {expert, first tile of the expert, its tile count, its rows}
+    const int4 info = ws.tile_info[id / n_tiles_n];
+    const int local = id - info.y * n_tiles_n;
+    const int n = local / info.z;
+    const int j = local - n * info.z;
+    const int left = info.w - j * kTileM;
     TileCoord c;
-    c.e = e;
+    c.e = info.x;
     c.n = n;
-    c.row0 = m_tile * kTileM;
-    c.rows = ws.tile_rows[m_tile];
+    c.row0 = (info.y + j) * kTileM;
+    c.rows = left < kTileM ? left : kTileM;
     return c;
+}
+
+// Work units.  Normally one unit = one tile over the whole K range.  When there are at most
+// half as many tiles as CTAs (decode-sized batches) every tile is cut into `split` K ranges so
+// that all SMs stream weights; the partial tiles are summed by the last unit to finish.
+struct UnitPlan {
+    int units, split;
+};
+template <int KBLOCKS, bool SPLITK>
+__device__ __forceinline__ UnitPlan plan_units(int total_tiles, int num_ctas) {
+    UnitPlan p;
+    p.split = 1;
+    if (SPLITK && total_tiles > 0 && total_tiles * 2 <= num_ctas) {
+        int s = num_ctas / total_tiles;
+        const int max_split = KBLOCKS / 4;  // at least four K blocks per unit
+        p.split = s < max_split ? s : max_split;
+    }
+    p.units = total_tiles * p.split;
+    return p;
+}
+// K-block range [kb0, kb1) of split `s` out of `split`
+template <int KBLOCKS>
+__device__ __forceinline__ void unit_range(int s, int split, int& kb0, int& kb1) {
+    kb0 = (KBLOCKS * s) / split;
+    kb1 = (KBLOCKS * (s + 1)) / split;
 }
 
 // tcgen05.wait::ld with the destination registers as in/out operands, so that the
@@ -96,10 +120,24 @@ __device__ __forceinline__ void tmem_ld_wait2(uint32_t (&a)[32], uint32_t (&b)[3
                  : "memory");
 }
 
-template <int OFF>
+// acc[OFF + j] += raw[j] * s for 32 accumulator columns.  PACKED uses the two-wide fp32 FMA of
+// sm_100 (same IEEE result per element, half the issue slots); it pays off in GEMM1, while in
+// GEMM2 the extra register pairing costs more than it saves (measured), so GEMM2 stays scalar.
+template <int OFF, bool PACKED>
 __device__ __forceinline__ void promote32(float (&acc)[128], const uint32_t (&r)[32], float s) {
+    if (PACKED) {
+        const float2 s2 = make_float2(s, s);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) acc[OFF + j] = fmaf(__uint_as_float(r[j]), s, acc[OFF + j]);
+        for (int j = 0; j < 32; j += 2) {
+            const float2 d = __ffma2_rn(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), s2,
+                                        make_float2(acc[OFF + j], acc[OFF + j + 1]));
+            acc[OFF + j] = d.x;
+            acc[OFF + j + 1] = d.y;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[OFF + j] = fmaf(__uint_as_float(r[j]), s, acc[OFF + j]);
+    }
 }
 
 // Scale load that the compiler cannot sink towards its use: issued (as volatile asm) one
@@ -115,7 +153,9 @@ __device__ __forceinline__ float round_bf16(float x) {
 }
 
 // MODE 1: GEMM1 + SwiGLU + requant (K = 7168).  MODE 2: GEMM2 -> bf16 Y (K = 2048).
-template <int MODE>
+// SPLITK compiles the split-K path in; the plain instantiation carries none of its code
+// (having it in the main kernel cost 5-7 % on mid-size batches through register pressure).
+template <int MODE, bool SPLITK>
 __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
     const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, Workspace ws,
     const float* __restrict__ w_scale, int silu_exact)
@@ -142,6 +182,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
             mbar_init(smem_u32(&sh->acc_empty[s]), kEpilogueWarps);
             mbar_init(smem_u32(&sh->amax_bar[s]), kEpilogueThreads);
         }
+        mbar_init(smem_u32(&sh->splitk_bar), kEpilogueThreads);
         sh->abort = 0;
         fence_mbar_init();
     }
@@ -152,7 +193,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
     // Everything above is independent of earlier kernels; from here on their results are read.
     pdl_wait();
     const int total_tiles = ws.num_tiles[0] * kTilesN;
-    if ((int)blockIdx.x >= total_tiles) return;  // nothing for this CTA: leave before touching TMEM
+    const UnitPlan plan = plan_units<kKBlocks, SPLITK>(total_tiles, (int)gridDim.x);
+    if ((int)blockIdx.x >= plan.units) return;  // nothing for this CTA: leave before touching TMEM
     if (warp == 2) {
         tmem_alloc(smem_u32(&sh->tmem_base), kTmemCols);
         tmem_relinquish();
@@ -164,14 +206,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
     volatile int* abort_flag = &sh->abort;
 
     if (warp < 4) {
-        setmaxnreg_dec<56>();
+        // register split between the producer warpgroup and the two promotion warpgroups:
+        // 56 / 224 for GEMM1, 40 / 232 for GEMM2 (both sum to <= 64 K registers per SM)
+        if (MODE == 1) setmaxnreg_dec<56>(); else setmaxnreg_dec<40>();
         if (warp == 0 && lane == 0) {
             // ------------------------------------------------------------ TMA producer
             uint32_t it = 0;
             bool ok = true;
-            for (int id = blockIdx.x; ok && id < total_tiles; id += gridDim.x) {
-                const TileCoord tc = decode_tile(ws, id, kTilesN);
-                for (int kb = 0; kb < kKBlocks; ++kb, ++it) {
+            for (int u = blockIdx.x; ok && u < plan.units; u += gridDim.x) {
+                const TileCoord tc = decode_tile(ws, u / plan.split, kTilesN);
+                int kb0, kb1;
+                unit_range<kKBlocks>(u % plan.split, plan.split, kb0, kb1);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
                     if (!mbar_wait(smem_u32(&sh->empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
@@ -206,8 +252,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
             const uint32_t idesc = make_idesc_e4m3(kTileM, kTileN);
             uint32_t it = 0;
             bool ok = true;
-            for (int id = blockIdx.x; ok && id < total_tiles; id += gridDim.x) {
-                for (int kb = 0; kb < kKBlocks; ++kb, ++it) {
+            for (int u = blockIdx.x; ok && u < plan.units; u += gridDim.x) {
+                int kb0, kb1;
+                unit_range<kKBlocks>(u % plan.split, plan.split, kb0, kb1);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t as = it & 1u;
                     const uint32_t aph = (it >> 1) & 1u;
                     if (!mbar_wait(smem_u32(&sh->acc_empty[as]), aph ^ 1u, abort_flag)) { ok = false; break; }
@@ -231,7 +279,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
         }
     } else {
         // ---------------------------------------------------------------- promotion + epilogue
-        setmaxnreg_inc<224>();
+        if (MODE == 1) setmaxnreg_inc<224>(); else setmaxnreg_inc<232>();
         const int ew = warp - 4;
         const int h = ew >> 2;       // which 128 of the tile's 256 accumulator columns
         const int q = warp & 3;      // TMEM lane quarter this warp may read
@@ -248,8 +296,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
         uint32_t it = 0;
         uint32_t tile_iter = 0;
         bool ok = true;
-        for (int id = blockIdx.x; ok && id < total_tiles; id += gridDim.x, ++tile_iter) {
-            const TileCoord tc = decode_tile(ws, id, kTilesN);
+        uint32_t splitk_uses = 0;
+        for (int u = blockIdx.x; ok && u < plan.units; u += gridDim.x) {
+            const int tile_id = u / plan.split;
+            const TileCoord tc = decode_tile(ws, tile_id, kTilesN);
+            int kb0, kb1;
+            unit_range<kKBlocks>(u % plan.split, plan.split, kb0, kb1);
             const int grow = tc.row0 + row;
             const float* sfa = ((MODE == 1) ? ws.sfa1 : ws.sfa2) + grow;
             const float* sw_lo;
@@ -264,14 +316,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
             float acc[128];
 #pragma unroll
             for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
+            const bool warp_has_rows = q * 32 < tc.rows;
 
-            float sa_n = ld_scale_early(sfa);
-            float lo_n = ld_scale_early(sw_lo);
-            float hi_n = ld_scale_early(sw_hi);
-            for (int kb = 0; kb < kKBlocks; ++kb, ++it) {
+            float sa_n = ld_scale_early(sfa + (size_t)kb0 * ws.m_cap);
+            float lo_n = ld_scale_early(sw_lo + kb0);
+            float hi_n = ld_scale_early(sw_hi + kb0);
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const float s_lo = sa_n * lo_n;
                 const float s_hi = sa_n * hi_n;
-                if (kb + 1 < kKBlocks) {
+                if (kb + 1 < kb1) {
                     sa_n = ld_scale_early(sfa + (size_t)(kb + 1) * ws.m_cap);
                     lo_n = ld_scale_early(sw_lo + kb + 1);
                     hi_n = ld_scale_early(sw_hi + kb + 1);
@@ -282,25 +335,100 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
+                if (!warp_has_rows) {
+                    // none of this warp's 32 rows is a routed row (short expert tail): nothing to
+                    // promote, release the accumulator stage at once
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[as]));
+                    continue;
+                }
                 const uint32_t t = lane_addr + as * kTileN;
                 uint32_t r0[32], r1[32];
                 tmem_ld_32x32(t + c0, r0);
                 tmem_ld_32x32(t + c1, r1);
                 tmem_ld_wait2(r0, r1);
-                promote32<0>(acc, r0, s_lo);
+                promote32<0, MODE == 1>(acc, r0, s_lo);
                 tmem_ld_32x32(t + c2, r0);
-                promote32<32>(acc, r1, s_lo);
+                promote32<32, MODE == 1>(acc, r1, s_lo);
                 tmem_ld_32x32(t + c3, r1);
                 tmem_ld_wait2(r0, r1);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[as]));
-                promote32<64>(acc, r0, s_hi);
-                promote32<96>(acc, r1, s_hi);
+                promote32<64, MODE == 1>(acc, r0, s_hi);
+                promote32<96, MODE == 1>(acc, r1, s_hi);
             }
             if (!ok) break;
 
             const bool valid = row < tc.rows;
+            if (SPLITK && plan.split > 1) {
+                // Park this unit's partial tile (valid rows only), count arrivals per tile; the
+                // last unit of the tile adds the partials in split order and runs the epilogue.
+                float4* mine = reinterpret_cast<float4*>(ws.splitk_partial + ((size_t)u * 2 + h) * (kTileM * 128) +
+                                                         (size_t)row * 128);
+                if (valid) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        __stcg(mine + j, make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]));
+                }
+                __threadfence();
+                const uint32_t bar = smem_u32(&sh->splitk_bar);
+                mbar_arrive(bar);
+                ok = mbar_wait(bar, splitk_uses & 1u, abort_flag);
+                ++splitk_uses;
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if (threadIdx.x == 4 * 32) {
+                    const int ticket = atomicAdd(&ws.ctrl->splitk_ticket[tile_id], 1);
+                    const int last = (ticket == plan.split - 1) ? 1 : 0;
+                    if (last) ws.ctrl->splitk_ticket[tile_id] = 0;
+                    sh->splitk_last = last;
+                }
+                mbar_arrive(bar);
+                ok = mbar_wait(bar, splitk_uses & 1u, abort_flag);
+                ++splitk_uses;
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if (!sh->splitk_last) continue;
+                __threadfence();
+#pragma unroll
+                for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
+                if (valid) {
+                    // fixed summation order (split 0, 1, ...); the next split's first half is
+                    // requested before the current one is added, to overlap the L2 latency
+                    const float4* src0 = reinterpret_cast<const float4*>(
+                        ws.splitk_partial + ((size_t)(tile_id * plan.split) * 2 + h) * (kTileM * 128) + (size_t)row * 128);
+                    constexpr size_t kSplitStride = (size_t)2 * kTileM * 128 / 4;  // float4 per split
+                    float4 nxt[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) nxt[j] = __ldcg(src0 + j);
+                    for (int sp = 0; sp < plan.split; ++sp) {
+                        const float4* src = src0 + (size_t)sp * kSplitStride;
+                        float4 hi[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) hi[j] = __ldcg(src + 16 + j);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            acc[4 * j] += nxt[j].x;
+                            acc[4 * j + 1] += nxt[j].y;
+                            acc[4 * j + 2] += nxt[j].z;
+                            acc[4 * j + 3] += nxt[j].w;
+                        }
+                        if (sp + 1 < plan.split) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) nxt[j] = __ldcg(src + kSplitStride + j);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            acc[64 + 4 * j] += hi[j].x;
+                            acc[64 + 4 * j + 1] += hi[j].y;
+                            acc[64 + 4 * j + 2] += hi[j].z;
+                            acc[64 + 4 * j + 3] += hi[j].w;
+                        }
+                    }
+                }
+            }
             if (MODE == 1) {
                 // D is rounded to bf16 (the reference materialises it in bf16), then
                 // v = silu(x2) * x1 in fp32, absmax over the row's 128-column block.
@@ -319,6 +447,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                 sh->amax[tp][h][row] = amax;
                 mbar_arrive(smem_u32(&sh->amax_bar[tp]));
                 ok = mbar_wait(smem_u32(&sh->amax_bar[tp]), (tile_iter >> 1) & 1u, abort_flag);
+                ++tile_iter;
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 const float maxv = fmaxf(amax, sh->amax[tp][h ^ 1][row]);
@@ -421,17 +550,24 @@ size_t tensor_map_bytes() { return sizeof(CUtensorMap); }
 
 cudaError_t configure_gemm_kernels()
 {
-    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)kGemmSmemBytes);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(grouped_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)kGemmSmemBytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(grouped_gemm_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kGemmSmemBytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(grouped_gemm_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kGemmSmemBytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(grouped_gemm_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kGemmSmemBytes);
+    return e;
 }
 
 int gemm_tiles_n(int mode) { return mode == 1 ? kInter / kBlock : kHidden / kTileN; }
 
 cudaError_t launch_grouped_gemm(int mode, const void* tmap_a, const void* tmap_b, const Workspace& ws,
-                                const float* w_scale, int silu_exact, int num_ctas, cudaStream_t stream)
+                                const float* w_scale, int silu_exact, int num_ctas, int split_k, cudaStream_t stream)
 {
     const CUtensorMap* ma = static_cast<const CUtensorMap*>(tmap_a);
     const CUtensorMap* mb = static_cast<const CUtensorMap*>(tmap_b);
@@ -445,8 +581,12 @@ cudaError_t launch_grouped_gemm(int mode, const void* tmap_a, const void* tmap_b
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (mode == 1) return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<1>, *ma, *mb, ws, w_scale, silu_exact);
-    return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<2>, *ma, *mb, ws, w_scale, silu_exact);
+    if (mode == 1) {
+        if (split_k) return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<1, true>, *ma, *mb, ws, w_scale, silu_exact);
+        return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<1, false>, *ma, *mb, ws, w_scale, silu_exact);
+    }
+    if (split_k) return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<2, true>, *ma, *mb, ws, w_scale, silu_exact);
+    return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<2, false>, *ma, *mb, ws, w_scale, silu_exact);
 }
 
 }  // namespace moe

@@ -22,6 +22,10 @@ constexpr int kNumGroups = 8;
 constexpr int kTopKGroup = 4;
 constexpr int kTileM = 128;          // rows of one expert tile (expert row ranges are padded to it)
 constexpr int kMaxLocalExperts = 256;
+// Split-K (small batches only): a tile's K range is divided over several CTAs when there are
+// fewer tiles than SMs; their fp32 partial tiles meet in a scratch of kSplitKSlots slots of
+// 128 x 256 floats (one slot per work unit, units <= number of CTAs <= kSplitKSlots).
+constexpr int kSplitKSlots = 192;
 
 // What the dispatch step does with a token's experts that fall into one 32-expert
 // shard.  The fields restate, as data, the branch structure of the reference's
@@ -49,6 +53,7 @@ struct Control {
     int blocks_done;                     // routing CTAs finished (ticket for the last-CTA scan)
     int pad;
     int expert_rows[kMaxLocalExperts];   // copy of the counters of the last call (diagnostics)
+    int splitk_ticket[kSplitKSlots];     // per-tile arrival counters of the split-K reduction (self-clearing)
 };
 
 enum KernelStatus : int {
@@ -62,8 +67,8 @@ enum KernelStatus : int {
 struct Workspace {
     Control* ctrl;
     int* expert_offset;     // [E+1] first packed row of each expert (multiples of 128)
-    int* tile_expert;       // [max_tiles] local expert of each 128-row tile
-    int* tile_rows;         // [max_tiles] valid rows in the tile (1..128)
+    int4* tile_info;        // [max_tiles] per 128-row tile: {local expert, first tile of that expert,
+                            //             tiles of that expert, routed rows of that expert}
     int* num_tiles;         // [1]
     int* topk_idx;          // [T,8] global expert ids in selection order
     float* topk_weight;     // [T,8] normalised weights (before routed_scaling_factor)
@@ -76,6 +81,7 @@ struct Workspace {
     uint8_t* a2;            // [M_cap, I]   e4m3 SwiGLU output
     float* sfa2;            // [16, M_cap]
     __nv_bfloat16* y;       // [M_cap, H]   GEMM2 rows before the weighted combine
+    float* splitk_partial;  // [kSplitKSlots, 128 * 256] fp32 partial tiles of split-K work units
     int m_cap;              // packed-row capacity (multiple of 128)
     int max_tiles;
 };

@@ -20,7 +20,7 @@ cudaError_t launch_combine(const Workspace&, void*, int, cudaStream_t);
 int encode_kmajor_u8_map(void*, const void*, uint64_t, uint64_t, uint64_t, uint32_t);
 size_t tensor_map_bytes();
 cudaError_t configure_gemm_kernels();
-cudaError_t launch_grouped_gemm(int, const void*, const void*, const Workspace&, const float*, int, int,
+cudaError_t launch_grouped_gemm(int, const void*, const void*, const Workspace&, const float*, int, int, int,
                                 cudaStream_t);
 int gemm_tiles_n(int mode);
 }  // namespace moe
@@ -54,8 +54,8 @@ struct Carve {
 };
 
 struct Layout {
-    size_t ctrl, expert_offset, tile_expert, tile_rows, num_tiles, topk_idx, topk_weight, pair_count, pair_code,
-        pair_weight, row_token, a1, sfa1, a2, sfa2, y, total;
+    size_t ctrl, expert_offset, tile_info, num_tiles, topk_idx, topk_weight, pair_count, pair_code,
+        pair_weight, row_token, a1, sfa1, a2, sfa2, y, splitk, total;
     int m_cap, max_tiles;
 };
 
@@ -67,8 +67,7 @@ Layout make_layout(int T, int E)
     Carve c;
     L.ctrl = c.take(sizeof(Control));
     L.expert_offset = c.take(sizeof(int) * (kMaxLocalExperts + 1));
-    L.tile_expert = c.take(sizeof(int) * L.max_tiles);
-    L.tile_rows = c.take(sizeof(int) * L.max_tiles);
+    L.tile_info = c.take(sizeof(int4) * L.max_tiles);
     L.num_tiles = c.take(sizeof(int) * 4);
     L.topk_idx = c.take(sizeof(int) * (size_t)T * kTopK);
     L.topk_weight = c.take(sizeof(float) * (size_t)T * kTopK);
@@ -81,6 +80,7 @@ Layout make_layout(int T, int E)
     L.a2 = c.take((size_t)L.m_cap * kInter);
     L.sfa2 = c.take(sizeof(float) * (size_t)kInterBlocks * L.m_cap);
     L.y = c.take(sizeof(__nv_bfloat16) * (size_t)L.m_cap * kHidden);
+    L.splitk = c.take(sizeof(float) * (size_t)kSplitKSlots * kTileM * 256);
     L.total = c.off;
     return L;
 }
@@ -202,23 +202,19 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
                                   (float)a.routed_scaling_factor, pol, /*do_scan=*/1, stream);
     mark(1);
     mark(2);
-    // most 128-row tiles this batch can produce: one per (token, expert) pair, and no more
-    // than the rows / 128 plus one partial tile per local expert
-    const long long pairs = 8LL * T;
-    long long m_tiles = pairs / kTileM + E;
-    if (m_tiles > pairs) m_tiles = pairs;
-    auto ctas = [&](int mode) {
-        const long long t = m_tiles * gemm_tiles_n(mode);
-        return (int)(t < h->num_sms ? t : h->num_sms);
-    };
+    // decode-sized batches may leave most SMs without a tile: there the split-K instantiation
+    // (chosen here from T alone, it decides on the device whether to split) spreads the K range
+    const int split_k = T <= 4 ? 1 : 0;
+    // one persistent CTA per SM; CTAs without work leave at once, spare ones take split-K units
+    auto ctas = [&](int) { return h->num_sms < kSplitKSlots ? h->num_sms : kSplitKSlots; };
     if (e == cudaSuccess) e = launch_permute(a.hidden_states, a.hidden_states_scale, h->ws, T, stream);
     mark(3);
     if (e == cudaSuccess)
         e = launch_grouped_gemm(1, h->tmap_a1, h->tmap_w1, h->ws, a.gemm1_weights_scale, h->opt_exact_silu,
-                                ctas(1), stream);
+                                ctas(1), split_k, stream);
     mark(4);
     if (e == cudaSuccess)
-        e = launch_grouped_gemm(2, h->tmap_a2, h->tmap_w2, h->ws, a.gemm2_weights_scale, 0, ctas(2), stream);
+        e = launch_grouped_gemm(2, h->tmap_a2, h->tmap_w2, h->ws, a.gemm2_weights_scale, 0, ctas(2), split_k, stream);
     mark(5);
     if (e == cudaSuccess) e = launch_combine(h->ws, a.output, T, stream);
     mark(6);
@@ -313,8 +309,7 @@ int moe_fp8_b200_create(moe_fp8_b200_handle* out, int device, int max_tokens, in
     Workspace& w = h->ws;
     w.ctrl = reinterpret_cast<Control*>(h->base + L.ctrl);
     w.expert_offset = reinterpret_cast<int*>(h->base + L.expert_offset);
-    w.tile_expert = reinterpret_cast<int*>(h->base + L.tile_expert);
-    w.tile_rows = reinterpret_cast<int*>(h->base + L.tile_rows);
+    w.tile_info = reinterpret_cast<int4*>(h->base + L.tile_info);
     w.num_tiles = reinterpret_cast<int*>(h->base + L.num_tiles);
     w.topk_idx = reinterpret_cast<int*>(h->base + L.topk_idx);
     w.topk_weight = reinterpret_cast<float*>(h->base + L.topk_weight);
@@ -327,6 +322,7 @@ int moe_fp8_b200_create(moe_fp8_b200_handle* out, int device, int max_tokens, in
     w.a2 = h->base + L.a2;
     w.sfa2 = reinterpret_cast<float*>(h->base + L.sfa2);
     w.y = reinterpret_cast<__nv_bfloat16*>(h->base + L.y);
+    w.splitk_partial = reinterpret_cast<float*>(h->base + L.splitk);
     w.m_cap = L.m_cap;
     w.max_tiles = L.max_tiles;
     // Small control arrays start defined; the large row buffers are written before use.

@@ -167,11 +167,8 @@ __device__ __forceinline__ void scan_tiles_block(const Workspace& ws, int num_lo
         }
     }
     if (!overflow && e < num_local_experts) {
-        for (int j = 0; j < k; ++j) {
-            ws.tile_expert[base + j] = e;
-            const int left = m - j * kTileM;
-            ws.tile_rows[base + j] = left < kTileM ? left : kTileM;
-        }
+        const int4 info = make_int4(e, base, k, m);
+        for (int j = 0; j < k; ++j) ws.tile_info[base + j] = info;
     }
 }
 
