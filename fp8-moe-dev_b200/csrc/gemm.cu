@@ -42,6 +42,11 @@ constexpr int kTmemCols = 512;
 constexpr int kEpilogueWarps = 8;
 constexpr int kEpilogueThreads = kEpilogueWarps * 32;
 
+constexpr int kSplitKMaxRows = 4;    // split-K is used for batches of at most this many tokens
+constexpr int kSplitKMaxSplit = 14;  // 56 K blocks / 4
+
+static_assert(kHiddenBlocks / 4 <= kSplitKMaxSplit, "split-K register array too small");
+
 struct GemmShared {
     uint64_t full[kStages];
     uint64_t empty[kStages];
@@ -52,6 +57,7 @@ struct GemmShared {
     uint32_t tmem_base;
     int abort;
     int splitk_last;
+    alignas(16) float splitk_sum[kSplitKMaxRows][256];   // read and written as float4
     float amax[2][2][kTileM];
 };
 
@@ -88,10 +94,15 @@ template <int KBLOCKS, bool SPLITK>
 __device__ __forceinline__ UnitPlan plan_units(int total_tiles, int num_ctas) {
     UnitPlan p;
     p.split = 1;
-    if (SPLITK && total_tiles > 0 && total_tiles * 2 <= num_ctas) {
-        int s = num_ctas / total_tiles;
-        const int max_split = KBLOCKS / 4;  // at least four K blocks per unit
-        p.split = s < max_split ? s : max_split;
+    if (SPLITK && total_tiles > 0 && total_tiles < num_ctas) {
+        // rounds x (K blocks per unit + reduction overhead, about six K blocks' worth), units capped
+        // by the scratch slots; ties keep the smaller split
+        int best = KBLOCKS;
+        for (int s = 2; s <= KBLOCKS / 4 && total_tiles * s <= kSplitKSlots; ++s) {
+            const int rounds = (total_tiles * s + num_ctas - 1) / num_ctas;
+            const int cost = rounds * ((KBLOCKS + s - 1) / s + 6);
+            if (cost < best) { best = cost; p.split = s; }
+        }
     }
     p.units = total_tiles * p.split;
     return p;
@@ -101,6 +112,29 @@ template <int KBLOCKS>
 __device__ __forceinline__ void unit_range(int s, int split, int& kb0, int& kb1) {
     kb0 = (KBLOCKS * s) / split;
     kb1 = (KBLOCKS * (s + 1)) / split;
+}
+
+// Split-K: sums the partial rows of one tile over its `split` units into shared memory.  Called by
+// the 256 promotion threads of the last unit to finish; thread `et` owns one float4 of the
+// (kSplitKMaxRows x 256) block, all splits' loads are in flight together and are added in split
+// order.  Kept out of line so that its registers do not weigh on the K loop.
+__device__ __noinline__ void splitk_sum_partials(const float* partial, float* sum_smem, int tile_id, int split,
+                                                 int rows, int et)
+{
+    const int r = et >> 6, c4 = et & 63;
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < rows) {
+        const float4* src =
+            reinterpret_cast<const float4*>(partial + ((size_t)(tile_id * split) * kSplitKMaxRows + r) * 256) + c4;
+        float4 v[kSplitKMaxSplit];
+#pragma unroll
+        for (int sp = 0; sp < kSplitKMaxSplit; ++sp)
+            if (sp < split) v[sp] = __ldcg(src + (size_t)sp * (kSplitKMaxRows * 256 / 4));
+#pragma unroll
+        for (int sp = 0; sp < kSplitKMaxSplit; ++sp)
+            if (sp < split) { sum.x += v[sp].x; sum.y += v[sp].y; sum.z += v[sp].z; sum.w += v[sp].w; }
+    }
+    reinterpret_cast<float4*>(sum_smem)[et] = sum;
 }
 
 // tcgen05.wait::ld with the destination registers as in/out operands, so that the
@@ -363,16 +397,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
 
             const bool valid = row < tc.rows;
             if (SPLITK && plan.split > 1) {
-                // Park this unit's partial tile (valid rows only), count arrivals per tile; the
-                // last unit of the tile adds the partials in split order and runs the epilogue.
-                float4* mine = reinterpret_cast<float4*>(ws.splitk_partial + ((size_t)u * 2 + h) * (kTileM * 128) +
-                                                         (size_t)row * 128);
+                // Split-K reduction (batches of at most kSplitKMaxRows tokens, so a tile has at most
+                // that many routed rows).  Every unit parks its partial rows in global scratch and
+                // takes a ticket; the last unit of the tile sums all partials -- one float4 per
+                // thread, all splits' loads in flight together, fixed split order -- into shared
+                // memory, from where the owning threads pick up their accumulators again.
+                float4* mine = reinterpret_cast<float4*>(ws.splitk_partial + ((size_t)u * kSplitKMaxRows + row) * 256 +
+                                                         (size_t)h * 128);
                 if (valid) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
                         __stcg(mine + j, make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]));
+                    __threadfence();
                 }
-                __threadfence();
                 const uint32_t bar = smem_u32(&sh->splitk_bar);
                 mbar_arrive(bar);
                 ok = mbar_wait(bar, splitk_uses & 1u, abort_flag);
@@ -392,40 +429,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                 if (!ok) break;
                 if (!sh->splitk_last) continue;
                 __threadfence();
-#pragma unroll
-                for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
+                splitk_sum_partials(ws.splitk_partial, &sh->splitk_sum[0][0], tile_id, plan.split, tc.rows,
+                                    (int)threadIdx.x - 4 * 32);
+                mbar_arrive(bar);
+                ok = mbar_wait(bar, splitk_uses & 1u, abort_flag);
+                ++splitk_uses;
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
                 if (valid) {
-                    // fixed summation order (split 0, 1, ...); the next split's first half is
-                    // requested before the current one is added, to overlap the L2 latency
-                    const float4* src0 = reinterpret_cast<const float4*>(
-                        ws.splitk_partial + ((size_t)(tile_id * plan.split) * 2 + h) * (kTileM * 128) + (size_t)row * 128);
-                    constexpr size_t kSplitStride = (size_t)2 * kTileM * 128 / 4;  // float4 per split
-                    float4 nxt[16];
+                    const float4* src = reinterpret_cast<const float4*>(&sh->splitk_sum[row][h * 128]);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) nxt[j] = __ldcg(src0 + j);
-                    for (int sp = 0; sp < plan.split; ++sp) {
-                        const float4* src = src0 + (size_t)sp * kSplitStride;
-                        float4 hi[16];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) hi[j] = __ldcg(src + 16 + j);
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            acc[4 * j] += nxt[j].x;
-                            acc[4 * j + 1] += nxt[j].y;
-                            acc[4 * j + 2] += nxt[j].z;
-                            acc[4 * j + 3] += nxt[j].w;
-                        }
-                        if (sp + 1 < plan.split) {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) nxt[j] = __ldcg(src + kSplitStride + j);
-                        }
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            acc[64 + 4 * j] += hi[j].x;
-                            acc[64 + 4 * j + 1] += hi[j].y;
-                            acc[64 + 4 * j + 2] += hi[j].z;
-                            acc[64 + 4 * j + 3] += hi[j].w;
-                        }
+                    for (int j = 0; j < 32; ++j) {
+                        const float4 v = src[j];
+                        acc[4 * j] = v.x; acc[4 * j + 1] = v.y; acc[4 * j + 2] = v.z; acc[4 * j + 3] = v.w;
                     }
                 }
             }

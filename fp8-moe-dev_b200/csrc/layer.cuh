@@ -22,10 +22,10 @@ constexpr int kNumGroups = 8;
 constexpr int kTopKGroup = 4;
 constexpr int kTileM = 128;          // rows of one expert tile (expert row ranges are padded to it)
 constexpr int kMaxLocalExperts = 256;
-// Split-K (small batches only): a tile's K range is divided over several CTAs when there are
-// fewer tiles than SMs; their fp32 partial tiles meet in a scratch of kSplitKSlots slots of
-// 128 x 256 floats (one slot per work unit, units <= number of CTAs <= kSplitKSlots).
-constexpr int kSplitKSlots = 192;
+// Split-K (batches of at most four tokens): a tile's K range is divided over several CTAs when
+// there are fewer tiles than SMs; their fp32 partial rows meet in a scratch of kSplitKSlots slots
+// (one per work unit).
+constexpr int kSplitKSlots = 320;
 
 // What the dispatch step does with a token's experts that fall into one 32-expert
 // shard.  The fields restate, as data, the branch structure of the reference's
@@ -81,7 +81,7 @@ struct Workspace {
     uint8_t* a2;            // [M_cap, I]   e4m3 SwiGLU output
     float* sfa2;            // [16, M_cap]
     __nv_bfloat16* y;       // [M_cap, H]   GEMM2 rows before the weighted combine
-    float* splitk_partial;  // [kSplitKSlots, 128 * 256] fp32 partial tiles of split-K work units
+    float* splitk_partial;  // [kSplitKSlots, 4, 256] fp32 partial rows of split-K work units
     int m_cap;              // packed-row capacity (multiple of 128)
     int max_tiles;
 };

@@ -80,7 +80,7 @@ Layout make_layout(int T, int E)
     L.a2 = c.take((size_t)L.m_cap * kInter);
     L.sfa2 = c.take(sizeof(float) * (size_t)kInterBlocks * L.m_cap);
     L.y = c.take(sizeof(__nv_bfloat16) * (size_t)L.m_cap * kHidden);
-    L.splitk = c.take(sizeof(float) * (size_t)kSplitKSlots * kTileM * 256);
+    L.splitk = c.take(sizeof(float) * (size_t)kSplitKSlots * 4 * 256);  // kSplitKMaxRows rows of 256 floats per unit
     L.total = c.off;
     return L;
 }
@@ -95,6 +95,7 @@ struct moe_fp8_b200_ctx {
     int opt_reference_pruning = 1;
     int opt_exact_silu = 0;
     bool counters_dirty = false;
+    int opt_stop_after = 0;   // diagnostics: enqueue only the first N stages (0 = all)
     uint8_t* base = nullptr;
     Layout layout{};
     Workspace ws{};
@@ -202,21 +203,22 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
                                   (float)a.routed_scaling_factor, pol, /*do_scan=*/1, stream);
     mark(1);
     mark(2);
+    const int stop = h->opt_stop_after > 0 ? h->opt_stop_after : 99;
     // decode-sized batches may leave most SMs without a tile: there the split-K instantiation
     // (chosen here from T alone, it decides on the device whether to split) spreads the K range
-    const int split_k = T <= 4 ? 1 : 0;
+    const int split_k = T <= 4 ? 1 : 0;   // 4 = kSplitKMaxRows of the GEMM kernel
     // one persistent CTA per SM; CTAs without work leave at once, spare ones take split-K units
-    auto ctas = [&](int) { return h->num_sms < kSplitKSlots ? h->num_sms : kSplitKSlots; };
-    if (e == cudaSuccess) e = launch_permute(a.hidden_states, a.hidden_states_scale, h->ws, T, stream);
+    auto ctas = [&](int) { return h->num_sms; };
+    if (e == cudaSuccess && stop >= 2) e = launch_permute(a.hidden_states, a.hidden_states_scale, h->ws, T, stream);
     mark(3);
-    if (e == cudaSuccess)
+    if (e == cudaSuccess && stop >= 3)
         e = launch_grouped_gemm(1, h->tmap_a1, h->tmap_w1, h->ws, a.gemm1_weights_scale, h->opt_exact_silu,
                                 ctas(1), split_k, stream);
     mark(4);
-    if (e == cudaSuccess)
+    if (e == cudaSuccess && stop >= 4)
         e = launch_grouped_gemm(2, h->tmap_a2, h->tmap_w2, h->ws, a.gemm2_weights_scale, 0, ctas(2), split_k, stream);
     mark(5);
-    if (e == cudaSuccess) e = launch_combine(h->ws, a.output, T, stream);
+    if (e == cudaSuccess && stop >= 5) e = launch_combine(h->ws, a.output, T, stream);
     mark(6);
     if (e != cudaSuccess) {
         h->counters_dirty = true;
@@ -369,6 +371,7 @@ int moe_fp8_b200_set_option(moe_fp8_b200_handle h, int option, int value)
     switch (option) {
         case MOE_FP8_B200_OPT_REFERENCE_PRUNING: h->opt_reference_pruning = value ? 1 : 0; return MOE_FP8_B200_OK;
         case MOE_FP8_B200_OPT_EXACT_SILU: h->opt_exact_silu = value ? 1 : 0; return MOE_FP8_B200_OK;
+        case MOE_FP8_B200_OPT_STOP_AFTER_STAGE: h->opt_stop_after = value; return MOE_FP8_B200_OK;
         case MOE_FP8_B200_OPT_STAGE_TIMING:
             h->opt_stage_timing = value ? 1 : 0;
             h->timed_runs = 0;

@@ -32,11 +32,21 @@ __device__ __forceinline__ float ordered_to_float(uint32_t k) {
 
 constexpr float kNegSentinel = -1e30f;
 
+// Appends one kept (local expert, weight) pair to the token's list (static indexing keeps
+// the lists in registers).
+__device__ __forceinline__ void emit_pair(int (&p_le)[kTopK], float (&p_w)[kTopK], int& n, int le, float w) {
+#pragma unroll
+    for (int i = 0; i < kTopK; ++i) {
+        if (i == n) { p_le[i] = le; p_w[i] = w; }
+    }
+    ++n;
+}
+
 // Applies the dispatch policy to the experts of token `t` that fall into shard `s`
 // (local experts [32 s, 32 s + 32)) and appends the kept pairs.  Run by one lane.
 __device__ __forceinline__ void dispatch_one_shard(
     const int (&idx)[kTopK], const float (&wn)[kTopK], int s, int local_expert_offset,
-    const DispatchPolicy& pol, float rsf, int t, int& n_pairs, const Workspace& ws)
+    const DispatchPolicy& pol, float rsf, int& n_pairs, int (&p_le)[kTopK], float (&p_w)[kTopK])
 {
     const int lo = s * kShardExperts;
     if (!pol.prune) {
@@ -46,11 +56,7 @@ __device__ __forceinline__ void dispatch_one_shard(
             if ((unsigned)(le - lo) < (unsigned)kShardExperts) {
                 const float wk = wn[k];
                 if (pol.skip_zero_weight && wk == 0.0f) continue;
-                const int slot = atomicAdd(&ws.ctrl->expert_count[le], 1);
-                const float w_scaled = wk * rsf;
-                ws.pair_code[(size_t)t * kTopK + n_pairs] = ((uint32_t)le << 24) | (uint32_t)slot;
-                ws.pair_weight[(size_t)t * kTopK + n_pairs] = w_scaled;
-                ++n_pairs;
+                emit_pair(p_le, p_w, n_pairs, le, wk * rsf);
             }
         }
         return;
@@ -110,11 +116,7 @@ __device__ __forceinline__ void dispatch_one_shard(
     for (int i = 0; i < kKeep; ++i) {
         const int le = keep_le[i];
         if (i < max_keep && le >= 0) {
-            const int slot = atomicAdd(&ws.ctrl->expert_count[le], 1);
-            const float w_scaled = keep_w[i] * renorm * rsf;
-            ws.pair_code[(size_t)t * kTopK + n_pairs] = ((uint32_t)le << 24) | (uint32_t)slot;
-            ws.pair_weight[(size_t)t * kTopK + n_pairs] = w_scaled;
-            ++n_pairs;
+            emit_pair(p_le, p_w, n_pairs, le, keep_w[i] * renorm * rsf);
         }
     }
 }
@@ -126,13 +128,15 @@ __device__ __forceinline__ void dispatch_one_shard(
 // are then cleared for the next call.  (The reference does the scan in a separate one-warp
 // kernel and then reads the totals back on the host, kernel/moe_fp8.cu:838-870, 2816-2824.)
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ void scan_tiles_block(const Workspace& ws, int num_local_experts)
+__device__ __forceinline__ void scan_tiles_block(const Workspace& ws, int num_local_experts, const int* local_counts)
 {
     __shared__ int s_warp_total[kMaxLocalExperts / 32];
     const int e = threadIdx.x;
     const int lane = e & 31, warp = e >> 5;
-    // the counters were written by other CTAs' atomics: read them past the L1
-    const int m = (e < num_local_experts) ? __ldcg(&ws.ctrl->expert_count[e]) : 0;
+    // single-CTA launches count in shared memory (local_counts); otherwise the counters were
+    // written by other CTAs' atomics and are read past the L1
+    int m = 0;
+    if (e < num_local_experts) m = local_counts ? local_counts[e] : __ldcg(&ws.ctrl->expert_count[e]);
     const int k = (m + kTileM - 1) / kTileM;
     int incl = k;
 #pragma unroll
@@ -155,7 +159,7 @@ __device__ __forceinline__ void scan_tiles_block(const Workspace& ws, int num_lo
     if (e < num_local_experts) {
         ws.expert_offset[e] = overflow ? 0 : base * kTileM;
         ws.ctrl->expert_rows[e] = m;
-        ws.ctrl->expert_count[e] = 0;
+        if (!local_counts) ws.ctrl->expert_count[e] = 0;
     }
     if (e == 0) {
         ws.expert_offset[num_local_experts] = total * kTileM;
@@ -178,11 +182,23 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_dispatch_kernel(
     const float* __restrict__ logits, const __nv_bfloat16* __restrict__ bias, Workspace ws, int T,
     int local_expert_offset, int num_local_experts, float rsf, DispatchPolicy pol, int do_scan)
 {
+    // Rows are counted per CTA in shared memory first; one global atomic per (CTA, expert)
+    // then reserves a contiguous slot range (a single-CTA launch needs no global atomic).
+    __shared__ int s_cnt[kMaxLocalExperts];
+    __shared__ int s_base[kMaxLocalExperts];
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * kRouteWarps + (threadIdx.x >> 5);
     constexpr uint32_t kFull = 0xffffffffu;
+    const bool single_cta = do_scan && gridDim.x == 1;
+    s_cnt[threadIdx.x] = 0;
     pdl_launch_dependents();
     pdl_wait();  // the previous call's kernels still read the pair tables and offsets
+    __syncthreads();
+    int n_pairs = 0;
+    int p_le[kTopK], p_rank[kTopK];
+    float p_w[kTopK];
+#pragma unroll
+    for (int i = 0; i < kTopK; ++i) { p_le[i] = 0; p_rank[i] = 0; p_w[i] = 0.0f; }
     if (do_scan && blockIdx.x == 0 && threadIdx.x == 0) {
         ws.ctrl->status = kStatusOk;
         ws.ctrl->status_detail = 0;
@@ -283,19 +299,47 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_dispatch_kernel(
     }
 
     if (lane == 0) {
-        int n_pairs = 0;
         const int shards = num_local_experts / kShardExperts;
         for (int sh = 0; sh < shards; ++sh) {
-            dispatch_one_shard(idx, wn, sh, local_expert_offset, pol, rsf, t, n_pairs, ws);
+            dispatch_one_shard(idx, wn, sh, local_expert_offset, pol, rsf, n_pairs, p_le, p_w);
         }
-        ws.pair_count[t] = n_pairs;
+#pragma unroll
+        for (int i = 0; i < kTopK; ++i) {
+            if (i < n_pairs) p_rank[i] = atomicAdd(&s_cnt[p_le[i]], 1);
+        }
     }
     }  // t < T
 
+    __syncthreads();
+    {
+        const int e = threadIdx.x;
+        int base = 0;
+        if (!single_cta && e < num_local_experts) {
+            const int c = s_cnt[e];
+            if (c > 0) base = atomicAdd(&ws.ctrl->expert_count[e], c);
+        }
+        s_base[e] = base;
+    }
+    __syncthreads();
+    if (t < T && lane == 0) {
+#pragma unroll
+        for (int i = 0; i < kTopK; ++i) {
+            if (i < n_pairs) {
+                const uint32_t slot = (uint32_t)(s_base[p_le[i]] + p_rank[i]);
+                ws.pair_code[(size_t)t * kTopK + i] = ((uint32_t)p_le[i] << 24) | slot;
+                ws.pair_weight[(size_t)t * kTopK + i] = p_w[i];
+            }
+        }
+        ws.pair_count[t] = n_pairs;
+    }
+
     if (!do_scan) return;
+    if (single_cta) {
+        scan_tiles_block(ws, num_local_experts, s_cnt);
+        return;
+    }
     // Last CTA to get here turns the counters into offsets and tiles.
     __shared__ int s_is_last;
-    __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
         const int ticket = atomicAdd(&ws.ctrl->blocks_done, 1);
@@ -304,7 +348,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_dispatch_kernel(
     __syncthreads();
     if (s_is_last) {
         __threadfence();
-        scan_tiles_block(ws, num_local_experts);
+        scan_tiles_block(ws, num_local_experts, nullptr);
     }
 }
 

@@ -71,7 +71,11 @@ enum {
     MOE_FP8_B200_OPT_EXACT_SILU = 2,
     /* 1: record CUDA events around every stage of each run (not capturable into a graph
      * while on); read them with moe_fp8_b200_stage_times.  Setting it restarts the count. */
-    MOE_FP8_B200_OPT_STAGE_TIMING = 3
+    MOE_FP8_B200_OPT_STAGE_TIMING = 3,
+    /* Diagnostics: N > 0 enqueues only the first N stages of a run (1 routing+dispatch+scan,
+     * 2 +permute, 3 +GEMM1, 4 +GEMM2, 5 = all); the output is then not (fully) written.
+     * 0 (default) runs the whole layer. */
+    MOE_FP8_B200_OPT_STOP_AFTER_STAGE = 4
 };
 
 /* Intermediate buffers readable after a run (moe_fp8_b200_read_intermediate). */
