@@ -155,8 +155,10 @@ __device__ __forceinline__ void tmem_ld_wait2(uint32_t (&a)[32], uint32_t (&b)[3
 }
 
 // acc[OFF + j] += raw[j] * s for 32 accumulator columns.  PACKED uses the two-wide fp32 FMA of
-// sm_100 (same IEEE result per element, half the issue slots); it pays off in GEMM1, while in
-// GEMM2 the extra register pairing costs more than it saves (measured), so GEMM2 stays scalar.
+// sm_100: same IEEE result per element and the same FMA-pipe time, but half the issue slots.
+// That matters because the MMA-issuing thread shares its scheduler with two of these warps: long
+// bursts of scalar FMAs starve it (measured: 728 -> 592 cycles per K block in an isolated
+// two-stage pipeline when the promotion uses the packed form).
 template <int OFF, bool PACKED>
 __device__ __forceinline__ void promote32(float (&acc)[128], const uint32_t (&r)[32], float s) {
     if (PACKED) {
@@ -240,9 +242,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
     volatile int* abort_flag = &sh->abort;
 
     if (warp < 4) {
-        // register split between the producer warpgroup and the two promotion warpgroups:
-        // 56 / 224 for GEMM1, 40 / 232 for GEMM2 (both sum to <= 64 K registers per SM)
-        if (MODE == 1) setmaxnreg_dec<56>(); else setmaxnreg_dec<40>();
+        // register split: 56 per thread for the producer warpgroup, 224 for the two promotion
+        // warpgroups (128 * 56 + 256 * 224 <= 64 K registers per SM)
+        setmaxnreg_dec<56>();
         if (warp == 0 && lane == 0) {
             // ------------------------------------------------------------ TMA producer
             uint32_t it = 0;
@@ -286,16 +288,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
             const uint32_t idesc = make_idesc_e4m3(kTileM, kTileN);
             uint32_t it = 0;
             bool ok = true;
+            bool next_full_ready = false;
             for (int u = blockIdx.x; ok && u < plan.units; u += gridDim.x) {
                 int kb0, kb1;
                 unit_range<kKBlocks>(u % plan.split, plan.split, kb0, kb1);
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t as = it & 1u;
                     const uint32_t aph = (it >> 1) & 1u;
-                    if (!mbar_wait(smem_u32(&sh->acc_empty[as]), aph ^ 1u, abort_flag)) { ok = false; break; }
                     const uint32_t s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
-                    if (!mbar_wait(smem_u32(&sh->full[s]), ph, abort_flag)) { ok = false; break; }
+                    // The operand stage is normally long since loaded; its barrier was already
+                    // probed while the previous block's MMAs ran (next_full_ready), which keeps
+                    // that probe's latency off the release -> issue chain below.
+                    if (!next_full_ready && !mbar_wait(smem_u32(&sh->full[s]), ph, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&sh->acc_empty[as]), aph ^ 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_addr = base + s * kStageBytes;
                     const uint64_t adesc = make_kmajor_sw128_desc(a_addr);
@@ -308,12 +314,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                     }
                     tc_commit(smem_u32(&sh->empty[s]));
                     tc_commit(smem_u32(&sh->acc_full[as]));
+                    {
+                        const uint32_t nit = it + 1;
+                        next_full_ready = mbar_try_wait(smem_u32(&sh->full[nit % kStages]), (nit / kStages) & 1u);
+                    }
                 }
             }
         }
     } else {
         // ---------------------------------------------------------------- promotion + epilogue
-        if (MODE == 1) setmaxnreg_inc<224>(); else setmaxnreg_inc<232>();
+        setmaxnreg_inc<224>();
         const int ew = warp - 4;
         const int h = ew >> 2;       // which 128 of the tile's 256 accumulator columns
         const int q = warp & 3;      // TMEM lane quarter this warp may read
@@ -354,14 +364,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
 
             float sa_n = ld_scale_early(sfa + (size_t)kb0 * ws.m_cap);
             float lo_n = ld_scale_early(sw_lo + kb0);
-            float hi_n = ld_scale_early(sw_hi + kb0);
+            float hi_n = (MODE == 1) ? ld_scale_early(sw_hi + kb0) : 0.0f;
             for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const float s_lo = sa_n * lo_n;
-                const float s_hi = sa_n * hi_n;
+                const float s_hi = (MODE == 1) ? sa_n * hi_n : s_lo;   // GEMM2: one weight block per thread
                 if (kb + 1 < kb1) {
                     sa_n = ld_scale_early(sfa + (size_t)(kb + 1) * ws.m_cap);
                     lo_n = ld_scale_early(sw_lo + kb + 1);
-                    hi_n = ld_scale_early(sw_hi + kb + 1);
+                    if (MODE == 1) hi_n = ld_scale_early(sw_hi + kb + 1);
                 }
                 const uint32_t as = it & 1u;
                 const uint32_t aph = (it >> 1) & 1u;
@@ -382,16 +392,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                 tmem_ld_32x32(t + c0, r0);
                 tmem_ld_32x32(t + c1, r1);
                 tmem_ld_wait2(r0, r1);
-                promote32<0, MODE == 1>(acc, r0, s_lo);
+                promote32<0, true>(acc, r0, s_lo);
                 tmem_ld_32x32(t + c2, r0);
-                promote32<32, MODE == 1>(acc, r1, s_lo);
+                promote32<32, true>(acc, r1, s_lo);
                 tmem_ld_32x32(t + c3, r1);
                 tmem_ld_wait2(r0, r1);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[as]));
-                promote32<64, MODE == 1>(acc, r0, s_hi);
-                promote32<96, MODE == 1>(acc, r1, s_hi);
+                promote32<64, true>(acc, r0, s_hi);
+                promote32<96, true>(acc, r1, s_hi);
             }
             if (!ok) break;
 
