@@ -25,6 +25,7 @@ EXPORTS = [
     "moe_fp8_b200_create", "moe_fp8_b200_destroy", "moe_fp8_b200_last_error", "moe_fp8_b200_set_option",
     "moe_fp8_b200_run", "moe_fp8_b200_run_host", "moe_fp8_b200_check", "moe_fp8_b200_read_intermediate",
     "moe_fp8_b200_reference_policy", "moe_fp8_b200_stage_times", "moe_fp8_b200_route_noalloc",
+    "moe_fp8_b200_exchange_bytes", "moe_fp8_b200_run_reduce_scatter",
 ]
 NOALLOC_MAX_TOKENS = 4096
 
@@ -37,6 +38,12 @@ class Args(C.Structure):
         ("gemm2_weights", C.c_void_p), ("gemm2_weights_scale", C.c_void_p), ("local_expert_offset", C.c_int64),
         ("routed_scaling_factor", C.c_double), ("output", C.c_void_p), ("num_tokens", C.c_int32),
     ]
+
+
+class Exchange(C.Structure):
+    """moe_fp8_b200_exchange"""
+    _fields_ = [("peer_buffers", C.c_void_p * 8), ("buffer_bytes", C.c_size_t), ("rank", C.c_int32),
+                ("world", C.c_int32), ("epoch", C.c_uint32)]
 
 
 _lib = None
@@ -69,6 +76,10 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [H, C.POINTER(Args), C.c_void_p]
+    lib.moe_fp8_b200_exchange_bytes.restype = C.c_size_t
+    lib.moe_fp8_b200_exchange_bytes.argtypes = [C.c_int, C.c_int]
+    lib.moe_fp8_b200_run_reduce_scatter.restype = C.c_int
+    lib.moe_fp8_b200_run_reduce_scatter.argtypes = [H, C.POINTER(Args), C.POINTER(Exchange), C.c_void_p]
     lib.moe_fp8_b200_check.restype = C.c_int
     lib.moe_fp8_b200_check.argtypes = [H, C.c_void_p]
     lib.moe_fp8_b200_read_intermediate.restype = C.c_int

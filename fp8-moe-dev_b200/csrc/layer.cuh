@@ -54,6 +54,8 @@ struct Control {
     int pad;
     int expert_rows[kMaxLocalExperts];   // copy of the counters of the last call (diagnostics)
     int splitk_ticket[kSplitKSlots];     // per-tile arrival counters of the split-K reduction (self-clearing)
+    int push_done;                       // combine-and-push CTAs finished (ticket, self-clearing)
+    int pad2[3];
 };
 
 enum KernelStatus : int {
@@ -61,6 +63,27 @@ enum KernelStatus : int {
     kStatusGemm1Timeout = 101,
     kStatusGemm2Timeout = 102,
     kStatusRowOverflow = 103,
+    kStatusExchangeTimeout = 104,
+};
+
+// Cross-GPU exchange of the fused combine + reduce-scatter (expert-parallel ranks of one NVSwitch
+// box).  Every rank owns one receive buffer of identical layout in peer-mapped memory:
+//   [world sources] u32 (first 256 bytes)                    epoch of the last complete push
+//   [2 parities][world sources][tokens_per_rank][7168] bf16   partial rows, written by the source
+//   [2 parities][world sources][present_stride]       u8     1 if the source sent that row
+// Rank r owns tokens [r * tokens_per_rank, (r + 1) * tokens_per_rank).  Data are double-buffered
+// by epoch parity; a source may push epoch e + 2 only after it has reduced epoch e + 1, which
+// implies that every owner has finished reading epoch e (its push of e + 1 follows its own
+// reduce of e in stream order), so no further back-signal is needed.
+constexpr int kMaxRanks = 8;
+struct ExchangeView {
+    uint8_t* peer[kMaxRanks];   // receive buffer of every rank, mapped into this process
+    int rank, world;
+    int tokens_per_rank;        // ceil(T / world)
+    int present_stride;         // tokens_per_rank rounded up to 16
+    uint32_t epoch;
+    size_t data_offset;         // rows start here (the flags occupy the bytes before)
+    size_t rows_bytes_per_parity, present_bytes_per_parity;
 };
 
 // Device pointers into the workspace (all owned by the handle).

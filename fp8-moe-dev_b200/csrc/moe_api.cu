@@ -17,6 +17,8 @@ cudaError_t launch_route_dispatch(const float*, const void*, const Workspace&, i
                                   const DispatchPolicy&, int, cudaStream_t);
 cudaError_t launch_permute(const void*, const float*, const Workspace&, int, cudaStream_t);
 cudaError_t launch_combine(const Workspace&, void*, int, cudaStream_t);
+cudaError_t launch_combine_push(const Workspace&, const ExchangeView&, int, cudaStream_t);
+cudaError_t launch_reduce_owned(const Workspace&, const ExchangeView&, int, void*, cudaStream_t);
 int encode_kmajor_u8_map(void*, const void*, uint64_t, uint64_t, uint64_t, uint32_t);
 size_t tensor_map_bytes();
 cudaError_t configure_gemm_kernels();
@@ -157,7 +159,8 @@ void resolve_reference_policy(int T, DispatchPolicy& p)
     p.renorm = (T == 14107) ? 0 : 1;
 }
 
-int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_t stream)
+int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_t stream,
+                  const ExchangeView* ex = nullptr)
 {
     const int T = a.num_tokens;
     const int E = h->num_local_experts;
@@ -218,7 +221,14 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
     if (e == cudaSuccess && stop >= 4)
         e = launch_grouped_gemm(2, h->tmap_a2, h->tmap_w2, h->ws, a.gemm2_weights_scale, 0, ctas(2), split_k, stream);
     mark(5);
-    if (e == cudaSuccess && stop >= 5) e = launch_combine(h->ws, a.output, T, stream);
+    if (e == cudaSuccess && stop >= 5) {
+        if (ex) {
+            e = launch_combine_push(h->ws, *ex, T, stream);
+            if (e == cudaSuccess) e = launch_reduce_owned(h->ws, *ex, T, a.output, stream);
+        } else {
+            e = launch_combine(h->ws, a.output, T, stream);
+        }
+    }
     mark(6);
     if (e != cudaSuccess) {
         h->counters_dirty = true;
@@ -386,6 +396,55 @@ int moe_fp8_b200_run(moe_fp8_b200_handle h, const moe_fp8_b200_args* args, void*
     if (v != MOE_FP8_B200_OK) return v;
     if (args->num_tokens == 0) return MOE_FP8_B200_OK;
     return enqueue_layer(h, *args, static_cast<cudaStream_t>(stream));
+}
+
+namespace {
+constexpr size_t kExchangeFlagBytes = 256;
+void exchange_layout(int T, int world, ExchangeView& v)
+{
+    v.world = world;
+    v.tokens_per_rank = (T + world - 1) / world;
+    v.present_stride = (v.tokens_per_rank + 15) / 16 * 16;
+    v.data_offset = kExchangeFlagBytes;
+    v.rows_bytes_per_parity = (size_t)world * v.tokens_per_rank * kHidden * sizeof(__nv_bfloat16);
+    v.present_bytes_per_parity = align_up((size_t)world * v.present_stride, 256);
+}
+}  // namespace
+
+size_t moe_fp8_b200_exchange_bytes(int num_tokens, int world)
+{
+    if (num_tokens < 0 || (world != 1 && world != 2 && world != 4 && world != 8)) return 0;
+    ExchangeView v;
+    exchange_layout(num_tokens, world, v);
+    return v.data_offset + 2 * v.rows_bytes_per_parity + 2 * v.present_bytes_per_parity;
+}
+
+int moe_fp8_b200_run_reduce_scatter(moe_fp8_b200_handle h, const moe_fp8_b200_args* args,
+                                    const moe_fp8_b200_exchange* x, void* stream)
+{
+    const int v = validate(h, args);
+    if (v != MOE_FP8_B200_OK) return v;
+    if (!x) return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "exchange is NULL");
+    if (x->world != 1 && x->world != 2 && x->world != 4 && x->world != 8)
+        return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "world %d is not 1, 2, 4 or 8", x->world);
+    if (x->rank < 0 || x->rank >= x->world)
+        return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "rank %d outside [0, %d)", x->rank, x->world);
+    if (x->epoch == 0) return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "epoch must start at 1");
+    if (args->num_tokens == 0) return MOE_FP8_B200_OK;
+    ExchangeView view;
+    exchange_layout(args->num_tokens, x->world, view);
+    const size_t need = moe_fp8_b200_exchange_bytes(args->num_tokens, x->world);
+    if (x->buffer_bytes < need)
+        return fail(h, MOE_FP8_B200_ERR_CAPACITY, "exchange buffers hold %zu bytes, %d tokens on %d ranks need %zu",
+                    x->buffer_bytes, args->num_tokens, x->world, need);
+    for (int i = 0; i < kMaxRanks; ++i) {
+        view.peer[i] = i < x->world ? static_cast<uint8_t*>(x->peer_buffers[i]) : nullptr;
+        if (i < x->world && (!view.peer[i] || ((uintptr_t)view.peer[i] & 255u)))
+            return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "peer_buffers[%d] is NULL or not 256-byte aligned", i);
+    }
+    view.rank = x->rank;
+    view.epoch = x->epoch;
+    return enqueue_layer(h, *args, static_cast<cudaStream_t>(stream), &view);
 }
 
 int moe_fp8_b200_run_host(moe_fp8_b200_handle h, const moe_fp8_b200_args* args, void* stream_v)

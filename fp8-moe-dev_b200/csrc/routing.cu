@@ -488,4 +488,164 @@ cudaError_t launch_combine(const Workspace& ws, void* out, int T, cudaStream_t s
                       T);
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Fused combine + reduce-scatter over NVLink (no counterpart in the reference, which has no
+// multi-GPU code).  Instead of writing its partial [T, 7168] output locally and handing it to
+// a collective, every rank writes each weighted row sum straight into the receive buffer of
+// the rank that owns the token (plain peer stores; rows of tokens without a local expert are
+// not sent at all, only a one-byte "absent" mark), then raises a per-source epoch flag on
+// every peer.  The owner waits (bounded) for all sources' flags and adds the rows that are
+// present, in rank order, in fp32.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(kCombineThreads) combine_push_kernel(Workspace ws, ExchangeView ex, int T)
+{
+    const int t = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int parity = (int)(ex.epoch & 1u);
+    if (t < T) {
+        int n_pairs = ws.pair_count[t];
+        if (ws.num_tiles[0] == 0) n_pairs = 0;
+        const int owner = t / ex.tokens_per_rank;
+        const int tl = t - owner * ex.tokens_per_rank;
+        uint8_t* dst_base = ex.peer[owner] + ex.data_offset;
+        if (n_pairs > 0) {
+            float acc[2][8];
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[c][j] = 0.0f;
+            for (int p = 0; p < n_pairs; ++p) {
+                const uint32_t code = ws.pair_code[(size_t)t * kTopK + p];
+                const float w = ws.pair_weight[(size_t)t * kTopK + p];
+                const int row = ws.expert_offset[code >> 24] + (int)(code & 0x00ffffffu);
+                const uint4* src = reinterpret_cast<const uint4*>(ws.y + (size_t)row * kHidden);
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const uint4 raw = __ldg(src + threadIdx.x + c * kCombineThreads);
+                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __bfloat1622float2(h2[j]);
+                        acc[c][2 * j] += f.x * w;
+                        acc[c][2 * j + 1] += f.y * w;
+                    }
+                }
+            }
+            uint4* dst = reinterpret_cast<uint4*>(dst_base + (size_t)parity * ex.rows_bytes_per_parity +
+                                                  ((size_t)ex.rank * ex.tokens_per_rank + tl) * (kHidden * 2));
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint4 packed;
+                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(acc[c][2 * j], acc[c][2 * j + 1]);
+                dst[threadIdx.x + c * kCombineThreads] = packed;
+            }
+        }
+        if (threadIdx.x == 0) {
+            uint8_t* present = dst_base + 2 * ex.rows_bytes_per_parity + (size_t)parity * ex.present_bytes_per_parity +
+                               (size_t)ex.rank * ex.present_stride + tl;
+            *present = n_pairs > 0 ? 1 : 0;
+        }
+    }
+    // All of this CTA's peer stores become visible system-wide before it takes its ticket; the
+    // last CTA then publishes this rank's epoch on every peer.
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int ticket = atomicAdd(&ws.ctrl->push_done, 1);
+        if (ticket == (int)gridDim.x - 1) {
+            ws.ctrl->push_done = 0;
+            __threadfence_system();
+            for (int o = 0; o < ex.world; ++o) {
+                uint32_t* flag = reinterpret_cast<uint32_t*>(ex.peer[o]) + ex.rank;
+                st_release_sys_u32(flag, ex.epoch);
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kCombineThreads) reduce_owned_kernel(Workspace ws, ExchangeView ex, int T,
+                                                                       __nv_bfloat16* __restrict__ out)
+{
+    const int tl = blockIdx.x;   // token owned by this rank
+    pdl_launch_dependents();
+    pdl_wait();
+    const int parity = (int)(ex.epoch & 1u);
+    const uint8_t* mine = ex.peer[ex.rank] + ex.data_offset;
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) {
+        // bounded wait for every source's epoch flag (a peer that never arrives must not hang us)
+        const uint32_t* flags = reinterpret_cast<const uint32_t*>(ex.peer[ex.rank]);
+        int ok = 1;
+        const uint64_t t0 = global_timer_ns();
+        for (int src = 0; src < ex.world; ++src) {
+            uint32_t it = 0;
+            // epochs only grow; the signed difference also survives wrap-around
+            while ((int32_t)(ld_acquire_sys_u32(flags + src) - ex.epoch) < 0) {
+                if ((++it & 0x3ffu) == 0u && global_timer_ns() - t0 > kWaitLimitNs) { ok = 0; break; }
+            }
+            if (!ok) break;
+        }
+        if (!ok) atomicCAS(&ws.ctrl->status, kStatusOk, kStatusExchangeTimeout);
+        s_ok = ok;
+    }
+    __syncthreads();
+    const int t = ex.rank * ex.tokens_per_rank + tl;
+    if (t >= T) return;
+    float acc[2][8];
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[c][j] = 0.0f;
+    if (s_ok) {
+        const uint8_t* present = mine + 2 * ex.rows_bytes_per_parity + (size_t)parity * ex.present_bytes_per_parity + tl;
+        for (int src = 0; src < ex.world; ++src) {
+            if (present[(size_t)src * ex.present_stride] == 0) continue;
+            const uint4* row = reinterpret_cast<const uint4*>(mine + (size_t)parity * ex.rows_bytes_per_parity +
+                                                              ((size_t)src * ex.tokens_per_rank + tl) * (kHidden * 2));
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const uint4 raw = row[threadIdx.x + c * kCombineThreads];
+                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __bfloat1622float2(h2[j]);
+                    acc[c][2 * j] += f.x;
+                    acc[c][2 * j + 1] += f.y;
+                }
+            }
+        }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)tl * kHidden);
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        uint4 packed;
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(acc[c][2 * j], acc[c][2 * j + 1]);
+        dst[threadIdx.x + c * kCombineThreads] = packed;
+    }
+}
+
+cudaError_t launch_combine_push(const Workspace& ws, const ExchangeView& ex, int T, cudaStream_t stream)
+{
+    return launch_pdl(combine_push_kernel, dim3(T), dim3(kCombineThreads), 0, stream, ws, ex, T);
+}
+cudaError_t launch_reduce_owned(const Workspace& ws, const ExchangeView& ex, int T, void* out, cudaStream_t stream)
+{
+    return launch_pdl(reduce_owned_kernel, dim3(ex.tokens_per_rank), dim3(kCombineThreads), 0, stream, ws, ex, T,
+                      static_cast<__nv_bfloat16*>(out));
+}
 }  // namespace moe

@@ -6,8 +6,11 @@ multi-GPU code; its `local_expert_offset` argument (kernel/moe_fp8.cu:2668, 462-
 hook this builds on.
 
 The reduction is the path's one exchange step.  `partial -> all_reduce` (every rank ends
-with the full [T,7168] output) or `partial -> reduce_scatter` (rank r ends with tokens
-[r*T/G, (r+1)*T/G)).  The host-side planning (who owns which experts / tokens) is plain
+with the full [T,7168] output), `partial -> reduce_scatter` (rank r ends with tokens
+[r*T/G, (r+1)*T/G)), both through NCCL, or `fused`: the combine kernel itself stores each
+token's row into the owning rank's receive buffer over NVLink (plain peer stores into
+symmetric memory) and the owner adds what arrived, so no partial [T,7168] tensor and no
+separate collective exist.  The host-side planning (who owns which experts / tokens) is plain
 Python so that it can be tested with gloo ranks on CPU.
 """
 from __future__ import annotations
@@ -73,10 +76,53 @@ class ShardedMoe:
         self.rank, self.world, self.group = rank, world, group
         self.local_expert_offset, self.num_local_experts = expert_range(rank, world)
         self.layer = MoeLayer(max_tokens, self.num_local_experts, device)
+        self.max_tokens = max_tokens
+        self._exchange = None   # (symmetric buffer, handle, peer pointers, bytes), made on first fused run
+        self._epoch = 0
+
+    def _ensure_exchange(self):
+        """Allocate and exchange the receive buffers (torch symmetric memory: plumbing only;
+        every byte that crosses NVLink is moved by this package's own kernels)."""
+        if self._exchange is not None:
+            return self._exchange
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _lib
+        nbytes = int(_lib.load().moe_fp8_b200_exchange_bytes(self.max_tokens, self.world))
+        dev = torch.device("cuda", self.layer.device)
+        group = self.group if self.group is not None else dist.group.WORLD
+        buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
+        hdl = symm_mem.rendezvous(buf, group=group)
+        buf.zero_()
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=group)   # nobody pushes before every buffer has been zeroed
+        self._exchange = (buf, hdl, [int(p) for p in hdl.buffer_ptrs], nbytes)
+        return self._exchange
+
+    def run_fused(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                  gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, routed_scaling_factor,
+                  scatter_out: Optional[torch.Tensor] = None):
+        """The layer with combine and reduce-scatter in one step; returns this rank's
+        [ceil(T / world), 7168] slice of the summed output."""
+        T = int(routing_logits.shape[0])
+        per = (T + self.world - 1) // self.world
+        if scatter_out is None:
+            scatter_out = torch.empty((per, 7168), dtype=torch.bfloat16, device=routing_logits.device)
+        if T == 0:
+            return scatter_out
+        _, _, ptrs, nbytes = self._ensure_exchange()
+        self._epoch += 1
+        return self.layer.run_reduce_scatter(
+            routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+            gemm2_weights, gemm2_weights_scale, self.local_expert_offset, routed_scaling_factor, scatter_out,
+            ptrs, nbytes, self.rank, self.world, self._epoch)
 
     def run(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
             gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, routed_scaling_factor, output,
             mode: str = "all_reduce", scatter_out: Optional[torch.Tensor] = None):
+        if mode == "fused":
+            return self.run_fused(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                                  gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, routed_scaling_factor,
+                                  scatter_out)
         self.layer.run(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
                        gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, self.local_expert_offset,
                        routed_scaling_factor, output)

@@ -101,7 +101,7 @@ class MoeLayer:
     # -- the operator -----------------------------------------------------------------
     def _args(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
               gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
-              routed_scaling_factor, output, host: bool):
+              routed_scaling_factor, output, host: bool, out_rows: Optional[int] = None):
         T = int(routing_logits.shape[0])
         E = self.num_local_experts
         dev = torch.device("cuda", self.device)
@@ -114,7 +114,7 @@ class MoeLayer:
         _check_tensor("gemm1_weights_scale", gemm1_weights_scale, torch.float32, (E, N1 // 128, H // 128), dev)
         _check_tensor("gemm2_weights", gemm2_weights, torch.float8_e4m3fn, (E, H, I), dev)
         _check_tensor("gemm2_weights_scale", gemm2_weights_scale, torch.float32, (E, H // 128, I // 128), dev)
-        _check_tensor("output", output, torch.bfloat16, (T, H), io_dev)
+        _check_tensor("output", output, torch.bfloat16, (T if out_rows is None else out_rows, H), io_dev)
         a = _lib.Args()
         a.routing_logits = routing_logits.data_ptr()
         a.routing_bias = routing_bias.data_ptr()
@@ -143,6 +143,29 @@ class MoeLayer:
         if rc != _lib.OK:
             self._raise(rc)
         return output
+
+    def run_reduce_scatter(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                           gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                           routed_scaling_factor, owned_output, peer_buffers, buffer_bytes: int, rank: int,
+                           world: int, epoch: int, stream: Optional[int] = None):
+        """Expert-parallel run with the cross-rank sum fused into the combine step:
+        `owned_output` [ceil(T / world), 7168] receives this rank's token slice of the summed
+        output.  `peer_buffers` are the ranks' receive buffers as mapped into this process."""
+        T = int(routing_logits.shape[0])
+        per = (T + world - 1) // world
+        a = self._args(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                       gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                       routed_scaling_factor, owned_output, host=False, out_rows=per)
+        x = _lib.Exchange()
+        for i, ptr in enumerate(peer_buffers):
+            x.peer_buffers[i] = int(ptr)
+        x.buffer_bytes, x.rank, x.world, x.epoch = int(buffer_bytes), int(rank), int(world), int(epoch) & 0xFFFFFFFF
+        if stream is None:
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._lib.moe_fp8_b200_run_reduce_scatter(self._h, C.byref(a), C.byref(x), C.c_void_p(stream))
+        if rc != _lib.OK:
+            self._raise(rc)
+        return owned_output
 
     def run_host(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
                  gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,

@@ -134,6 +134,38 @@ MOE_FP8_B200_API int moe_fp8_b200_run(moe_fp8_b200_handle h, const moe_fp8_b200_
  * end-to-end form a host-resident caller of the reference operator sees. */
 MOE_FP8_B200_API int moe_fp8_b200_run_host(moe_fp8_b200_handle h, const moe_fp8_b200_args* args, void* stream);
 
+/* ---- expert-parallel run with the reduce-scatter fused into the combine step -----------
+ * No counterpart in the reference (it has no multi-GPU code; its local_expert_offset
+ * argument, kernel/moe_fp8.cu:2671, only says which 32 experts a rank holds).  `world` ranks
+ * of one NVLink box each run the layer for their own experts on the full, replicated token
+ * batch.  Instead of writing a partial [T, 7168] output for a collective, the combine kernel
+ * stores each token's weighted row sum straight into the receive buffer of the rank that owns
+ * the token (rank r owns tokens [r * ceil(T / world), (r + 1) * ceil(T / world))), with plain
+ * peer stores, and the owner adds the rows it received in rank order in fp32.  Rows of tokens
+ * without an expert on the sending rank are not sent.
+ *
+ * peer_buffers[i] is rank i's receive buffer as mapped into THIS process (peer access or an
+ * IPC / symmetric-memory mapping; peer_buffers[rank] is the local one); every buffer holds at
+ * least moe_fp8_b200_exchange_bytes(T, world) bytes, is 256-byte aligned and was zeroed once
+ * before the first call.  `epoch` starts at 1 and grows by exactly 1 on every call, on every
+ * rank alike (all ranks make the same sequence of calls with the same T).  The waits on peers
+ * are bounded (1 s): a rank that never arrives leaves MOE_FP8_B200_ERR_DEVICE in
+ * moe_fp8_b200_check, not a hung GPU. */
+typedef struct moe_fp8_b200_exchange {
+    void* peer_buffers[8];
+    size_t buffer_bytes;   /* size of each buffer */
+    int32_t rank;
+    int32_t world;         /* 1, 2, 4 or 8 */
+    uint32_t epoch;
+} moe_fp8_b200_exchange;
+
+MOE_FP8_B200_API size_t moe_fp8_b200_exchange_bytes(int num_tokens, int world);
+
+/* args->output receives this rank's owned rows only: [ceil(T / world), 7168] bf16 (rows past
+ * T, on the last ranks, are not written).  Everything else as moe_fp8_b200_run. */
+MOE_FP8_B200_API int moe_fp8_b200_run_reduce_scatter(moe_fp8_b200_handle h, const moe_fp8_b200_args* args,
+                                                     const moe_fp8_b200_exchange* exchange, void* stream);
+
 /* Synchronises `stream` and returns MOE_FP8_B200_ERR_DEVICE if any kernel of earlier
  * runs recorded a failure in the device status word. */
 MOE_FP8_B200_API int moe_fp8_b200_check(moe_fp8_b200_handle h, void* stream);

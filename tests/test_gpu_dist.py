@@ -59,14 +59,25 @@ def _worker(rank, world, port, T, q):
         lo, hi = token_range(rank, world, T)
         ok_scatter = torch.equal(scat[:hi - lo], want[lo:hi])
         nonzero = bool(full.float().abs().sum() > 0)
-        q.put((rank, ok_sum, ok_scatter, nonzero))
+        # combine + reduce-scatter fused into one step over peer memory, three calls in a row
+        # (both parities of the receive buffer and its reuse); with two ranks the fp32 sum of
+        # two bf16 rows rounded once equals the bf16 sum, so the results must be identical
+        ok_fused = True
+        for _ in range(3):
+            torch.cuda.synchronize()
+            dist.barrier()
+            got = moe.run(*dev, *w, 2.5, out, mode="fused")
+            moe.layer.check()
+            ok_fused = ok_fused and got.shape[0] == (T + world - 1) // world and torch.equal(got[:hi - lo], want[lo:hi])
+        q.put((rank, ok_sum, ok_scatter and ok_fused, nonzero))
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_gpu_expert_parallel_sum():
-    world, T = 2, 96
+@pytest.mark.parametrize("T", [96, 33])
+def test_two_gpu_expert_parallel_sum(T):
+    world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
