@@ -317,19 +317,22 @@ def cpu_baseline(inputs, weights, sample_tokens=64):
 
 def run_ours(args, rank, world, local):
     pkg = entry.load_package()
-    from fp8_moe_dev_b200.dist import combine_partials
+    from fp8_moe_dev_b200.dist import ShardedMoe, combine_partials
     T, offset, E, inputs, weights = make_workload(args.workload, rank, world)
     dev = [x.cuda() for x in inputs]
     w1, s1, w2, s2 = weights
-    layer = pkg.MoeLayer(T, E, local)
+    moe = ShardedMoe(T, rank, world, local) if world > 1 else None
+    layer = moe.layer if moe else pkg.MoeLayer(T, E, local)
     out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
 
     per = (T + world - 1) // world
     scat = torch.empty(per, H, dtype=torch.bfloat16, device="cuda")
 
     def step(mode=args.collective):
+        if mode == "fused" and moe:
+            return moe.run_fused(*dev, w1, s1, w2, s2, RSF, scatter_out=scat)
         layer.run(*dev, w1, s1, w2, s2, offset, RSF, out)
-        combine_partials(out, mode, scatter_out=scat)
+        return combine_partials(out, mode, scatter_out=scat)
 
     step()
     layer.check()
@@ -355,8 +358,7 @@ def run_ours(args, rank, world, local):
             dev[0].copy_(pin[0], non_blocking=True)
             dev[2].copy_(pin[1], non_blocking=True)
             dev[3].copy_(pin[2], non_blocking=True)
-            layer.run(*dev, w1, s1, w2, s2, offset, RSF, out)
-            res = combine_partials(out, args.collective, scatter_out=scat)
+            res = step()
             host_out[:res.shape[0]].copy_(res, non_blocking=True)
             torch.cuda.current_stream().synchronize()
     e2e_ms = time_steps(e2e_step, max(3, args.steps // 2), 3, world) if not args.skip_e2e else float("nan")
@@ -364,8 +366,9 @@ def run_ours(args, rank, world, local):
     d2h = (host_out if (world == 1 or args.collective == "all_reduce") else scat).numel() * 2
     other_ms = None
     if world > 1:
-        other = "all_reduce" if args.collective == "reduce_scatter" else "reduce_scatter"
-        other_ms = time_steps(lambda: step(other), max(5, args.steps // 2), 3, world)
+        other_ms = {m: round(time_steps(lambda: step(m), max(5, args.steps // 2), 3, world), 4)
+                    for m in ("fused", "reduce_scatter", "all_reduce") if m != args.collective}
+        layer.check()
 
     pk = peaks()
     g1_ms = max_over_ranks(stages["gemm1"], world)
@@ -383,13 +386,14 @@ def run_ours(args, rank, world, local):
                    "l2": f"inputs larger than L2 (weights {E * 44.04e-3:.1f} GB on this GPU), no flush",
                    "ideal_scaling_bound": round(rows_total / rows_max, 3) if rows_max else None,
                    "collective": None if world == 1 else args.collective,
-                   "other_collective_ms_per_step": None if other_ms is None else round(other_ms, 4)},
+                   "other_collective_ms_per_step": other_ms},
         "clocks": clk.summary(),
         "e2e": None if args.skip_e2e else {"value": round(T / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "path": "moe_fp8_b200_run_host (C ABI, host buffers)" if world == 1
-                        else f"pinned H2D + moe_fp8_b200_run + NCCL {args.collective} + D2H"},
-        "gpu_launches": 6 * args.steps * world,
+                        else ("pinned H2D + moe_fp8_b200_run_reduce_scatter (peer stores) + D2H" if args.collective == "fused"
+                              else f"pinned H2D + moe_fp8_b200_run + NCCL {args.collective} + D2H")},
+        "gpu_launches": (6 if (world > 1 and args.collective == "fused") else 5) * args.steps * world,
         "stage_ms": {k: round(max_over_ranks(v, world), 4) for k, v in stages.items()},
         "layer_tflops": round(rows_max * FLOPS_PER_ROW / (ms * 1e-3) / 1e12, 1),
         "roofline": {"kernel": "grouped_gemm_kernel<1> (GEMM1 + SwiGLU + requant)", "bound": "tensor",
@@ -443,7 +447,7 @@ def run_reference(args, rank, world, local):
         out.copy_(parts[0])
         for s in range(1, shards):
             out.add_(parts[s])
-        combine_partials(out, args.collective, scatter_out=scat)
+        combine_partials(out, "reduce_scatter" if args.collective == "fused" else args.collective, scatter_out=scat)
 
     with ClockSampler(local) as clk:
         ms = time_steps(step, args.steps, args.warmup, world)
@@ -473,10 +477,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="t12288_e256")
-    ap.add_argument("--collective", choices=["reduce_scatter", "all_reduce"], default="reduce_scatter",
-                    help="how the ranks' bf16 partial outputs are summed for N > 1: reduce_scatter leaves rank r "
+    ap.add_argument("--collective", choices=["fused", "reduce_scatter", "all_reduce"], default="reduce_scatter",
+                    help="how the ranks' partial outputs are summed for N > 1: reduce_scatter leaves rank r "
                          "with tokens [r*T/N, (r+1)*T/N) (the inverse of the all-gather that replicated the "
-                         "inputs); all_reduce leaves every rank with all T tokens")
+                         "inputs); all_reduce leaves every rank with all T tokens; fused gives the reduce_scatter "
+                         "result with the exchange done by the combine kernel's own peer stores (the reference "
+                         "arm uses NCCL reduce_scatter for it)")
     ap.add_argument("--skip-small", action="store_true", help="skip the T=1/16/1024 single-shard latencies")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the host fp32 baseline")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")

@@ -507,18 +507,35 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
     return v;
 }
 
-__global__ void __launch_bounds__(kCombineThreads) combine_push_kernel(Workspace ws, ExchangeView ex, int T)
+// Select without dynamic indexing: the view is a kernel parameter, and indexing its pointer
+// array with a run-time value would make the compiler copy it to local memory.
+__device__ __forceinline__ uint8_t* peer_ptr(const ExchangeView& ex, int i) {
+    uint8_t* p = ex.peer[0];
+#pragma unroll
+    for (int k = 1; k < kMaxRanks; ++k)
+        if (i == k) p = ex.peer[k];
+    return p;
+}
+
+__global__ void __launch_bounds__(kCombineThreads, 2) combine_push_kernel(Workspace ws, ExchangeView ex, int T)
 {
-    const int t = blockIdx.x;
     pdl_launch_dependents();
     pdl_wait();
     const int parity = (int)(ex.epoch & 1u);
-    if (t < T) {
-        int n_pairs = ws.pair_count[t];
-        if (ws.num_tiles[0] == 0) n_pairs = 0;
+    const bool any_tiles = ws.num_tiles[0] != 0;
+    // Persistent CTAs walk the tokens starting with the next rank's slice and ending with their
+    // own, so the remote stores go out first and every rank starts on a different destination.
+    // One system-scope fence per CTA, after its last store, instead of one per token.
+    const int span = ex.tokens_per_rank * ex.world;
+    const int start = ((ex.rank + 1) % ex.world) * ex.tokens_per_rank;
+    for (int i = blockIdx.x; i < span; i += gridDim.x) {
+        int t = start + i;
+        if (t >= span) t -= span;
+        if (t >= T) continue;
+        const int n_pairs = any_tiles ? ws.pair_count[t] : 0;
         const int owner = t / ex.tokens_per_rank;
         const int tl = t - owner * ex.tokens_per_rank;
-        uint8_t* dst_base = ex.peer[owner] + ex.data_offset;
+        uint8_t* dst_base = peer_ptr(ex, owner) + ex.data_offset;
         if (n_pairs > 0) {
             float acc[2][8];
 #pragma unroll
@@ -569,7 +586,7 @@ __global__ void __launch_bounds__(kCombineThreads) combine_push_kernel(Workspace
             ws.ctrl->push_done = 0;
             __threadfence_system();
             for (int o = 0; o < ex.world; ++o) {
-                uint32_t* flag = reinterpret_cast<uint32_t*>(ex.peer[o]) + ex.rank;
+                uint32_t* flag = reinterpret_cast<uint32_t*>(peer_ptr(ex, o)) + ex.rank;
                 st_release_sys_u32(flag, ex.epoch);
             }
         }
@@ -583,11 +600,12 @@ __global__ void __launch_bounds__(kCombineThreads) reduce_owned_kernel(Workspace
     pdl_launch_dependents();
     pdl_wait();
     const int parity = (int)(ex.epoch & 1u);
-    const uint8_t* mine = ex.peer[ex.rank] + ex.data_offset;
+    uint8_t* const mine_base = peer_ptr(ex, ex.rank);
+    const uint8_t* mine = mine_base + ex.data_offset;
     __shared__ int s_ok;
     if (threadIdx.x == 0) {
         // bounded wait for every source's epoch flag (a peer that never arrives must not hang us)
-        const uint32_t* flags = reinterpret_cast<const uint32_t*>(ex.peer[ex.rank]);
+        const uint32_t* flags = reinterpret_cast<const uint32_t*>(mine_base);
         int ok = 1;
         const uint64_t t0 = global_timer_ns();
         for (int src = 0; src < ex.world; ++src) {
@@ -641,7 +659,13 @@ __global__ void __launch_bounds__(kCombineThreads) reduce_owned_kernel(Workspace
 
 cudaError_t launch_combine_push(const Workspace& ws, const ExchangeView& ex, int T, cudaStream_t stream)
 {
-    return launch_pdl(combine_push_kernel, dim3(T), dim3(kCombineThreads), 0, stream, ws, ex, T);
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    const int span = ex.tokens_per_rank * ex.world;
+    const int grid = span < sms * 2 ? span : sms * 2;   // two resident CTAs per SM
+    return launch_pdl(combine_push_kernel, dim3(grid), dim3(kCombineThreads), 0, stream, ws, ex, T);
 }
 cudaError_t launch_reduce_owned(const Workspace& ws, const ExchangeView& ex, int T, void* out, cudaStream_t stream)
 {
