@@ -477,7 +477,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="t12288_e256")
-    ap.add_argument("--collective", choices=["fused", "reduce_scatter", "all_reduce"], default="reduce_scatter",
+    ap.add_argument("--collective", choices=["fused", "reduce_scatter", "all_reduce"], default="fused",
                     help="how the ranks' partial outputs are summed for N > 1: reduce_scatter leaves rank r "
                          "with tokens [r*T/N, (r+1)*T/N) (the inverse of the all-gather that replicated the "
                          "inputs); all_reduce leaves every rank with all T tokens; fused gives the reduce_scatter "
