@@ -25,7 +25,8 @@ EXPORTS = [
     "moe_fp8_b200_create", "moe_fp8_b200_destroy", "moe_fp8_b200_last_error", "moe_fp8_b200_set_option",
     "moe_fp8_b200_run", "moe_fp8_b200_run_host", "moe_fp8_b200_check", "moe_fp8_b200_read_intermediate",
     "moe_fp8_b200_reference_policy", "moe_fp8_b200_stage_times", "moe_fp8_b200_route_noalloc",
-    "moe_fp8_b200_exchange_bytes", "moe_fp8_b200_run_reduce_scatter",
+    "moe_fp8_b200_exchange_bytes", "moe_fp8_b200_run_reduce_scatter", "moe_fp8_b200_quantize_hidden",
+    "moe_fp8_b200_run_unfinalized", "moe_fp8_b200_finalize",
 ]
 NOALLOC_MAX_TOKENS = 4096
 
@@ -44,6 +45,12 @@ class Exchange(C.Structure):
     """moe_fp8_b200_exchange"""
     _fields_ = [("peer_buffers", C.c_void_p * 8), ("buffer_bytes", C.c_size_t), ("rank", C.c_int32),
                 ("world", C.c_int32), ("epoch", C.c_uint32)]
+
+
+class Unfinalized(C.Structure):
+    """moe_fp8_b200_unfinalized"""
+    _fields_ = [("y", C.c_void_p), ("expert_offset", C.c_void_p), ("pair_count", C.c_void_p),
+                ("pair_code", C.c_void_p), ("pair_weight", C.c_void_p), ("row_capacity", C.c_int32)]
 
 
 _lib = None
@@ -80,6 +87,12 @@ def load() -> C.CDLL:
     lib.moe_fp8_b200_exchange_bytes.argtypes = [C.c_int, C.c_int]
     lib.moe_fp8_b200_run_reduce_scatter.restype = C.c_int
     lib.moe_fp8_b200_run_reduce_scatter.argtypes = [H, C.POINTER(Args), C.POINTER(Exchange), C.c_void_p]
+    lib.moe_fp8_b200_quantize_hidden.restype = C.c_int
+    lib.moe_fp8_b200_quantize_hidden.argtypes = [H, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.moe_fp8_b200_run_unfinalized.restype = C.c_int
+    lib.moe_fp8_b200_run_unfinalized.argtypes = [H, C.POINTER(Args), C.POINTER(Unfinalized), C.c_void_p]
+    lib.moe_fp8_b200_finalize.restype = C.c_int
+    lib.moe_fp8_b200_finalize.argtypes = [H, C.c_int, C.c_void_p, C.c_void_p]
     lib.moe_fp8_b200_check.restype = C.c_int
     lib.moe_fp8_b200_check.argtypes = [H, C.c_void_p]
     lib.moe_fp8_b200_read_intermediate.restype = C.c_int

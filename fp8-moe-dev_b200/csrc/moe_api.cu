@@ -17,6 +17,7 @@ cudaError_t launch_route_dispatch(const float*, const void*, const Workspace&, i
                                   const DispatchPolicy&, int, cudaStream_t);
 cudaError_t launch_permute(const void*, const float*, const Workspace&, int, cudaStream_t);
 cudaError_t launch_combine(const Workspace&, void*, int, cudaStream_t);
+cudaError_t launch_quantize_rows(const void*, void*, float*, int, cudaStream_t);
 cudaError_t launch_combine_push(const Workspace&, const ExchangeView&, int, cudaStream_t);
 cudaError_t launch_reduce_owned(const Workspace&, const ExchangeView&, int, void*, cudaStream_t);
 int encode_kmajor_u8_map(void*, const void*, uint64_t, uint64_t, uint64_t, uint32_t);
@@ -160,7 +161,7 @@ void resolve_reference_policy(int T, DispatchPolicy& p)
 }
 
 int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_t stream,
-                  const ExchangeView* ex = nullptr)
+                  const ExchangeView* ex = nullptr, bool finalize = true)
 {
     const int T = a.num_tokens;
     const int E = h->num_local_experts;
@@ -221,7 +222,7 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
     if (e == cudaSuccess && stop >= 4)
         e = launch_grouped_gemm(2, h->tmap_a2, h->tmap_w2, h->ws, a.gemm2_weights_scale, 0, ctas(2), split_k, stream);
     mark(5);
-    if (e == cudaSuccess && stop >= 5) {
+    if (e == cudaSuccess && stop >= 5 && finalize) {
         if (ex) {
             e = launch_combine_push(h->ws, *ex, T, stream);
             if (e == cudaSuccess) e = launch_reduce_owned(h->ws, *ex, T, a.output, stream);
@@ -237,7 +238,7 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
     return MOE_FP8_B200_OK;
 }
 
-int validate(moe_fp8_b200_handle h, const moe_fp8_b200_args* a)
+int validate(moe_fp8_b200_handle h, const moe_fp8_b200_args* a, bool need_output = true)
 {
     if (!h) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
     if (!a) return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "args is NULL");
@@ -247,7 +248,8 @@ int validate(moe_fp8_b200_handle h, const moe_fp8_b200_args* a)
                     h->max_tokens);
     if (a->num_tokens == 0) return MOE_FP8_B200_OK;
     if (!a->routing_logits || !a->routing_bias || !a->hidden_states || !a->hidden_states_scale ||
-        !a->gemm1_weights || !a->gemm1_weights_scale || !a->gemm2_weights || !a->gemm2_weights_scale || !a->output)
+        !a->gemm1_weights || !a->gemm1_weights_scale || !a->gemm2_weights || !a->gemm2_weights_scale ||
+        (need_output && !a->output))
         return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "a tensor pointer is NULL");
     if (a->local_expert_offset < 0 || a->local_expert_offset >= kNumExperts)
         return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "local_expert_offset %lld outside [0, 256)",
@@ -445,6 +447,49 @@ int moe_fp8_b200_run_reduce_scatter(moe_fp8_b200_handle h, const moe_fp8_b200_ar
     view.rank = x->rank;
     view.epoch = x->epoch;
     return enqueue_layer(h, *args, static_cast<cudaStream_t>(stream), &view);
+}
+
+int moe_fp8_b200_quantize_hidden(moe_fp8_b200_handle h, const void* x, int num_tokens, void* q, float* scale,
+                                 void* stream)
+{
+    if (!h) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
+    if (num_tokens < 0) return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "num_tokens %d < 0", num_tokens);
+    if (num_tokens == 0) return MOE_FP8_B200_OK;
+    if (!x || !q || !scale) return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "a tensor pointer is NULL");
+    if (((uintptr_t)x & 15u) || ((uintptr_t)q & 15u) || ((uintptr_t)scale & 3u))
+        return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "x and q must be 16-byte aligned");
+    const cudaError_t e = launch_quantize_rows(x, q, scale, num_tokens, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "quantize launch failed: %s", cudaGetErrorString(e));
+    return MOE_FP8_B200_OK;
+}
+
+int moe_fp8_b200_run_unfinalized(moe_fp8_b200_handle h, const moe_fp8_b200_args* args,
+                                 moe_fp8_b200_unfinalized* views, void* stream)
+{
+    const int v = validate(h, args, /*need_output=*/false);
+    if (v != MOE_FP8_B200_OK) return v;
+    if (!views) return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "views is NULL");
+    views->y = h->ws.y;
+    views->expert_offset = h->ws.expert_offset;
+    views->pair_count = h->ws.pair_count;
+    views->pair_code = h->ws.pair_code;
+    views->pair_weight = h->ws.pair_weight;
+    views->row_capacity = h->ws.m_cap;
+    if (args->num_tokens == 0) return MOE_FP8_B200_OK;
+    return enqueue_layer(h, *args, static_cast<cudaStream_t>(stream), nullptr, /*finalize=*/false);
+}
+
+int moe_fp8_b200_finalize(moe_fp8_b200_handle h, int num_tokens, void* output, void* stream)
+{
+    if (!h) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
+    if (num_tokens < 0 || num_tokens > h->max_tokens)
+        return fail(h, MOE_FP8_B200_ERR_CAPACITY, "num_tokens %d outside [0, %d]", num_tokens, h->max_tokens);
+    if (num_tokens == 0) return MOE_FP8_B200_OK;
+    if (!output || ((uintptr_t)output & 15u))
+        return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "output is NULL or not 16-byte aligned");
+    const cudaError_t e = launch_combine(h->ws, output, num_tokens, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "combine launch failed: %s", cudaGetErrorString(e));
+    return MOE_FP8_B200_OK;
 }
 
 int moe_fp8_b200_run_host(moe_fp8_b200_handle h, const moe_fp8_b200_args* args, void* stream_v)

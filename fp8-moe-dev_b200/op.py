@@ -38,6 +38,19 @@ def _check_tensor(name, t, dtype, shape, device=None):
         raise ValueError(f"{name} must live on {device}, got {t.device}")
 
 
+class _DeviceSpan:
+    """A borrowed range of device memory, presented through the CUDA array interface."""
+
+    def __init__(self, ptr, shape, typestr):
+        self.__cuda_array_interface__ = dict(shape=tuple(shape), typestr=typestr, data=(int(ptr), False), version=3,
+                                             strides=None)
+
+
+def _device_view(ptr, shape, typestr, device):
+    """torch tensor over memory the library owns (no copy)."""
+    return torch.as_tensor(_DeviceSpan(ptr, shape, typestr), device=torch.device("cuda", device))
+
+
 class MoeLayer:
     """One handle = one GPU's workspace for up to `max_tokens` tokens and `num_local_experts`
     experts (32 per reference shard; 64/128/256 hold several shards on one GPU)."""
@@ -114,7 +127,8 @@ class MoeLayer:
         _check_tensor("gemm1_weights_scale", gemm1_weights_scale, torch.float32, (E, N1 // 128, H // 128), dev)
         _check_tensor("gemm2_weights", gemm2_weights, torch.float8_e4m3fn, (E, H, I), dev)
         _check_tensor("gemm2_weights_scale", gemm2_weights_scale, torch.float32, (E, H // 128, I // 128), dev)
-        _check_tensor("output", output, torch.bfloat16, (T if out_rows is None else out_rows, H), io_dev)
+        if output is not None:
+            _check_tensor("output", output, torch.bfloat16, (T if out_rows is None else out_rows, H), io_dev)
         a = _lib.Args()
         a.routing_logits = routing_logits.data_ptr()
         a.routing_bias = routing_bias.data_ptr()
@@ -126,7 +140,7 @@ class MoeLayer:
         a.gemm2_weights_scale = gemm2_weights_scale.data_ptr()
         a.local_expert_offset = int(local_expert_offset)
         a.routed_scaling_factor = float(routed_scaling_factor)
-        a.output = output.data_ptr()
+        a.output = output.data_ptr() if output is not None else None
         a.num_tokens = T
         return a
 
@@ -166,6 +180,61 @@ class MoeLayer:
         if rc != _lib.OK:
             self._raise(rc)
         return owned_output
+
+    # -- the operators either side of the layer ----------------------------------------
+    def quantize_hidden(self, x, q_out=None, scale_out=None, stream: Optional[int] = None):
+        """bf16 x [T, 7168] (device) -> (e4m3 [T, 7168], fp32 scales [56, T]): the pair `run` takes."""
+        T = int(x.shape[0])
+        dev = torch.device("cuda", self.device)
+        _check_tensor("x", x, torch.bfloat16, (T, H), dev)
+        if q_out is None:
+            q_out = torch.empty((T, H), dtype=torch.float8_e4m3fn, device=dev)
+        if scale_out is None:
+            scale_out = torch.empty((H // 128, T), dtype=torch.float32, device=dev)
+        _check_tensor("q_out", q_out, torch.float8_e4m3fn, (T, H), dev)
+        _check_tensor("scale_out", scale_out, torch.float32, (H // 128, T), dev)
+        if stream is None:
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._lib.moe_fp8_b200_quantize_hidden(self._h, x.data_ptr(), T, q_out.data_ptr(), scale_out.data_ptr(),
+                                                    C.c_void_p(stream))
+        if rc != _lib.OK:
+            self._raise(rc)
+        return q_out, scale_out
+
+    def run_unfinalized(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                        gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                        routed_scaling_factor, stream: Optional[int] = None):
+        """The layer without the weighted combine.  Returns views INTO the workspace (valid until
+        the next run on this layer): y bf16 [row_capacity, 7168], expert_offset int32 [E+1],
+        pair_count int32 [T], pair_code int32 [T, 8] ((local expert << 24) | slot), pair_weight
+        fp32 [T, 8]."""
+        T = int(routing_logits.shape[0])
+        a = self._args(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                       gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                       routed_scaling_factor, None, host=False)
+        v = _lib.Unfinalized()
+        if stream is None:
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._lib.moe_fp8_b200_run_unfinalized(self._h, C.byref(a), C.byref(v), C.c_void_p(stream))
+        if rc != _lib.OK:
+            self._raise(rc)
+        E, cap = self.num_local_experts, int(v.row_capacity)
+        return dict(
+            y=_device_view(v.y, (cap, H), "<i2", self.device).view(torch.bfloat16),
+            expert_offset=_device_view(v.expert_offset, (E + 1,), "<i4", self.device),
+            pair_count=_device_view(v.pair_count, (T,), "<i4", self.device),
+            pair_code=_device_view(v.pair_code, (T, 8), "<i4", self.device),
+            pair_weight=_device_view(v.pair_weight, (T, 8), "<f4", self.device))
+
+    def finalize(self, num_tokens: int, output, stream: Optional[int] = None):
+        """The weighted combine of the latest unfinalized run into bf16 `output` [T, 7168]."""
+        _check_tensor("output", output, torch.bfloat16, (int(num_tokens), H), torch.device("cuda", self.device))
+        if stream is None:
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._lib.moe_fp8_b200_finalize(self._h, int(num_tokens), output.data_ptr(), C.c_void_p(stream))
+        if rc != _lib.OK:
+            self._raise(rc)
+        return output
 
     def run_host(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
                  gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,

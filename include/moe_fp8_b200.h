@@ -166,6 +166,38 @@ MOE_FP8_B200_API size_t moe_fp8_b200_exchange_bytes(int num_tokens, int world);
 MOE_FP8_B200_API int moe_fp8_b200_run_reduce_scatter(moe_fp8_b200_handle h, const moe_fp8_b200_args* args,
                                                      const moe_fp8_b200_exchange* exchange, void* stream);
 
+/* ---- the operators either side of the layer ---------------------------------------------
+ * Quantise-on-entry: bf16 activations x [num_tokens, 7168] (device) -> e4m3 q [num_tokens, 7168]
+ * and scales fp32 [56, num_tokens], i.e. exactly the hidden_states / hidden_states_scale pair
+ * that run() takes (kernel/moe_fp8.cu:2665-2666; the reference expects its caller to have done
+ * this).  1x128 blocks, scale = amax / 448 (1 for an all-zero block), payload
+ * e4m3_rn_satfinite(x / scale) -- the scheme of kernel/moe_fp8.cu:1823-1830 with a true division.
+ * Asynchronous on `stream`.  x and q must be 16-byte aligned. */
+MOE_FP8_B200_API int moe_fp8_b200_quantize_hidden(moe_fp8_b200_handle h, const void* x_bf16, int num_tokens,
+                                                  void* q_out, float* scale_out, void* stream);
+
+/* The layer without its last step (what FlashInfer's fused-MoE operator calls
+ * do_finalize = false): routing, dispatch, both GEMMs, but no weighted combine.  The views
+ * point into the handle's workspace and stay valid until the next run on this handle.
+ * Row r of the (token t, pair p) contribution is
+ *     expert_offset[pair_code[t*8+p] >> 24] + (pair_code[t*8+p] & 0xffffff),
+ * and run()'s output is  out[t,:] = bf16(sum_{p < pair_count[t]} float(y[row_p,:]) * pair_weight[t*8+p])
+ * accumulated with fp32 FMAs in pair order (kernel/moe_fp8.cu:2276-2321).  args->output may be
+ * NULL.  moe_fp8_b200_finalize applies exactly that last step to the state the latest
+ * unfinalized run left in the workspace. */
+typedef struct moe_fp8_b200_unfinalized {
+    const void* y;                 /* bf16 [row_capacity, 7168] GEMM2 rows, grouped by expert */
+    const int32_t* expert_offset;  /* [num_local_experts + 1] first row of each expert (multiples of 128) */
+    const int32_t* pair_count;     /* [T] kept (token, local expert) pairs */
+    const uint32_t* pair_code;     /* [T, 8] (local expert << 24) | slot inside the expert */
+    const float* pair_weight;      /* [T, 8] routing weight * renormalisation * routed_scaling_factor */
+    int32_t row_capacity;
+} moe_fp8_b200_unfinalized;
+
+MOE_FP8_B200_API int moe_fp8_b200_run_unfinalized(moe_fp8_b200_handle h, const moe_fp8_b200_args* args,
+                                                  moe_fp8_b200_unfinalized* views, void* stream);
+MOE_FP8_B200_API int moe_fp8_b200_finalize(moe_fp8_b200_handle h, int num_tokens, void* output, void* stream);
+
 /* Synchronises `stream` and returns MOE_FP8_B200_ERR_DEVICE if any kernel of earlier
  * runs recorded a failure in the device status word. */
 MOE_FP8_B200_API int moe_fp8_b200_check(moe_fp8_b200_handle h, void* stream);

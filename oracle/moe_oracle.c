@@ -103,6 +103,26 @@ API void oracle_e4m3_decode(const uint8_t* src, float* dst, long n) {
     init_lut();
     for (long i = 0; i < n; ++i) dst[i] = e4m3_lut[src[i]];
 }
+/* Quantise-on-entry (the producer of hidden_states / hidden_states_scale, which the reference
+ * takes already quantised, kernel/moe_fp8.cu:2665-2666): x bf16 [T, K] -> q e4m3 [T, K] and
+ * scale fp32 [K/128, T], the 1x128 scheme of kernel/moe_fp8.cu:1823-1826 (scale = amax / 448,
+ * 1 for an all-zero block) with the payload e4m3(x / scale). */
+API void oracle_quantize_rows(const uint16_t* x, long T, long K, uint8_t* q, float* scale_out) {
+    init_lut();
+    const long KB = K / BLK;
+#pragma omp parallel for schedule(static)
+    for (long t = 0; t < T; ++t) {
+        for (long kb = 0; kb < KB; ++kb) {
+            const uint16_t* src = x + t * K + kb * BLK;
+            float amax = 0.0f;
+            for (int j = 0; j < BLK; ++j) amax = fmaxf(amax, fabsf(bf16_to_f32(src[j])));
+            const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
+            for (int j = 0; j < BLK; ++j) q[t * K + kb * BLK + j] = f32_to_e4m3(bf16_to_f32(src[j]) / scale);
+            scale_out[kb * T + t] = scale;
+        }
+    }
+}
+
 API void oracle_e4m3_encode(const float* src, uint8_t* dst, long n) {
     for (long i = 0; i < n; ++i) dst[i] = f32_to_e4m3(src[i]);
 }

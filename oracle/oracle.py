@@ -73,6 +73,16 @@ def e4m3_encode(x: np.ndarray) -> np.ndarray:
     return out
 
 
+def quantize_rows(x_bf16: np.ndarray):
+    """bf16 codes [T, K] (uint16) -> (e4m3 codes [T, K] uint8, scales fp32 [K/128, T])."""
+    x = _c(x_bf16, np.uint16)
+    T, K = x.shape
+    q = np.empty((T, K), np.uint8)
+    sc = np.empty((K // 128, T), np.float32)
+    lib().oracle_quantize_rows(_p(x), C.c_long(T), C.c_long(K), _p(q), _p(sc))
+    return q, sc
+
+
 def bf16_encode(x: np.ndarray) -> np.ndarray:
     x = _c(x, np.float32)
     out = np.empty(x.shape, np.uint16)

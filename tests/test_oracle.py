@@ -134,3 +134,19 @@ def test_faithful_and_fp32_modes_agree_on_a_tiny_case(oracle, pkg):
     ref = (raw * sc).sum(-1)
     assert np.allclose(d[:, :256], ref, rtol=1e-2, atol=1e-2)
     del w1, s1, w2, s2
+
+
+def test_quantize_rows_matches_the_torch_definition(oracle, pkg):
+    """Quantise-on-entry: the C restatement against torch's fp32 statement of the same scheme
+    (1x128 blocks, scale = amax / 448 or 1, payload e4m3(x / scale)), bit for bit."""
+    from fp8_moe_dev_b200 import gen
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(19, 7168, generator=g) * (0.01 + 5 * torch.rand(19, 1, generator=g))).to(torch.bfloat16)
+    x[4, 256:384] = 0
+    x[6] = 0
+    x[7, 0] = -2.5e38
+    q, s = gen.quantize_rows_1x128(x)
+    oq, os_ = oracle.quantize_rows(np_u16(x))
+    assert np.array_equal(np_u8(q), oq)
+    assert np.array_equal(s.numpy().view(np.uint32), os_.view(np.uint32))
+    assert os_.shape == (56, 19) and float(os_[2, 4]) == 1.0 and int(oq[4, 256:384].max()) == 0
