@@ -295,6 +295,28 @@ def small_config_latencies(pkg, weights, bias_dev, reference_mod=None):
     return out
 
 
+def adjacent_ops(layer, T, dev, weights, offset):
+    """The operators either side of the layer, timed alone on the bench workload: quantise-on-entry
+    (HBM-bound: 2 B read + 1 B written per element, 4 B per 128-block) and the layer without its
+    final combine (what a caller that finalises elsewhere pays)."""
+    pk = peaks()
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    q = torch.empty(T, H, dtype=torch.float8_e4m3fn, device="cuda")
+    sc = torch.empty(H // 128, T, dtype=torch.float32, device="cuda")
+    qt = sorted(_event_times_us(lambda: layer.quantize_hidden(x, q, sc), 30)[5:])
+    q_us = qt[len(qt) // 2]
+    q_bytes = T * H * 3 + 4 * (H // 128) * T
+    gbs = q_bytes / (q_us * 1e-6) / 1e9
+    w1, s1, w2, s2 = weights
+    ut = sorted(_event_times_us(lambda: layer.run_unfinalized(*dev, w1, s1, w2, s2, offset, RSF), 12)[3:])
+    layer.check()
+    return {"quantize_hidden": {"tokens": T, "latency_us": round(q_us, 2), "bytes": q_bytes,
+                                "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm_gbs"],
+                                             "unit": "GB/s", "frac": round(gbs / pk["hbm_gbs"], 4)},
+                                "note": "working set (3 B/element) fits L2 only below ~5800 tokens"},
+            "run_unfinalized": {"tokens": T, "latency_us": round(ut[len(ut) // 2], 1)}}
+
+
 def cpu_baseline(inputs, weights, sample_tokens=64):
     """Host fp32 dequantise-and-compute baseline (the layer's definition, oracle port), timed on
     a bounded sample: the first `sample_tokens` tokens against the first 32-expert shard."""
@@ -409,6 +431,8 @@ def run_ours(args, rank, world, local):
     if rank == 0 and world == 1:
         if not args.skip_small:
             line["configs"] = small_config_latencies(pkg, weights, dev[1])
+        if not args.skip_small:
+            line["adjacent_ops"] = adjacent_ops(layer, T, dev, weights, offset)
         if not args.skip_cpu:
             line["cpu_baseline"] = cpu_baseline(inputs, weights)
     layer.close()

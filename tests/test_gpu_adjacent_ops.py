@@ -52,7 +52,7 @@ def test_quantize_hidden_roundtrip_error_bound(pkg, layer32):
     q, s = layer32.quantize_hidden(x)
     deq = q.float().view(T, H // 128, 128) * s.t().contiguous().unsqueeze(-1)
     err = (deq - x.float().view(T, H // 128, 128)).abs()
-    bound = s.t().contiguous().unsqueeze(-1) * 16.0     # half of the largest step (32) between e4m3 codes
+    bound = s.t().contiguous().unsqueeze(-1) * (16.0 * (1 + 1e-4))   # half of the largest e4m3 step (32), plus fp32 slack
     assert bool((err <= bound).all())
     amax = x.float().view(T, H // 128, 128).abs().amax(-1)
     assert torch.equal(s.t().contiguous(), amax / 448.0) or torch.allclose(s.t(), amax / 448.0, rtol=2e-7, atol=0)
@@ -88,18 +88,41 @@ def test_unfinalized_plus_finalize_equals_run(pkg, layer32, T, offset):
     code = v["pair_code"].long() & 0xFFFFFFFF
     rows = v["expert_offset"].long()[code >> 24] + (code & 0xFFFFFF)
     acc = torch.zeros(T, H, dtype=torch.float32, device="cuda")
+    mag = torch.zeros(T, H, dtype=torch.float32, device="cuda")
     for p in range(8):
         live = (cnt > p)
         r = torch.where(live, rows[:, p], torch.zeros_like(rows[:, p]))
         contrib = v["y"][r].float() * v["pair_weight"][:, p:p + 1]
         acc = torch.where(live.unsqueeze(-1), acc + contrib, acc)
+        mag = torch.where(live.unsqueeze(-1), mag + contrib.abs(), mag)
     manual = acc.to(torch.bfloat16).cpu()
-    # torch rounds the product before the add where the kernel uses a fused multiply-add:
-    # the two can differ in the last bf16 bit of a few elements
+    # torch rounds the product before the add where the kernel uses a fused multiply-add: the two
+    # can differ by fp32 rounding of the terms (which cancellation magnifies relative to the sum)
+    # and then in the last bf16 bit
     diff = (manual.float() - want.float()).abs()
-    assert bool((diff <= 2 ** -7 * want.float().abs() + 1e-30).all())
+    assert bool((diff <= 2 ** -7 * want.float().abs() + 2 ** -20 * mag.cpu() + 1e-30).all())
     assert float((manual != want).float().mean()) < 0.02
     out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
     layer32.finalize(T, out)
     layer32.check()
     assert torch.equal(out.cpu(), want)
+
+
+def test_quantize_hidden_every_bf16_maximum(pkg, oracle, layer32):
+    """Every positive finite bf16 value (subnormals included) as a block maximum: the scale
+    amax / 448 and the payloads must match the oracle's divisions bit for bit."""
+    codes = np.arange(1, 0x7F80, dtype=np.uint16)
+    T = (codes.size + 55) // 56
+    x16 = np.zeros((T, 56, 128), np.uint16)
+    flat = x16.reshape(T * 56, 128)
+    flat[:codes.size, 0] = codes
+    # companions below the maximum: the same value with a smaller exponent / other significand, negated
+    comp = torch.from_numpy(codes.view(np.int16).copy()).view(torch.bfloat16).float()
+    for j, f in enumerate((0.5, -0.7109375, 0.33203125, -0.0625, 0.9921875, -0.001953125), start=1):
+        flat[:codes.size, j * 7] = hp.np_u16((comp * f).to(torch.bfloat16))
+    x = torch.from_numpy(x16.reshape(T, 7168).view(np.int16).copy()).view(torch.bfloat16)
+    q, s = layer32.quantize_hidden(x.cuda())
+    torch.cuda.synchronize()
+    want_q, want_s = oracle.quantize_rows(hp.np_u16(x))
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), want_s.view(np.uint32))
+    assert np.array_equal(q.view(torch.uint8).cpu().numpy(), want_q)
