@@ -14,6 +14,8 @@ LIB_PATH = HERE / "libmoe_fp8_b200.so"
 OK = 0
 ERR_INVALID_ARGUMENT, ERR_CUDA, ERR_CAPACITY, ERR_DEVICE, ERR_UNSUPPORTED = -1, -2, -3, -4, -5
 OPT_REFERENCE_PRUNING, OPT_EXACT_SILU, OPT_STAGE_TIMING = 1, 2, 3
+OPT_STOP_AFTER_STAGE, OPT_DECODE_KERNEL = 4, 5
+DECODE_MAX_TOKENS = 8
 
 BUF = dict(
     expert_count=0, expert_offset=1, topk_idx=2, topk_weight=3, pair_count=4, pair_code=5, pair_weight=6,

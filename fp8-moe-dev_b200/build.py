@@ -26,7 +26,7 @@ NVCC_FLAGS = [
     "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
 ]
-CU_SOURCES = ["routing.cu", "gemm.cu", "moe_api.cu", "noalloc.cu", "quantize.cu"]
+CU_SOURCES = ["routing.cu", "gemm.cu", "moe_api.cu", "noalloc.cu", "quantize.cu", "decode.cu"]
 
 
 def _nvcc() -> str:

@@ -55,7 +55,9 @@ struct Control {
     int expert_rows[kMaxLocalExperts];   // copy of the counters of the last call (diagnostics)
     int splitk_ticket[kSplitKSlots];     // per-tile arrival counters of the split-K reduction (self-clearing)
     int push_done;                       // combine-and-push CTAs finished (ticket, self-clearing)
-    int pad2[3];
+    unsigned dec_count;                  // grid barrier of the decode kernel: arrivals (self-clearing) ...
+    unsigned dec_phase;                  // ... and generation
+    int pad2;
 };
 
 enum KernelStatus : int {
@@ -64,6 +66,7 @@ enum KernelStatus : int {
     kStatusGemm2Timeout = 102,
     kStatusRowOverflow = 103,
     kStatusExchangeTimeout = 104,
+    kStatusDecodeTimeout = 105,
 };
 
 // Cross-GPU exchange of the fused combine + reduce-scatter (expert-parallel ranks of one NVSwitch

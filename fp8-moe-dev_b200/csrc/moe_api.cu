@@ -10,6 +10,7 @@
 #include <string>
 
 #include "../../include/moe_fp8_b200.h"
+#include "decode.cuh"
 #include "layer.cuh"
 
 namespace moe {
@@ -99,6 +100,8 @@ struct moe_fp8_b200_ctx {
     int opt_exact_silu = 0;
     bool counters_dirty = false;
     int opt_stop_after = 0;   // diagnostics: enqueue only the first N stages (0 = all)
+    int opt_decode = 1;       // single-kernel path for batches of at most kDecodeMaxTokens tokens
+    int decode_ctas_per_sm = 0;
     uint8_t* base = nullptr;
     Layout layout{};
     Workspace ws{};
@@ -200,6 +203,34 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
     if (h->counters_dirty) {
         e = cudaMemsetAsync(h->ws.ctrl, 0, sizeof(Control), stream);
         h->counters_dirty = false;
+    }
+    if (h->opt_decode && h->decode_ctas_per_sm > 0 && T <= kDecodeMaxTokens && finalize && !ex &&
+        h->opt_stop_after == 0) {
+        // the whole layer as one cooperative kernel, one CTA per SM
+        DecodeArgs d;
+        d.logits = a.routing_logits;
+        d.bias = static_cast<const __nv_bfloat16*>(a.routing_bias);
+        d.hidden = static_cast<const uint8_t*>(a.hidden_states);
+        d.hscale = a.hidden_states_scale;
+        d.w1 = static_cast<const uint8_t*>(a.gemm1_weights);
+        d.s1 = a.gemm1_weights_scale;
+        d.w2 = static_cast<const uint8_t*>(a.gemm2_weights);
+        d.s2 = a.gemm2_weights_scale;
+        d.out = static_cast<__nv_bfloat16*>(a.output);
+        d.T = T;
+        d.local_expert_offset = (int)a.local_expert_offset;
+        d.num_local_experts = E;
+        d.rsf = (float)a.routed_scaling_factor;
+        d.silu_exact = h->opt_exact_silu;
+        d.pol = pol;
+        mark(0);
+        if (e == cudaSuccess) e = launch_decode_layer(d, h->ws, h->num_sms, stream);
+        for (int i = 1; i <= 6; ++i) mark(i);
+        if (e != cudaSuccess) {
+            h->counters_dirty = true;
+            return fail(h, MOE_FP8_B200_ERR_CUDA, "decode launch failed: %s", cudaGetErrorString(e));
+        }
+        return MOE_FP8_B200_OK;
     }
     mark(0);
     if (e == cudaSuccess)
@@ -312,6 +343,7 @@ int moe_fp8_b200_create(moe_fp8_b200_handle* out, int device, int max_tokens, in
     h->max_tokens = max_tokens;
     h->num_local_experts = num_local_experts;
     h->num_sms = prop.multiProcessorCount;
+    h->decode_ctas_per_sm = decode_max_ctas_per_sm();
     h->layout = make_layout(max_tokens, num_local_experts);
     e = cudaMalloc(&h->base, h->layout.total);
     if (e != cudaSuccess) {
@@ -384,6 +416,7 @@ int moe_fp8_b200_set_option(moe_fp8_b200_handle h, int option, int value)
         case MOE_FP8_B200_OPT_REFERENCE_PRUNING: h->opt_reference_pruning = value ? 1 : 0; return MOE_FP8_B200_OK;
         case MOE_FP8_B200_OPT_EXACT_SILU: h->opt_exact_silu = value ? 1 : 0; return MOE_FP8_B200_OK;
         case MOE_FP8_B200_OPT_STOP_AFTER_STAGE: h->opt_stop_after = value; return MOE_FP8_B200_OK;
+        case MOE_FP8_B200_OPT_DECODE_KERNEL: h->opt_decode = value ? 1 : 0; return MOE_FP8_B200_OK;
         case MOE_FP8_B200_OPT_STAGE_TIMING:
             h->opt_stage_timing = value ? 1 : 0;
             h->timed_runs = 0;
@@ -543,11 +576,14 @@ int moe_fp8_b200_check(moe_fp8_b200_handle h, void* stream)
     int st[2] = {0, 0};
     e = cudaMemcpy(st, &h->ws.ctrl->status, sizeof(st), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "status read: %s", cudaGetErrorString(e));
+    if (st[0] != kStatusOk) h->counters_dirty = true;   // a cut-short run may have left counters behind
     if (st[0] != kStatusOk)
         return fail(h, MOE_FP8_B200_ERR_DEVICE, "device status %d (detail %d): %s", st[0], st[1],
                     st[0] == kStatusGemm1Timeout   ? "GEMM1 gave up on a bounded wait"
                     : st[0] == kStatusGemm2Timeout ? "GEMM2 gave up on a bounded wait"
                     : st[0] == kStatusRowOverflow  ? "routed rows exceed the workspace capacity"
+                    : st[0] == kStatusExchangeTimeout ? "a peer rank's rows did not arrive within the wait limit"
+                    : st[0] == kStatusDecodeTimeout   ? "the decode kernel gave up on a grid barrier"
                                                    : "unknown");
     return MOE_FP8_B200_OK;
 }

@@ -95,6 +95,12 @@ class MoeLayer:
         if rc != _lib.OK:
             self._raise(rc)
 
+    def set_decode_kernel(self, on: bool):
+        """Batches of at most 8 tokens: one cooperative kernel (default) or the staged chain."""
+        rc = self._lib.moe_fp8_b200_set_option(self._h, _lib.OPT_DECODE_KERNEL, int(bool(on)))
+        if rc != _lib.OK:
+            self._raise(rc)
+
     STAGES = ("route_dispatch", "scan", "permute", "gemm1", "gemm2", "combine")
 
     def set_stage_timing(self, on: bool):

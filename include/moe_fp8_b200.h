@@ -75,8 +75,17 @@ enum {
     /* Diagnostics: N > 0 enqueues only the first N stages of a run (1 routing+dispatch+scan,
      * 2 +permute, 3 +GEMM1, 4 +GEMM2, 5 = all); the output is then not (fully) written.
      * 0 (default) runs the whole layer. */
-    MOE_FP8_B200_OPT_STOP_AFTER_STAGE = 4
+    MOE_FP8_B200_OPT_STOP_AFTER_STAGE = 4,
+    /* 1 (default): batches of at most MOE_FP8_B200_DECODE_MAX_TOKENS tokens run as one
+     * cooperative kernel (routing, both GEMMs on warp-level MMAs straight from global memory,
+     * combine; two bounded grid barriers) instead of the five-kernel chain.  Same results up
+     * to fp32 summation order inside GEMM1.  That kernel fills only the routing and pair
+     * tables of the workspace (EXPERT_COUNT, TOPK_*, PAIR_*); 0 selects the chain, which also
+     * leaves the packed rows, tiles and offsets behind for moe_fp8_b200_read_intermediate.
+     * Unfinalised, stage-limited and multi-GPU-exchange runs always use the chain. */
+    MOE_FP8_B200_OPT_DECODE_KERNEL = 5
 };
+#define MOE_FP8_B200_DECODE_MAX_TOKENS 8
 
 /* Intermediate buffers readable after a run (moe_fp8_b200_read_intermediate). */
 enum {
