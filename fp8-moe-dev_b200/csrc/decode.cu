@@ -11,9 +11,12 @@
 //   * phase 1 (GEMM1 + SwiGLU): a unit is 8 SwiGLU columns of one active expert = 8 linear +
 //     8 gated rows of W1, i.e. exactly one 16-row A tile of the warp-level
 //     mma.sync.m16n8k32 (e4m3 x e4m3 -> fp32), with the expert's <= 8 token rows as the 8-wide
-//     B tile.  The weights go from global memory straight into the A fragments (each weight
-//     byte is used once; shared memory would only add a hop), the 16 warps split K, promote
-//     per 128-K block with the two scales like the staged kernel, and meet in shared memory.
+//     B tile.  The weights arrive by TMA, 16 rows x 1 KB per step (two boxes of 8 rows in
+//     phase 1, one of 16 in phase 2) through a ring of four steps per half CTA; the warps
+//     split K, promote per 128-K block with the two scales like the staged kernel, and meet
+//     in shared memory.  (Per-thread loads and per-row bulk copies both left the HBM two
+//     thirds idle: the first for the loads in flight a thread can hold, the second for the
+//     rate at which one thread can issue sixteen copies per step.)
 //     In the accumulator layout a thread owns the linear and the gated value of the same
 //     (column, token), so SwiGLU needs no exchange.  v = silu(gate) * lin goes to a small
 //     fp32 scratch (the 1x128 requantisation needs whole 128-column blocks, which span units);
@@ -21,7 +24,8 @@
 //     scratch (same arithmetic as the staged epilogue), streams 16 rows of W2 per unit the
 //     same way, and writes bf16 y rows; grid barrier; phase 3 is the weighted combine.
 // The first weights of phase 2 are requested before the barrier, so the barrier and the
-// requantisation hide behind their latency.  The two grid barriers are bounded waits.
+// requantisation hide behind their latency.  Every wait (mbarriers, grid barriers) is bounded.
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
@@ -38,15 +42,25 @@ namespace {
 
 constexpr int kDecWarps = 16;
 constexpr int kDecThreads = kDecWarps * 32;
-constexpr int kDecMaxActive = kDecodeMaxTokens * kTopK;   // 64 (token, expert) pairs at most
-constexpr int kHidStride = kHidden + 64;   // row strides that spread the eight token rows over the banks
+constexpr int kHalfWarps = 8;                           // the CTA works as two halves of 8 warps
+constexpr int kHalfThreads = kHalfWarps * 32;
+constexpr int kDecMaxActive = kDecodeMaxTokens * kTopK; // 64 (token, expert) pairs at most
+constexpr int kHidStride = kHidden + 64;                // row strides that spread rows over the banks
 constexpr int kA2Stride = kInter + 64;
 constexpr int kG1Cols = 8;                              // SwiGLU columns of a phase-1 unit
 constexpr int kG1Units = kInter / kG1Cols;              // 256 per expert
 constexpr int kG2Cols = 16;                             // output columns of a phase-2 unit
 constexpr int kG2Units = kHidden / kG2Cols;             // 448 per expert
-constexpr int kG1Steps = (kHiddenBlocks + kDecWarps - 1) / kDecWarps;   // K blocks per warp (4, last may be absent)
-static_assert(kInterBlocks == kDecWarps, "phase 2 gives each warp one K block");
+// A step = 16 weight rows x 1 KB of K (8 K blocks, one per warp of the half).
+constexpr int kStepRows = 16;
+constexpr int kStepK = kHalfWarps * kBlock;             // 1024 bytes of every row
+constexpr int kStepStride = kStepK;                     // rows of a step lie densely, as TMA writes them
+constexpr int kStepBytes = kStepRows * kStepK;          // 16 KB arrive per step
+constexpr int kG1Steps = kHidden / kStepK;              // 7 per phase-1 unit
+constexpr int kG2Steps = kInter / kStepK;               // 2 per phase-2 unit
+constexpr int kRing = 4;                                // steps in flight per half
+static_assert(kHidden % kStepK == 0 && kInter % kStepK == 0, "K splits into whole steps");
+static_assert(2 * kDecodeMaxTokens * kA2Stride <= kDecodeMaxTokens * kHidStride, "phase 2 rows reuse the hidden-row area");
 
 struct DecodeShared {
     int n_active, n_rows, abort, pad;
@@ -58,11 +72,17 @@ struct DecodeShared {
     int act_expert[kDecMaxActive], act_m[kDecMaxActive], act_row0[kDecMaxActive];
     int act_tok[kDecMaxActive][kDecodeMaxTokens];
     int expert_slot[kMaxLocalExperts];
-    float scale[kDecodeMaxTokens][kHiddenBlocks];   // phase 1: [slot][kb] hidden scales; phase 2: [slot][kb < 16]
-    float w2_scale[2][kInterBlocks];
-    alignas(16) float red[2][kDecWarps][128];
-    alignas(16) uint8_t stage[kDecodeMaxTokens * kHidStride];
+    float hid_scale[kDecodeMaxTokens][kHiddenBlocks];      // [token][kb]
+    float a2_scale[2][kDecodeMaxTokens][kInterBlocks];     // per half: [slot][kb] of the requantised rows
+    alignas(8) uint64_t full_bar[2][kRing];
+    alignas(8) uint64_t empty_bar[2][kRing];
+    alignas(8) uint64_t hid_bar;
+    alignas(16) float red[2][2][kHalfWarps][128];          // per half, by unit parity: the warps' partial sums
+    // phase 1: the hidden rows of all tokens; phase 2: each half's requantised rows of its expert
+    alignas(128) uint8_t rows[kDecodeMaxTokens * kHidStride];
+    alignas(128) uint8_t wring[2][kRing][kStepRows * kStepStride];
 };
+static_assert(sizeof(DecodeShared) <= 227 * 1024, "decode kernel shared memory");
 
 __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
@@ -71,17 +91,13 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const unsigned* p) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_release_gpu(unsigned* p, uint32_t v) {
-    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 
-// Weights are read exactly once: streaming loads that do not linger in L1.
-__device__ __forceinline__ uint4 ld_stream(const uint8_t* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
+// Untiled bulk copy global -> shared memory of this CTA, completion counted on an mbarrier.
+// Both addresses and the size are multiples of 16 bytes.  No multicast.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
 }
 
 __device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -93,39 +109,44 @@ __device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// One 128-K block: rows r / r + 8 of the A tile in lo[2] / hi[2] (16 B at byte 16c and at byte
-// 64 + 16c of the block, c = lane % 4), the token rows' same bytes in b[2].  Which 4 bytes feed
-// which k index of the MMA is the same for A and B, and a dot product does not care about more.
-__device__ __forceinline__ void mma_block(float (&c)[4], const uint4 (&lo)[2], const uint4 (&hi)[2], const uint4 (&b)[2]) {
+// One 128-K block of the warp-level MMA tile: `arow` points at this K block in weight row r of
+// the staged step (row r + 8 lies 8 strides further), `brow` at the same K block of token slot
+// r's row; r = lane / 4, c = lane % 4.  A thread takes bytes [16c, 16c+16) and [64+16c, 64+16c+16)
+// of the block from each; which 4 bytes feed which k index of the MMA is the same for A and B,
+// and a dot product does not care about more.  (The choice cannot depend on the row: a product
+// pairs the A bytes of one lane group with the B bytes of another.  The weight rows are 1 KB apart,
+// so rows r and r + 1, which share a shared-memory access phase, collide two-way; that is cheap.)
+__device__ __forceinline__ void mma_block(float (&acc)[4], const uint8_t* arow, const uint8_t* brow) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        mma_e4m3(c, lo[h].x, hi[h].x, lo[h].y, hi[h].y, b[h].x, b[h].y);
-        mma_e4m3(c, lo[h].z, hi[h].z, lo[h].w, hi[h].w, b[h].z, b[h].w);
+        const int off = 64 * h;
+        const uint4 lo = *reinterpret_cast<const uint4*>(arow + off);
+        const uint4 hi = *reinterpret_cast<const uint4*>(arow + 8 * kStepStride + off);
+        const uint4 b = *reinterpret_cast<const uint4*>(brow + off);
+        mma_e4m3(acc, lo.x, hi.x, lo.y, hi.y, b.x, b.y);
+        mma_e4m3(acc, lo.z, hi.z, lo.w, hi.w, b.z, b.w);
     }
 }
 
-// All CTAs of the (cooperative, co-resident) grid meet here.  Bounded: a CTA that waits longer
+// All CTAs of the (cooperative, co-resident) grid meet here: one release-add on `counter`, then
+// acquire-polls until all have arrived.  The kernel has two barriers on two counters; CTA 0 clears
+// the second one before it arrives at the first (nobody can reach the second barrier earlier) and
+// the first one after it has passed the second (everybody has left the first by then), so a launch
+// finds and leaves the state it needs without a generation word.  Bounded: a CTA that waits longer
 // than the limit records the failure and returns false; its peers run into the same limit.
-__device__ __forceinline__ bool grid_barrier(Control* ctrl, DecodeShared* sh)
+__device__ __forceinline__ bool grid_barrier(unsigned* counter, Control* ctrl, DecodeShared* sh)
 {
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
-        const uint32_t phase = ld_acquire_gpu(&ctrl->dec_phase);
-        const unsigned ticket = atomicAdd(&ctrl->dec_count, 1u);
-        if (ticket == gridDim.x - 1) {
-            ctrl->dec_count = 0;
-            __threadfence();
-            st_release_gpu(&ctrl->dec_phase, phase + 1);
-        } else {
-            const uint64_t t0 = global_timer_ns();
-            uint32_t it = 0;
-            while (ld_acquire_gpu(&ctrl->dec_phase) == phase) {
-                if ((++it & 0x3fu) == 0u && global_timer_ns() - t0 > kWaitLimitNs) {
-                    atomicCAS(&ctrl->status, kStatusOk, kStatusDecodeTimeout);
-                    sh->abort = 1;
-                    break;
-                }
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
+        const uint64_t t0 = global_timer_ns();
+        uint32_t it = 0;
+        while (ld_acquire_gpu(counter) < gridDim.x) {
+            if ((++it & 0x3fu) == 0u && global_timer_ns() - t0 > kWaitLimitNs) {
+                atomicCAS(&ctrl->status, kStatusOk, kStatusDecodeTimeout);
+                sh->abort = 1;
+                break;
             }
         }
     }
@@ -133,17 +154,46 @@ __device__ __forceinline__ bool grid_barrier(Control* ctrl, DecodeShared* sh)
     return sh->abort == 0;
 }
 
-__global__ void __launch_bounds__(kDecThreads, 1) decode_layer_kernel(DecodeArgs a, Workspace ws)
+__global__ void __launch_bounds__(kDecThreads, 1) decode_layer_kernel(
+    DecodeArgs a, const __grid_constant__ CUtensorMap tmap_w1, const __grid_constant__ CUtensorMap tmap_w2, Workspace ws)
 {
-    extern __shared__ __align__(16) uint8_t smem_raw[];
+    extern __shared__ __align__(128) uint8_t smem_raw[];
     DecodeShared* sh = reinterpret_cast<DecodeShared*>(smem_raw);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r = lane >> 2, c = lane & 3;   // MMA fragment coordinates
     const int T = a.T, E = a.num_local_experts;
+    const bool clocked = blockIdx.x == 0 && tid == 0;
+    auto stamp = [&](int i) { if (clocked) ws.ctrl->dec_time[i] = global_timer_ns(); };
+    stamp(0);
+    volatile int* abort_flag = &sh->abort;
+
+    // The tokens' hidden rows start moving before anything else: nothing depends on routing here.
+    if (tid == 0) {
+        sh->abort = 0;
+        prefetch_tmap(&tmap_w1);
+        prefetch_tmap(&tmap_w2);
+        const uint32_t hb = smem_u32(&sh->hid_bar);
+        mbar_init(hb, 1);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int j = 0; j < kRing; ++j) {
+                mbar_init(smem_u32(&sh->full_bar[h][j]), 1);
+                mbar_init(smem_u32(&sh->empty_bar[h][j]), kHalfWarps);
+            }
+        fence_mbar_init();
+        mbar_expect_tx(hb, (uint32_t)T * kHidden);
+        for (int t = 0; t < T; ++t)
+            bulk_g2s(smem_u32(sh->rows + t * kHidStride), a.hidden + (size_t)t * kHidden, kHidden, hb);
+        if (blockIdx.x == 0) ws.ctrl->dec_phase = 0;   // second barrier's counter, see grid_barrier
+    }
+    for (int q = tid; q < T * kHiddenBlocks; q += kDecThreads) {
+        const int t = q % T, kb = q / T;
+        sh->hid_scale[t][kb] = __ldg(a.hscale + q);   // [56, T] -> [token][kb]
+    }
 
     // ------------------------------------------------------------------ routing (every CTA)
     if (tid < kMaxLocalExperts) sh->expert_slot[tid] = -1;
-    if (tid == 0) sh->abort = 0;
     if (warp < T) {
         int idx[kTopK];
         float wn[kTopK];
@@ -219,165 +269,243 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_layer_kernel(DecodeArgs
     }
     __syncthreads();
     const int n_active = sh->n_active;
+    stamp(1);
     float* act = ws.splitk_partial;   // [rows, 2048] fp32 SwiGLU output (the split-K scratch is idle on this path)
+
+    // The 16 warps work as two independent halves of 8 (named barriers 1 and 2): a half is one
+    // worker with its own unit range, weight ring and reduction buffer, so an SM always has two
+    // units in flight and the unit ranges are twice as fine.  Thread 0 of a half is its producer:
+    // it issues the bulk copies of a step (16 rows x 1 KB) as soon as the ring slot is free -- of
+    // the next unit and, before the grid barrier, of the next phase as well.  Warp hw of the half
+    // consumes K block hw of every step.
+    const int half = warp >> 3, hw = warp & (kHalfWarps - 1), htid = tid & (kHalfThreads - 1);
+    const int workers = (int)gridDim.x * 2, wk = (int)blockIdx.x * 2 + half;
+    const int bar_id = 1 + half;
+    const bool producer = htid == 0;
+    const int units1 = n_active * kG1Units, units2 = n_active * kG2Units;
+    const int u1_begin = (int)((long long)units1 * wk / workers), u1_end = (int)((long long)units1 * (wk + 1) / workers);
+    const int u2_begin = (int)((long long)units2 * wk / workers), u2_end = (int)((long long)units2 * (wk + 1) / workers);
+    const int S1 = (u1_end - u1_begin) * kG1Steps, S2 = (u2_end - u2_begin) * kG2Steps;
+    int issued = 0;     // steps issued so far by this half's producer (both phases)
+    int consumed = 0;   // steps consumed so far by this half
+    bool ok = true;
+
+    // producer only: step s of phase 1 (s < S1) or phase 2 (s - S1)
+    auto issue = [&](int s) -> bool {
+        const int slot = issued & (kRing - 1);
+        if (issued >= kRing &&
+            !mbar_wait(smem_u32(&sh->empty_bar[half][slot]), (uint32_t)((issued / kRing - 1) & 1), abort_flag))
+            return false;
+        const uint32_t bar = smem_u32(&sh->full_bar[half][slot]);
+        const uint32_t dst = smem_u32(&sh->wring[half][slot][0]);
+        mbar_expect_tx(bar, kStepBytes);
+        if (s < S1) {
+            const int u = u1_begin + s / kG1Steps, i = s % kG1Steps;
+            const int row = sh->act_expert[u / kG1Units] * kGemm1Out + (u % kG1Units) * kG1Cols;
+            tma_load_2d(dst, &tmap_w1, bar, i * (kStepK / 4), row);                              // 8 linear rows
+            tma_load_2d(dst + 8 * kStepStride, &tmap_w1, bar, i * (kStepK / 4), row + kInter);   // 8 gated rows
+        } else {
+            const int s2 = s - S1;
+            const int u = u2_begin + s2 / kG2Steps, i = s2 % kG2Steps;
+            tma_load_2d(dst, &tmap_w2, bar, i * (kStepK / 4), sh->act_expert[u / kG2Units] * kHidden + (u % kG2Units) * kG2Cols);
+        }
+        ++issued;
+        return true;
+    };
+    // everybody: wait for the next step's bytes; returns the ring slot
+    auto acquire = [&]() -> const uint8_t* {
+        const int slot = consumed & (kRing - 1);
+        if (!mbar_wait(smem_u32(&sh->full_bar[half][slot]), (uint32_t)((consumed / kRing) & 1), abort_flag)) ok = false;
+        return &sh->wring[half][slot][0];
+    };
+    auto release = [&]() {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh->empty_bar[half][consumed & (kRing - 1)]));
+        ++consumed;
+    };
+
+    if (producer) {
+        for (int s = 0; s < kRing && s < S1 + S2 && ok; ++s)
+            if (s < S1 || S1 == 0) ok = issue(s);   // phase-2 steps are not issued ahead of phase 1 here, see below
+    }
+    // the hidden rows must have landed before the first MMA
+    if (!mbar_wait(smem_u32(&sh->hid_bar), 0u, abort_flag)) ok = false;
 
     // ------------------------------------------------------------------ phase 1: GEMM1 + SwiGLU
     {
-        const int units = n_active * kG1Units;
-        const int u_begin = (int)((long long)units * blockIdx.x / gridDim.x);
-        const int u_end = (int)((long long)units * (blockIdx.x + 1) / gridDim.x);
-        uint4 wl[kG1Steps][2], wg[kG1Steps][2];
-        auto load_unit = [&](int u, int i) {
-            const int kb = warp + kDecWarps * i;
-            if (kb < kHiddenBlocks) {
-                const int e = sh->act_expert[u / kG1Units];
-                const int n = (u % kG1Units) * kG1Cols + r;
-                const uint8_t* lin = a.w1 + ((size_t)e * kGemm1Out + n) * kHidden + kb * kBlock + 16 * c;
-                const uint8_t* gat = lin + (size_t)kInter * kHidden;
-                wl[i][0] = ld_stream(lin);
-                wl[i][1] = ld_stream(lin + 64);
-                wg[i][0] = ld_stream(gat);
-                wg[i][1] = ld_stream(gat + 64);
+        int ai = 0, g = 0, m = 0;
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        // The weight scales of a unit's K blocks sit in lanes 0..13 of the warp that uses them (7
+        // linear, 7 gated), fetched one unit ahead so that no step waits for them.
+        auto unit_scales = [&](int u) -> float {
+            float v = 0.0f;
+            if (u < u1_end && lane < 2 * kG1Steps) {
+                const int e = sh->act_expert[u / kG1Units], gg = u % kG1Units;
+                const int blk = gg / (kBlock / kG1Cols) + (lane >= kG1Steps ? kInter / kBlock : 0);
+                const int kb = hw + kHalfWarps * (lane % kG1Steps);
+                v = __ldg(a.s1 + ((size_t)e * (kGemm1Out / kBlock) + blk) * kHiddenBlocks + kb);
             }
+            return v;
         };
-        if (u_begin < u_end) {
-#pragma unroll
-            for (int i = 0; i < kG1Steps; ++i) load_unit(u_begin, i);
-        }
-        int staged = -1;
-        for (int u = u_begin; u < u_end; ++u) {
-            const int ai = u / kG1Units, g = u % kG1Units;
-            const int e = sh->act_expert[ai], m = sh->act_m[ai];
-            if (ai != staged) {
-                __syncthreads();   // every warp is done with the previous expert's rows
-                for (int i = tid; i < m * (kHidden / 16); i += kDecThreads) {
-                    const int slot = i / (kHidden / 16), off = i % (kHidden / 16);
-                    const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.hidden + (size_t)sh->act_tok[ai][slot] * kHidden) + off);
-                    *reinterpret_cast<uint4*>(sh->stage + slot * kHidStride + off * 16) = v;
-                }
-                for (int i = tid; i < m * kHiddenBlocks; i += kDecThreads) {
-                    const int slot = i / kHiddenBlocks, kb = i % kHiddenBlocks;
-                    sh->scale[slot][kb] = __ldg(a.hscale + (size_t)kb * T + sh->act_tok[ai][slot]);
-                }
-                __syncthreads();
-                staged = ai;
+        float sc_cur = 0.0f, sc_next = unit_scales(u1_begin);
+        for (int s = 0; s < S1 && ok; ++s) {
+            const int u = u1_begin + s / kG1Steps, i = s % kG1Steps;
+            if (i == 0) {   // a new unit
+                ai = u / kG1Units;
+                g = u % kG1Units;
+                m = sh->act_m[ai];
+                sc_cur = sc_next;
+                sc_next = unit_scales(u + 1);
+                acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
             }
-            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            const float* s1l = a.s1 + ((size_t)e * (kGemm1Out / kBlock) + g / (kBlock / kG1Cols)) * kHiddenBlocks;
-            const float* s1g = s1l + (size_t)(kInter / kBlock) * kHiddenBlocks;
-#pragma unroll
-            for (int i = 0; i < kG1Steps; ++i) {
-                const int kb = warp + kDecWarps * i;
-                if (kb < kHiddenBlocks) {
-                    const uint8_t* brow = sh->stage + r * kHidStride + kb * kBlock + 16 * c;
-                    uint4 b[2];
-                    b[0] = *reinterpret_cast<const uint4*>(brow);
-                    b[1] = *reinterpret_cast<const uint4*>(brow + 64);
-                    float raw[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    mma_block(raw, wl[i], wg[i], b);
-                    const float sl = __ldg(s1l + kb), sg = __ldg(s1g + kb);
-                    const float sa0 = sh->scale[2 * c][kb], sa1 = sh->scale[2 * c + 1][kb];
-                    acc[0] = fmaf(raw[0], sa0 * sl, acc[0]);
-                    acc[1] = fmaf(raw[1], sa1 * sl, acc[1]);
-                    acc[2] = fmaf(raw[2], sa0 * sg, acc[2]);
-                    acc[3] = fmaf(raw[3], sa1 * sg, acc[3]);
-                }
-                if (u + 1 < u_end) load_unit(u + 1, i);   // the next unit's bytes fly during the reduction
+            const int kb = hw + kHalfWarps * i;
+            const float sl = __shfl_sync(0xffffffffu, sc_cur, i), sg = __shfl_sync(0xffffffffu, sc_cur, kG1Steps + i);
+            const int tok = sh->act_tok[ai][r < m ? r : 0];
+            const uint8_t* wst = acquire();
+            if (!ok) break;
+            float raw[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            mma_block(raw, wst + r * kStepStride + hw * kBlock + 16 * c, sh->rows + tok * kHidStride + kb * kBlock + 16 * c);
+            release();
+            if (producer && s + kRing < S1 + S2) {
+                // phase-2 steps may be issued from here on: their slots were phase-1 slots that are now free
+                if (!issue(s + kRing)) { ok = false; }
             }
-            float* red = &sh->red[u & 1][0][0];
-            *reinterpret_cast<float4*>(red + warp * 128 + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-            __syncthreads();
-            if (tid < 64) {
-                const int l = tid & 31, j = tid >> 5;
-                float lin = 0.0f, gate = 0.0f;
+            const int t0 = sh->act_tok[ai][2 * c < m ? 2 * c : 0], t1 = sh->act_tok[ai][2 * c + 1 < m ? 2 * c + 1 : 0];
+            const float sa0 = sh->hid_scale[t0][kb], sa1 = sh->hid_scale[t1][kb];
+            acc[0] = fmaf(raw[0], sa0 * sl, acc[0]);
+            acc[1] = fmaf(raw[1], sa1 * sl, acc[1]);
+            acc[2] = fmaf(raw[2], sa0 * sg, acc[2]);
+            acc[3] = fmaf(raw[3], sa1 * sg, acc[3]);
+            if (i == kG1Steps - 1) {   // the unit is complete: add the eight warps' partial sums
+                float* red = &sh->red[half][u & 1][0][0];
+                *reinterpret_cast<float4*>(red + hw * 128 + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                named_bar_sync(bar_id, kHalfThreads);
+                if (htid < 64) {
+                    const int l = htid & 31, jj = htid >> 5;
+                    float lin = 0.0f, gate = 0.0f;
 #pragma unroll
-                for (int w = 0; w < kDecWarps; ++w) {
-                    lin += red[w * 128 + l * 4 + j];
-                    gate += red[w * 128 + l * 4 + 2 + j];
-                }
-                const int slot = 2 * (l & 3) + j, col = g * kG1Cols + (l >> 2);
-                if (slot < m) {
-                    const float x1 = round_bf16(lin), x2 = round_bf16(gate);
-                    const float silu = a.silu_exact ? x2 / (1.0f + __expf(-x2))
-                                                    : x2 * (0.5f * (x2 * rsqrtf(fmaf(x2, x2, 4.0f)) + 1.0f));
-                    act[(size_t)(sh->act_row0[ai] + slot) * kInter + col] = silu * x1;
+                    for (int w = 0; w < kHalfWarps; ++w) {
+                        lin += red[w * 128 + l * 4 + jj];
+                        gate += red[w * 128 + l * 4 + 2 + jj];
+                    }
+                    const int slot = 2 * (l & 3) + jj, col = g * kG1Cols + (l >> 2);
+                    if (slot < m) {
+                        const float x1 = round_bf16(lin), x2 = round_bf16(gate);
+                        const float silu = a.silu_exact ? x2 / (1.0f + __expf(-x2))
+                                                        : x2 * (0.5f * (x2 * rsqrtf(fmaf(x2, x2, 4.0f)) + 1.0f));
+                        act[(size_t)(sh->act_row0[ai] + slot) * kInter + col] = silu * x1;
+                    }
                 }
             }
         }
     }
+    if (producer && S1 == 0 && ok) {   // nothing to do in phase 1: start phase 2's first steps now
+        for (int s = issued; s < kRing && s < S2 && ok; ++s) ok = issue(s);
+    }
+
+    // A half that gave up on a wait still lets its bulk copies land before the CTA may exit.
+    auto give_up = [&]() {
+        atomicCAS(&ws.ctrl->status, kStatusOk, kStatusDecodeTimeout);
+        sh->abort = 1;
+        if (producer) {
+            for (int g = consumed; g < issued; ++g) {
+                const uint32_t bar = smem_u32(&sh->full_bar[half][g & (kRing - 1)]);
+                const uint64_t t0 = global_timer_ns();
+                while (!mbar_try_wait(bar, (uint32_t)((g / kRing) & 1)) && global_timer_ns() - t0 < kWaitLimitNs) {}
+            }
+        }
+    };
 
     // ------------------------------------------------------------------ phase 2: requant + GEMM2
+    stamp(2);
+    if (!ok) give_up();
+    if (!grid_barrier(&ws.ctrl->dec_count, ws.ctrl, sh)) {
+        if (ok) give_up();
+        return;
+    }
+    stamp(3);
     {
-        const int units = n_active * kG2Units;
-        const int u_begin = (int)((long long)units * blockIdx.x / gridDim.x);
-        const int u_end = (int)((long long)units * (blockIdx.x + 1) / gridDim.x);
-        uint4 wl[2], wg[2];
-        auto load_unit = [&](int u) {
-            const int e = sh->act_expert[u / kG2Units];
-            const int hrow = (u % kG2Units) * kG2Cols + r;
-            const uint8_t* p = a.w2 + ((size_t)e * kHidden + hrow) * kInter + warp * kBlock + 16 * c;
-            wl[0] = ld_stream(p);
-            wl[1] = ld_stream(p + 64);
-            wg[0] = ld_stream(p + (size_t)8 * kInter);
-            wg[1] = ld_stream(p + (size_t)8 * kInter + 64);
+        uint8_t* a2rows = sh->rows + half * (kDecodeMaxTokens * kA2Stride);
+        float(*a2s)[kInterBlocks] = sh->a2_scale[half];
+        int staged = -1, ai = 0, hg = 0, m = 0;
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        auto unit_scales2 = [&](int u) -> float {   // lanes 0 and 1: this warp's two K blocks, one unit ahead
+            float v = 0.0f;
+            if (u < u2_end && lane < kG2Steps) {
+                const int e = sh->act_expert[u / kG2Units], hh = u % kG2Units;
+                v = __ldg(a.s2 + ((size_t)e * kHiddenBlocks + hh / (kBlock / kG2Cols)) * kInterBlocks + hw + kHalfWarps * lane);
+            }
+            return v;
         };
-        if (u_begin < u_end) load_unit(u_begin);   // in flight across the barrier
-        __threadfence();
-        if (!grid_barrier(ws.ctrl, sh)) return;
-        int staged = -1;
-        for (int u = u_begin; u < u_end; ++u) {
-            const int ai = u / kG2Units, hg = u % kG2Units;
-            const int e = sh->act_expert[ai], m = sh->act_m[ai];
-            if (ai != staged) {
-                __syncthreads();
-                // 1x128 requantisation of the expert's rows, as in the staged GEMM1 epilogue:
-                // scale = amax / 448 (1 if the block is zero), payload e4m3(v * (1 / scale))
-                for (int item = warp; item < m * kInterBlocks; item += kDecWarps) {
-                    const int slot = item / kInterBlocks, ib = item % kInterBlocks;
-                    const float4 v = __ldcg(reinterpret_cast<const float4*>(
-                        act + (size_t)(sh->act_row0[ai] + slot) * kInter + ib * kBlock) + lane);
-                    float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        float sc_cur = 0.0f, sc_next = unit_scales2(u2_begin);
+        for (int s = 0; s < S2 && ok; ++s) {
+            const int u = u2_begin + s / kG2Steps, i = s % kG2Steps;
+            if (i == 0) {
+                ai = u / kG2Units;
+                hg = u % kG2Units;
+                m = sh->act_m[ai];
+                if (ai != staged) {
+                    named_bar_sync(bar_id, kHalfThreads);   // the half is done with the previous expert's rows
+                    // 1x128 requantisation of the expert's rows, as in the staged GEMM1 epilogue:
+                    // scale = amax / 448 (1 if the block is zero), payload e4m3(v * (1 / scale))
+                    for (int item = hw; item < m * kInterBlocks; item += kHalfWarps) {
+                        const int slot = item / kInterBlocks, ib = item % kInterBlocks;
+                        const float4 v = __ldcg(reinterpret_cast<const float4*>(
+                            act + (size_t)(sh->act_row0[ai] + slot) * kInter + ib * kBlock) + lane);
+                        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
 #pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-                    const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
-                    const float inv = 1.0f / scale;
-                    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v.x * inv, v.y * inv), __NV_SATFINITE, __NV_E4M3);
-                    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v.z * inv, v.w * inv), __NV_SATFINITE, __NV_E4M3);
-                    *reinterpret_cast<uint32_t*>(sh->stage + slot * kA2Stride + ib * kBlock + lane * 4) = lo | (hi << 16);
-                    if (lane == 0) sh->scale[slot][ib] = scale;
+                        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                        const float sc = amax > 0.0f ? amax / 448.0f : 1.0f;
+                        const float inv = 1.0f / sc;
+                        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v.x * inv, v.y * inv), __NV_SATFINITE, __NV_E4M3);
+                        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v.z * inv, v.w * inv), __NV_SATFINITE, __NV_E4M3);
+                        *reinterpret_cast<uint32_t*>(a2rows + slot * kA2Stride + ib * kBlock + lane * 4) = lo | (hi << 16);
+                        if (lane == 0) a2s[slot][ib] = sc;
+                    }
+                    named_bar_sync(bar_id, kHalfThreads);
+                    staged = ai;
                 }
-                staged = ai;
+                sc_cur = sc_next;
+                sc_next = unit_scales2(u + 1);
+                acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
             }
-            if (tid < kInterBlocks)
-                sh->w2_scale[u & 1][tid] = __ldg(a.s2 + ((size_t)e * kHiddenBlocks + hg / (kBlock / kG2Cols)) * kInterBlocks + tid);
-            __syncthreads();   // rows, scales and the previous unit's reduction are settled
-            {
-                const uint8_t* brow = sh->stage + r * kA2Stride + warp * kBlock + 16 * c;
-                uint4 b[2];
-                b[0] = *reinterpret_cast<const uint4*>(brow);
-                b[1] = *reinterpret_cast<const uint4*>(brow + 64);
-                float raw[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                mma_block(raw, wl, wg, b);
-                *reinterpret_cast<float4*>(&sh->red[0][warp][lane * 4]) = make_float4(raw[0], raw[1], raw[2], raw[3]);
+            const int kb = hw + kHalfWarps * i;
+            const float sw = __shfl_sync(0xffffffffu, sc_cur, i);
+            const uint8_t* wst = acquire();
+            if (!ok) break;
+            float raw[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            mma_block(raw, wst + r * kStepStride + hw * kBlock + 16 * c, a2rows + r * kA2Stride + kb * kBlock + 16 * c);
+            release();
+            if (producer && s + kRing < S2) {
+                if (!issue(S1 + s + kRing)) { ok = false; }
             }
-            if (u + 1 < u_end) load_unit(u + 1);
-            __syncthreads();
-            if (tid < 128) {
-                // the K blocks are promoted in order with one FMA each, like the staged kernel
-                const int l = tid >> 2, i = tid & 3;
-                const int slot = 2 * (l & 3) + (i & 1), hrow = hg * kG2Cols + (l >> 2) + 8 * (i >> 1);
-                float acc = 0.0f;
+            const float sa0 = a2s[2 * c][kb] * sw, sa1 = a2s[2 * c + 1][kb] * sw;
+            acc[0] = fmaf(raw[0], sa0, acc[0]);
+            acc[1] = fmaf(raw[1], sa1, acc[1]);
+            acc[2] = fmaf(raw[2], sa0, acc[2]);
+            acc[3] = fmaf(raw[3], sa1, acc[3]);
+            if (i == kG2Steps - 1) {
+                float* red = &sh->red[half][u & 1][0][0];
+                *reinterpret_cast<float4*>(red + hw * 128 + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                named_bar_sync(bar_id, kHalfThreads);
+                if (htid < 128) {
+                    const int l = htid >> 2, q = htid & 3;
+                    const int slot = 2 * (l & 3) + (q & 1), hrow = hg * kG2Cols + (l >> 2) + 8 * (q >> 1);
+                    float sum = 0.0f;
 #pragma unroll
-                for (int kb = 0; kb < kInterBlocks; ++kb)
-                    acc = fmaf(sh->red[0][kb][l * 4 + i], sh->scale[slot][kb] * sh->w2_scale[u & 1][kb], acc);
-                if (slot < m) ws.y[(size_t)(sh->act_row0[ai] + slot) * kHidden + hrow] = __float2bfloat16_rn(acc);
+                    for (int w = 0; w < kHalfWarps; ++w) sum += red[w * 128 + l * 4 + q];
+                    if (slot < m) ws.y[(size_t)(sh->act_row0[ai] + slot) * kHidden + hrow] = __float2bfloat16_rn(sum);
+                }
             }
         }
     }
+    if (!ok) give_up();
 
     // ------------------------------------------------------------------ phase 3: weighted combine
-    __threadfence();
-    if (!grid_barrier(ws.ctrl, sh)) return;
+    stamp(4);
+    if (!grid_barrier(&ws.ctrl->dec_phase, ws.ctrl, sh)) return;
+    if (blockIdx.x == 0 && tid == 0) ws.ctrl->dec_count = 0;   // everybody has left the first barrier
+    stamp(5);
     {
         constexpr int kChunks = kHidden / 8;   // 16-byte chunks of a row
         for (int i = blockIdx.x * kDecThreads + tid; i < T * kChunks; i += gridDim.x * kDecThreads) {
@@ -404,6 +532,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_layer_kernel(DecodeArgs
             reinterpret_cast<uint4*>(a.out + (size_t)t * kHidden)[ch] = packed;
         }
     }
+    stamp(6);
 }
 
 }  // namespace
@@ -424,7 +553,8 @@ int decode_max_ctas_per_sm()
     return n;
 }
 
-cudaError_t launch_decode_layer(const DecodeArgs& args, const Workspace& ws, int num_ctas, cudaStream_t stream)
+cudaError_t launch_decode_layer(const DecodeArgs& args, const void* tmap_w1, const void* tmap_w2, const Workspace& ws,
+                                int num_ctas, cudaStream_t stream)
 {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(num_ctas);
@@ -436,7 +566,8 @@ cudaError_t launch_decode_layer(const DecodeArgs& args, const Workspace& ws, int
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, decode_layer_kernel, args, ws);
+    return cudaLaunchKernelEx(&cfg, decode_layer_kernel, args, *static_cast<const CUtensorMap*>(tmap_w1),
+                              *static_cast<const CUtensorMap*>(tmap_w2), ws);
 }
 
 }  // namespace moe

@@ -29,6 +29,8 @@ struct DecodeArgs {
 // Prepares the decode kernel on the current device (shared-memory opt-in) and returns how many
 // of its CTAs fit on one SM (0: it cannot run here).  Call once per device before launching.
 int decode_max_ctas_per_sm();
-cudaError_t launch_decode_layer(const DecodeArgs& args, const Workspace& ws, int num_ctas, cudaStream_t stream);
+// tmap_w1 / tmap_w2: tensor maps of the weights as rows of 32-bit words with 1 KB x 8 / 1 KB x 16 boxes.
+cudaError_t launch_decode_layer(const DecodeArgs& args, const void* tmap_w1, const void* tmap_w2, const Workspace& ws,
+                                int num_ctas, cudaStream_t stream);
 
 }  // namespace moe

@@ -572,6 +572,23 @@ int encode_kmajor_u8_map(void* out_map, const void* base, uint64_t k_bytes, uint
     return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+// rows x row_bytes viewed as 32-bit words, no swizzle; box = 1 KB of a row x box_rows rows
+// (the decode kernel's weight steps).
+int encode_rows_1k_map(void* out_map, const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows)
+{
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return -1;
+    CUtensorMap* m = static_cast<CUtensorMap*>(out_map);
+    const cuuint64_t dims[2] = {row_bytes / 4, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {256, box_rows};
+    const cuuint32_t es[2] = {1, 1};
+    const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, es,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
 size_t tensor_map_bytes() { return sizeof(CUtensorMap); }
 
 cudaError_t configure_gemm_kernels()

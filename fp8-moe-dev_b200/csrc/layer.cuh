@@ -55,9 +55,10 @@ struct Control {
     int expert_rows[kMaxLocalExperts];   // copy of the counters of the last call (diagnostics)
     int splitk_ticket[kSplitKSlots];     // per-tile arrival counters of the split-K reduction (self-clearing)
     int push_done;                       // combine-and-push CTAs finished (ticket, self-clearing)
-    unsigned dec_count;                  // grid barrier of the decode kernel: arrivals (self-clearing) ...
-    unsigned dec_phase;                  // ... and generation
+    unsigned dec_count;                  // arrival counters of the decode kernel's two grid barriers
+    unsigned dec_phase;                  // (cleared by CTA 0 of each launch, see decode.cu)
     int pad2;
+    unsigned long long dec_time[8];      // phase timestamps (ns) of CTA 0 in the last decode-kernel run
 };
 
 enum KernelStatus : int {

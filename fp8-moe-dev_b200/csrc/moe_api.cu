@@ -22,6 +22,7 @@ cudaError_t launch_quantize_rows(const void*, void*, float*, int, cudaStream_t);
 cudaError_t launch_combine_push(const Workspace&, const ExchangeView&, int, cudaStream_t);
 cudaError_t launch_reduce_owned(const Workspace&, const ExchangeView&, int, void*, cudaStream_t);
 int encode_kmajor_u8_map(void*, const void*, uint64_t, uint64_t, uint64_t, uint32_t);
+int encode_rows_1k_map(void*, const void*, uint64_t, uint64_t, uint32_t);
 size_t tensor_map_bytes();
 cudaError_t configure_gemm_kernels();
 cudaError_t launch_grouped_gemm(int, const void*, const void*, const Workspace&, const float*, int, int, int,
@@ -109,6 +110,8 @@ struct moe_fp8_b200_ctx {
     alignas(64) unsigned char tmap_a2[128];
     alignas(64) unsigned char tmap_w1[128];
     alignas(64) unsigned char tmap_w2[128];
+    alignas(64) unsigned char tmap_dec_w1[128];   // the decode kernel's views of the same weights
+    alignas(64) unsigned char tmap_dec_w2[128];
     const void* cached_w1 = nullptr;
     const void* cached_w2 = nullptr;
     // optional per-stage timing: events around each stage of the last kTimedRuns runs
@@ -178,11 +181,15 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
     if (a.gemm1_weights != h->cached_w1) {
         const int r = encode_kmajor_u8_map(h->tmap_w1, a.gemm1_weights, kHidden, kGemm1Out, E, 128);
         if (r != 0) return fail(h, MOE_FP8_B200_ERR_CUDA, "cuTensorMapEncodeTiled(W1) failed: %d", r);
+        const int r2 = encode_rows_1k_map(h->tmap_dec_w1, a.gemm1_weights, kHidden, (uint64_t)E * kGemm1Out, 8);
+        if (r2 != 0) return fail(h, MOE_FP8_B200_ERR_CUDA, "cuTensorMapEncodeTiled(W1, decode view) failed: %d", r2);
         h->cached_w1 = a.gemm1_weights;
     }
     if (a.gemm2_weights != h->cached_w2) {
         const int r = encode_kmajor_u8_map(h->tmap_w2, a.gemm2_weights, kInter, kHidden, E, 256);
         if (r != 0) return fail(h, MOE_FP8_B200_ERR_CUDA, "cuTensorMapEncodeTiled(W2) failed: %d", r);
+        const int r2 = encode_rows_1k_map(h->tmap_dec_w2, a.gemm2_weights, kInter, (uint64_t)E * kHidden, 16);
+        if (r2 != 0) return fail(h, MOE_FP8_B200_ERR_CUDA, "cuTensorMapEncodeTiled(W2, decode view) failed: %d", r2);
         h->cached_w2 = a.gemm2_weights;
     }
     cudaEvent_t* ev = nullptr;
@@ -224,7 +231,7 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
         d.silu_exact = h->opt_exact_silu;
         d.pol = pol;
         mark(0);
-        if (e == cudaSuccess) e = launch_decode_layer(d, h->ws, h->num_sms, stream);
+        if (e == cudaSuccess) e = launch_decode_layer(d, h->tmap_dec_w1, h->tmap_dec_w2, h->ws, h->num_sms, stream);
         for (int i = 1; i <= 6; ++i) mark(i);
         if (e != cudaSuccess) {
             h->counters_dirty = true;
@@ -632,6 +639,7 @@ int moe_fp8_b200_read_intermediate(moe_fp8_b200_handle h, int buffer, void* dst,
         case MOE_FP8_B200_BUF_SFA2: src = w.sfa2; size = sizeof(float) * kInterBlocks * M; break;
         case MOE_FP8_B200_BUF_Y: src = w.y; size = sizeof(__nv_bfloat16) * M * kHidden; break;
         case MOE_FP8_B200_BUF_STATUS: src = &w.ctrl->status; size = sizeof(int) * 2; break;
+        case MOE_FP8_B200_BUF_DECODE_TIMELINE: src = w.ctrl->dec_time; size = sizeof(w.ctrl->dec_time); break;
         default: return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "unknown buffer id %d", buffer);
     }
     if (offset > size || bytes > size - offset)
