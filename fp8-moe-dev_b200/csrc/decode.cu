@@ -59,6 +59,7 @@ constexpr int kStepBytes = kStepRows * kStepK;          // 16 KB arrive per step
 constexpr int kG1Steps = kHidden / kStepK;              // 7 per phase-1 unit
 constexpr int kG2Steps = kInter / kStepK;               // 2 per phase-2 unit
 constexpr int kRing = 4;                                // steps in flight per half
+constexpr int kCoopRouteTokens = 2;                     // up to here the CTA routes a token together
 static_assert(kHidden % kStepK == 0 && kInter % kStepK == 0, "K splits into whole steps");
 static_assert(2 * kDecodeMaxTokens * kA2Stride <= kDecodeMaxTokens * kHidStride, "phase 2 rows reuse the hidden-row area");
 
@@ -72,6 +73,12 @@ struct DecodeShared {
     int act_expert[kDecMaxActive], act_m[kDecMaxActive], act_row0[kDecMaxActive];
     int act_tok[kDecMaxActive][kDecodeMaxTokens];
     int expert_slot[kMaxLocalExperts];
+    // routing scratch
+    float r_gscore[kDecodeMaxTokens][kNumGroups];
+    int r_kept[kDecodeMaxTokens][kTopKGroup];
+    int r_count[kDecodeMaxTokens][kTopKGroup][32];
+    int r_idx[kDecodeMaxTokens][kTopK];
+    float r_sel[kDecodeMaxTokens][kTopK];
     float hid_scale[kDecodeMaxTokens][kHiddenBlocks];      // [token][kb]
     float a2_scale[2][kDecodeMaxTokens][kInterBlocks];     // per half: [slot][kb] of the requantised rows
     alignas(8) uint64_t full_bar[2][kRing];
@@ -193,33 +200,128 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_layer_kernel(
     }
 
     // ------------------------------------------------------------------ routing (every CTA)
+    // For one or two tokens: the same selection as route_token_warp (route_token.cuh), spread over
+    // the CTA's 16 warps, because the single-warp routine's chain of dependent reductions (about
+    // 4 us) would be the longest serial stretch of the kernel.  Scores and their order-preserving keys go to
+    // shared memory; one warp per (token, group) forms the group score; one thread per token keeps
+    // the four best groups; then the eight argmax rounds are replaced by counting, for each of the
+    // 128 live scores, how many of the others beat it (higher key, or equal key and earlier in the
+    // reference's tie order): the score with count k is the k-th pick.  Same picks, same order.
     if (tid < kMaxLocalExperts) sh->expert_slot[tid] = -1;
-    if (warp < T) {
+    float* r_s = reinterpret_cast<float*>(&sh->wring[1][kRing - 1][0]);                 // [T][256], idle ring slot
+    uint32_t* r_key = reinterpret_cast<uint32_t*>(r_s + kDecodeMaxTokens * kNumExperts);  // [T][256]
+    static_assert(2 * kDecodeMaxTokens * kNumExperts * 4 <= kStepRows * kStepStride, "routing scratch fits a ring slot");
+    stamp(12);
+    if (T <= kCoopRouteTokens) {
+        for (int q = tid; q < T * kNumExperts; q += kDecThreads) {
+            const float l = __ldg(a.logits + q);
+            const float sig = 1.0f / (1.0f + __expf(-l));
+            r_s[q] = sig;
+            r_key[q] = float_to_ordered(sig + __bfloat162float(a.bias[q & (kNumExperts - 1)]));
+        }
+        for (int q = tid; q < T * kTopKGroup * 32; q += kDecThreads) (&sh->r_count[0][0][0])[q] = 0;
+        __syncthreads();
+        for (int task = warp; task < T * kNumGroups; task += kDecWarps) {   // group score = two largest of the group
+            const uint32_t key = r_key[task * 32 + lane];
+            const uint32_t k1 = __reduce_max_sync(0xffffffffu, key);
+            const uint32_t holders = __ballot_sync(0xffffffffu, key == k1);
+            uint32_t k2 = k1;
+            if (__popc(holders) < 2) k2 = __reduce_max_sync(0xffffffffu, key == k1 ? 0u : key);
+            if (lane == 0) sh->r_gscore[task / kNumGroups][task % kNumGroups] = ordered_to_float(k1) + ordered_to_float(k2);
+        }
+        __syncthreads();
+        if (tid < T) {   // four best groups, lowest index first on ties
+            uint32_t kept_mask = 0;
+            for (int k = 0; k < kTopKGroup; ++k) {
+                float best = kNegSentinel;
+                int best_i = -1;
+                for (int i = 0; i < kNumGroups; ++i) {
+                    const float gsc = sh->r_gscore[tid][i];
+                    if (!((kept_mask >> i) & 1u) && gsc > best) { best = gsc; best_i = i; }
+                }
+                if (best_i >= 0) {
+                    kept_mask |= 1u << best_i;
+                    sh->r_kept[tid][k] = best_i;
+                } else {
+                    sh->r_kept[tid][k] = k;   // unreachable with finite scores; keeps the indices valid
+                }
+            }
+        }
+        __syncthreads();
+        // count[t][j][lane]: how many live scores beat score `lane` of the j-th kept group; the work of one
+        // (token, group) is split over four warps, one per opposing group
+        for (int task = warp; task < T * kTopKGroup * kTopKGroup; task += kDecWarps) {
+            const int t = task / (kTopKGroup * kTopKGroup), j = (task / kTopKGroup) % kTopKGroup, part = task % kTopKGroup;
+            const int g = sh->r_kept[t][j], g2 = sh->r_kept[t][part];
+            const uint32_t key = r_key[t * kNumExperts + g * 32 + lane];
+            const uint32_t tie = (uint32_t)g * 32u + (__brev((uint32_t)lane) >> 27);
+            const uint32_t* other = r_key + t * kNumExperts + g2 * 32;
+            int beat = 0;
+    #pragma unroll 8
+            for (int l2 = 0; l2 < 32; ++l2) {
+                const uint32_t key2 = other[l2];
+                const uint32_t tie2 = (uint32_t)g2 * 32u + (__brev((uint32_t)l2) >> 27);
+                beat += (key2 > key || (key2 == key && tie2 < tie)) ? 1 : 0;
+            }
+            atomicAdd(&sh->r_count[t][j][lane], beat);
+        }
+        __syncthreads();
+        for (int task = warp; task < T * kTopKGroup; task += kDecWarps) {
+            const int t = task / kTopKGroup, j = task % kTopKGroup;
+            const int rank = sh->r_count[t][j][lane];
+            if (rank < kTopK) {
+                const int ge = sh->r_kept[t][j] * 32 + lane;
+                sh->r_idx[t][rank] = ge;
+                sh->r_sel[t][rank] = r_s[t * kNumExperts + ge];
+            }
+        }
+        __syncthreads();
+    } else if (warp < T) {
+        // more tokens than that: one warp per token runs the staged chain's routine, the tokens in parallel
         int idx[kTopK];
         float wn[kTopK];
         route_token_warp(a.logits + (size_t)warp * kNumExperts, a.bias, lane, idx, wn);
-        if (blockIdx.x == 0 && lane < kTopK) {
+        if (lane < kTopK) {
             int my_idx = 0;
-            float my_w = 0.0f;
+            float my_s = 0.0f;
 #pragma unroll
             for (int k = 0; k < kTopK; ++k)
-                if (k == lane) { my_idx = idx[k]; my_w = wn[k]; }
-            ws.topk_idx[(size_t)warp * kTopK + lane] = my_idx;
-            ws.topk_weight[(size_t)warp * kTopK + lane] = my_w;
+                if (k == lane) { my_idx = idx[k]; my_s = wn[k]; }
+            sh->r_idx[warp][lane] = my_idx;
+            sh->r_sel[warp][lane] = my_s;   // already normalised
         }
-        if (lane == 0) {
-            int n_pairs = 0;
-            int p_le[kTopK];
-            float p_w[kTopK];
+    }
+    if (T > kCoopRouteTokens) __syncthreads();
+    stamp(8);
+    if (tid < T) {
+        const int t = tid;
+        int idx[kTopK];
+        float wn[kTopK];
+        float sumw = 1e-20f;
 #pragma unroll
-            for (int i = 0; i < kTopK; ++i) { p_le[i] = 0; p_w[i] = 0.0f; }
-            const int shards = E / kShardExperts;
-            for (int s = 0; s < shards; ++s)
-                dispatch_one_shard(idx, wn, s, a.local_expert_offset, a.pol, a.rsf, n_pairs, p_le, p_w);
-            sh->pair_count[warp] = n_pairs;
+        for (int k = 0; k < kTopK; ++k) { idx[k] = sh->r_idx[t][k]; sumw += sh->r_sel[t][k]; }
+        const float inv = 1.0f / sumw;
 #pragma unroll
-            for (int i = 0; i < kTopK; ++i) { sh->pair_le[warp][i] = p_le[i]; sh->pair_w[warp][i] = p_w[i]; }
+        for (int k = 0; k < kTopK; ++k) wn[k] = T <= kCoopRouteTokens ? sh->r_sel[t][k] * inv : sh->r_sel[t][k];
+        if (blockIdx.x == 0) {
+#pragma unroll
+            for (int k = 0; k < kTopK; ++k) {
+                ws.topk_idx[(size_t)t * kTopK + k] = idx[k];
+                ws.topk_weight[(size_t)t * kTopK + k] = wn[k];
+            }
         }
+        int n_pairs = 0;
+        int p_le[kTopK];
+        float p_w[kTopK];
+#pragma unroll
+        for (int i = 0; i < kTopK; ++i) { p_le[i] = 0; p_w[i] = 0.0f; }
+        const int shards = E / kShardExperts;
+        for (int sdx = 0; sdx < shards; ++sdx)
+            dispatch_one_shard(idx, wn, sdx, a.local_expert_offset, a.pol, a.rsf, n_pairs, p_le, p_w);
+        sh->pair_count[t] = n_pairs;
+#pragma unroll
+        for (int i = 0; i < kTopK; ++i) { sh->pair_le[t][i] = p_le[i]; sh->pair_w[t][i] = p_w[i]; }
+        stamp(9);
     }
     __syncthreads();
     if (tid == 0) {
@@ -246,6 +348,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_layer_kernel(
         for (int ai = 0; ai < n_active; ++ai) { sh->act_row0[ai] = rows; rows += sh->act_m[ai]; }
         sh->n_active = n_active;
         sh->n_rows = rows;
+        stamp(10);
     }
     __syncthreads();
     if (tid < T * kTopK) {
@@ -267,6 +370,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_layer_kernel(
             ws.ctrl->expert_rows[tid] = ai >= 0 ? sh->act_m[ai] : 0;
         }
     }
+    stamp(11);
     __syncthreads();
     const int n_active = sh->n_active;
     stamp(1);

@@ -58,7 +58,7 @@ struct Control {
     unsigned dec_count;                  // arrival counters of the decode kernel's two grid barriers
     unsigned dec_phase;                  // (cleared by CTA 0 of each launch, see decode.cu)
     int pad2;
-    unsigned long long dec_time[8];      // phase timestamps (ns) of CTA 0 in the last decode-kernel run
+    unsigned long long dec_time[16];     // phase timestamps (ns) of CTA 0 in the last decode-kernel run
 };
 
 enum KernelStatus : int {

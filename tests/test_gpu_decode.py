@@ -147,3 +147,29 @@ def test_decode_kernel_exact_silu_and_chain_agree(pkg, layers):
     c = hp.run_layer(dec, inputs, weights, 32).float().cpu().numpy()
     assert hp.error_stats(a, b)["rel_l2"] < 5e-3
     assert not np.array_equal(a, c)   # the option does reach the kernel
+
+
+def test_decode_routing_equals_chain_routing_on_many_batches_and_ties(pkg, layers):
+    """The decode kernel selects experts by counting instead of argmax rounds: its picks, their
+    order and weights must equal the staged routing kernel's bit for bit, also when scores tie
+    (coarsely quantised logits, zero bias: dozens of equal scores per token)."""
+    dec, chain = layers
+    T = 8
+    weights = hp.gpu_shard(0, 32)
+    g = torch.Generator().manual_seed(77)
+    zero_bias = torch.zeros(256, dtype=torch.bfloat16)
+    for trial in range(24):
+        logits, bias, hidden, hscale = hp.cpu_inputs(T, seed=2000 + trial)
+        if trial % 2:
+            logits = (torch.randn(T, 256, generator=g) * 1.5).round() / 2      # heavy ties
+            bias = zero_bias
+        if trial % 6 == 5:
+            logits = torch.zeros(T, 256)                                        # everything ties
+        inputs = (logits.contiguous(), bias, hidden, hscale)
+        hp.run_layer(dec, inputs, weights, 0)
+        td = _tables(dec, T)
+        hp.run_layer(chain, inputs, weights, 0)
+        tc = _tables(chain, T)
+        assert np.array_equal(td[0], tc[0]), f"trial {trial}: expert picks differ"
+        assert np.array_equal(td[1], tc[1]), f"trial {trial}: weights differ"
+        assert np.array_equal(td[2], tc[2]) and td[3] == tc[3] and np.array_equal(td[4], tc[4])
