@@ -232,12 +232,20 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
         d.pol = pol;
         mark(0);
         if (e == cudaSuccess) e = launch_decode_layer(d, h->tmap_dec_w1, h->tmap_dec_w2, h->ws, h->num_sms, stream);
-        for (int i = 1; i <= 6; ++i) mark(i);
-        if (e != cudaSuccess) {
-            h->counters_dirty = true;
-            return fail(h, MOE_FP8_B200_ERR_CUDA, "decode launch failed: %s", cudaGetErrorString(e));
+        if (e == cudaErrorCooperativeLaunchTooLarge) {
+            // fewer SMs than the device reports are available to this context (partitioned GPU):
+            // the grid cannot be co-resident, so this handle uses the chain from now on
+            cudaGetLastError();
+            h->decode_ctas_per_sm = 0;
+            e = cudaSuccess;
+        } else {
+            for (int i = 1; i <= 6; ++i) mark(i);
+            if (e != cudaSuccess) {
+                h->counters_dirty = true;
+                return fail(h, MOE_FP8_B200_ERR_CUDA, "decode launch failed: %s", cudaGetErrorString(e));
+            }
+            return MOE_FP8_B200_OK;
         }
-        return MOE_FP8_B200_OK;
     }
     mark(0);
     if (e == cudaSuccess)

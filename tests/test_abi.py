@@ -109,3 +109,41 @@ def test_product_never_touches_the_oracle():
         if f.suffix in (".py", ".cu", ".cuh", ".cc", ".h") and f.is_file():
             txt = f.read_text()
             assert "oracle" not in txt.lower(), f
+
+
+def test_exchange_buffer_sizing(pkg):
+    """moe_fp8_b200_exchange_bytes: flags + two parities of [world][ceil(T/world)] bf16 rows and
+    presence bytes; zero for an invalid world size; monotonic in T."""
+    lib = pkg._lib.load()
+    for world in (1, 2, 4, 8):
+        prev = 0
+        for T in (0, 1, 7, 8, 9, 1000, 12288, 16384):
+            per = (T + world - 1) // world
+            n = lib.moe_fp8_b200_exchange_bytes(T, world)
+            rows = 2 * world * per * 7168 * 2
+            assert n >= 256 + rows + 2 * world * per
+            assert n <= 256 + rows + 2 * (world * (per + 15) + 256)
+            assert n >= prev
+            prev = n
+    for world in (0, 3, 5, 16, -1):
+        assert lib.moe_fp8_b200_exchange_bytes(128, world) == 0
+    assert lib.moe_fp8_b200_exchange_bytes(-1, 2) == 0
+
+
+def test_python_binding_constants_match_the_header(pkg):
+    txt = (ROOT / "include" / "moe_fp8_b200.h").read_text()
+    consts = dict(re.findall(r"(MOE_FP8_B200_(?:OPT|BUF|ERR)\w+)\s*=\s*(-?\d+)", txt))
+    L = pkg._lib
+    assert int(consts["MOE_FP8_B200_OPT_REFERENCE_PRUNING"]) == L.OPT_REFERENCE_PRUNING
+    assert int(consts["MOE_FP8_B200_OPT_EXACT_SILU"]) == L.OPT_EXACT_SILU
+    assert int(consts["MOE_FP8_B200_OPT_STAGE_TIMING"]) == L.OPT_STAGE_TIMING
+    assert int(consts["MOE_FP8_B200_OPT_STOP_AFTER_STAGE"]) == L.OPT_STOP_AFTER_STAGE
+    assert int(consts["MOE_FP8_B200_OPT_DECODE_KERNEL"]) == L.OPT_DECODE_KERNEL
+    for name, val in L.BUF.items():
+        assert int(consts["MOE_FP8_B200_BUF_" + name.upper()]) == val, name
+    assert int(re.search(r"MOE_FP8_B200_DECODE_MAX_TOKENS\s+(\d+)", txt).group(1)) == L.DECODE_MAX_TOKENS
+    assert int(re.search(r"MOE_FP8_B200_NOALLOC_MAX_TOKENS\s+(\d+)", txt).group(1)) == L.NOALLOC_MAX_TOKENS
+    # struct layouts the ctypes mirror must reproduce (LP64)
+    assert C.sizeof(L.Args) == 8 * 8 + 8 + 8 + 8 + 8
+    assert C.sizeof(L.Exchange) == 8 * 8 + 8 + 4 + 4 + 8
+    assert C.sizeof(L.Unfinalized) == 5 * 8 + 8
