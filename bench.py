@@ -178,14 +178,20 @@ def make_workload(name: str, rank: int, world: int):
     return T, offset, E, (logits, bias, hidden, hscale), weights
 
 
-def time_steps(step, steps, warmup, world):
+def time_steps(step, steps, warmup, world, drain=None):
+    """`drain`: called after the warm-up and after the last timed step, for steps that return
+    before their work is finished (it must block the host until everything issued is done)."""
     for _ in range(warmup):
         step()
+    if drain:
+        drain()
     barrier(world)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
         step()
+    if drain:
+        drain()
     e1.record()
     barrier(world)
     return max_over_ranks(e0.elapsed_time(e1), world) / steps  # ms per step
@@ -372,9 +378,26 @@ def run_ours(args, rank, world, local):
     # end to end: per-step inputs start in pinned host memory, the result ends in host memory
     pin = [x.pin_memory() for x in (inputs[0], inputs[2], inputs[3])]
     host_out = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+    host_out2 = torch.empty(T, H, dtype=torch.bfloat16).pin_memory() if world == 1 else None
+    pipe = {"i": 0, "tickets": []}
     if world == 1:
-        def e2e_step():
+        def e2e_sync_step():
             layer.run_host(pin[0], dev[1], pin[1], pin[2], w1, s1, w2, s2, offset, RSF, host_out)
+
+        def e2e_step():
+            # pipelined host path, two calls in flight: every step copies its inputs from pinned host
+            # memory and lands its output in host memory; the output of step i-1 is awaited (read)
+            # right after step i has been issued
+            i = pipe["i"]
+            pipe["tickets"].append(layer.run_host_async(pin[0], dev[1], pin[1], pin[2], w1, s1, w2, s2, offset, RSF,
+                                                        host_out if i % 2 == 0 else host_out2))
+            if i >= 1:
+                layer.host_wait(pipe["tickets"][i - 1])
+            pipe["i"] = i + 1
+
+        def e2e_drain():
+            if pipe["tickets"]:
+                layer.host_wait(pipe["tickets"][-1])
     else:
         def e2e_step():
             dev[0].copy_(pin[0], non_blocking=True)
@@ -383,7 +406,14 @@ def run_ours(args, rank, world, local):
             res = step()
             host_out[:res.shape[0]].copy_(res, non_blocking=True)
             torch.cuda.current_stream().synchronize()
-    e2e_ms = time_steps(e2e_step, max(3, args.steps // 2), 3, world) if not args.skip_e2e else float("nan")
+    e2e_sync_ms = None
+    if args.skip_e2e:
+        e2e_ms = float("nan")
+    elif world == 1:
+        e2e_ms = time_steps(e2e_step, max(4, args.steps // 2), 3, world, drain=e2e_drain)
+        e2e_sync_ms = time_steps(e2e_sync_step, max(3, args.steps // 3), 2, world)
+    else:
+        e2e_ms = time_steps(e2e_step, max(3, args.steps // 2), 3, world)
     h2d = sum(x.numel() * x.element_size() for x in pin)
     d2h = (host_out if (world == 1 or args.collective == "all_reduce") else scat).numel() * 2
     other_ms = None
@@ -412,7 +442,10 @@ def run_ours(args, rank, world, local):
         "clocks": clk.summary(),
         "e2e": None if args.skip_e2e else {"value": round(T / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "path": "moe_fp8_b200_run_host (C ABI, host buffers)" if world == 1
+                "sync_call_ms_per_step": None if e2e_sync_ms is None else round(e2e_sync_ms, 4),
+                "path": "moe_fp8_b200_run_host_async + host_wait (C ABI, pinned host buffers, two calls in flight: copy-in of step "
+                        "i+1 and copy-out of step i-1 overlap the compute of step i); sync_call_ms_per_step = one blocking "
+                        "moe_fp8_b200_run_host per step" if world == 1
                         else ("pinned H2D + moe_fp8_b200_run_reduce_scatter (peer stores) + D2H" if args.collective == "fused"
                               else f"pinned H2D + moe_fp8_b200_run + NCCL {args.collective} + D2H")},
         "gpu_launches": (6 if (world > 1 and args.collective == "fused") else 5) * args.steps * world,

@@ -28,7 +28,8 @@ EXPORTS = [
     "moe_fp8_b200_run", "moe_fp8_b200_run_host", "moe_fp8_b200_check", "moe_fp8_b200_read_intermediate",
     "moe_fp8_b200_reference_policy", "moe_fp8_b200_stage_times", "moe_fp8_b200_route_noalloc",
     "moe_fp8_b200_exchange_bytes", "moe_fp8_b200_run_reduce_scatter", "moe_fp8_b200_quantize_hidden",
-    "moe_fp8_b200_run_unfinalized", "moe_fp8_b200_finalize",
+    "moe_fp8_b200_run_unfinalized", "moe_fp8_b200_finalize", "moe_fp8_b200_run_host_async",
+    "moe_fp8_b200_host_wait",
 ]
 NOALLOC_MAX_TOKENS = 4096
 
@@ -95,6 +96,10 @@ def load() -> C.CDLL:
     lib.moe_fp8_b200_run_unfinalized.argtypes = [H, C.POINTER(Args), C.POINTER(Unfinalized), C.c_void_p]
     lib.moe_fp8_b200_finalize.restype = C.c_int
     lib.moe_fp8_b200_finalize.argtypes = [H, C.c_int, C.c_void_p, C.c_void_p]
+    lib.moe_fp8_b200_run_host_async.restype = C.c_int
+    lib.moe_fp8_b200_run_host_async.argtypes = [H, C.POINTER(Args), C.c_void_p, C.POINTER(C.c_int64)]
+    lib.moe_fp8_b200_host_wait.restype = C.c_int
+    lib.moe_fp8_b200_host_wait.argtypes = [H, C.c_int64]
     lib.moe_fp8_b200_check.restype = C.c_int
     lib.moe_fp8_b200_check.argtypes = [H, C.c_void_p]
     lib.moe_fp8_b200_read_intermediate.restype = C.c_int

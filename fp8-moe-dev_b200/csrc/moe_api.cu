@@ -124,6 +124,13 @@ struct moe_fp8_b200_ctx {
     // staging for run_host (allocated on its first use)
     uint8_t* stage = nullptr;
     size_t stage_bytes = 0;
+    // pipelined host path: two staging sets, copy streams, per-set events
+    uint8_t* pipe_stage[2] = {nullptr, nullptr};
+    size_t pipe_bytes = 0;
+    cudaStream_t pipe_in = nullptr, pipe_out = nullptr;
+    cudaEvent_t pipe_in_done[2] = {nullptr, nullptr}, pipe_compute_done[2] = {nullptr, nullptr},
+                pipe_out_done[2] = {nullptr, nullptr};
+    int64_t pipe_seq = 0;
     std::string error;
 };
 
@@ -417,6 +424,14 @@ int moe_fp8_b200_destroy(moe_fp8_b200_handle h)
         for (auto& run : h->events)
             for (auto& x : run) cudaEventDestroy(x);
     if (h->stage) cudaFree(h->stage);
+    for (int i = 0; i < 2; ++i) {
+        if (h->pipe_stage[i]) cudaFree(h->pipe_stage[i]);
+        if (h->pipe_in_done[i]) cudaEventDestroy(h->pipe_in_done[i]);
+        if (h->pipe_compute_done[i]) cudaEventDestroy(h->pipe_compute_done[i]);
+        if (h->pipe_out_done[i]) cudaEventDestroy(h->pipe_out_done[i]);
+    }
+    if (h->pipe_in) cudaStreamDestroy(h->pipe_in);
+    if (h->pipe_out) cudaStreamDestroy(h->pipe_out);
     if (h->base) cudaFree(h->base);
     delete h;
     return MOE_FP8_B200_OK;
@@ -580,6 +595,88 @@ int moe_fp8_b200_run_host(moe_fp8_b200_handle h, const moe_fp8_b200_args* args, 
     e = cudaMemcpyAsync(args->output, d_out, sizeof(__nv_bfloat16) * (size_t)T * kHidden, cudaMemcpyDeviceToHost, stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "device-to-host copy: %s", cudaGetErrorString(e));
+    return MOE_FP8_B200_OK;
+}
+
+int moe_fp8_b200_run_host_async(moe_fp8_b200_handle h, const moe_fp8_b200_args* args, void* stream_v, int64_t* ticket)
+{
+    const int v = validate(h, args);
+    if (v != MOE_FP8_B200_OK) return v;
+    if (!ticket) return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "ticket is NULL");
+    const int T = args->num_tokens;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    cudaError_t e = cudaSuccess;
+    if (!h->pipe_in) {
+        e = cudaStreamCreateWithFlags(&h->pipe_in, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->pipe_out, cudaStreamNonBlocking);
+        for (int i = 0; i < 2 && e == cudaSuccess; ++i) {
+            e = cudaEventCreateWithFlags(&h->pipe_in_done[i], cudaEventDisableTiming);
+            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->pipe_compute_done[i], cudaEventDisableTiming);
+            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->pipe_out_done[i], cudaEventDisableTiming);
+        }
+        if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "pipeline set-up: %s", cudaGetErrorString(e));
+    }
+    const size_t Tm = (size_t)h->max_tokens;
+    const size_t b_logits = align_up(sizeof(float) * Tm * kNumExperts, 256);
+    const size_t b_hidden = align_up(Tm * kHidden, 256);
+    const size_t b_scale = align_up(sizeof(float) * (size_t)kHiddenBlocks * Tm, 256);
+    const size_t b_out = align_up(sizeof(__nv_bfloat16) * Tm * kHidden, 256);
+    if (!h->pipe_stage[0]) {   // sized once for max_tokens: no allocation between pipelined calls
+        const size_t need = b_logits + b_hidden + b_scale + b_out;
+        for (int i = 0; i < 2; ++i) {
+            e = cudaMalloc(&h->pipe_stage[i], need);
+            if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "cudaMalloc(pipeline staging %zu): %s", need, cudaGetErrorString(e));
+        }
+        h->pipe_bytes = need;
+    }
+    const int set = (int)(h->pipe_seq & 1);
+    *ticket = h->pipe_seq;
+    ++h->pipe_seq;
+    if (T == 0) {   // nothing to move; keep the set's events meaningful for host_wait
+        e = cudaEventRecord(h->pipe_out_done[set], h->pipe_out);
+        return e == cudaSuccess ? MOE_FP8_B200_OK : fail(h, MOE_FP8_B200_ERR_CUDA, "event record: %s", cudaGetErrorString(e));
+    }
+    uint8_t* d_logits = h->pipe_stage[set];
+    uint8_t* d_hidden = d_logits + b_logits;
+    uint8_t* d_scale = d_hidden + b_hidden;
+    uint8_t* d_out = d_scale + b_scale;
+    // copy-in: the set's inputs were last read by the compute of two calls ago
+    if (*ticket >= 2) e = cudaStreamWaitEvent(h->pipe_in, h->pipe_compute_done[set], 0);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(d_logits, args->routing_logits, sizeof(float) * (size_t)T * kNumExperts, cudaMemcpyHostToDevice, h->pipe_in);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_hidden, args->hidden_states, (size_t)T * kHidden, cudaMemcpyHostToDevice, h->pipe_in);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(d_scale, args->hidden_states_scale, sizeof(float) * (size_t)kHiddenBlocks * T, cudaMemcpyHostToDevice, h->pipe_in);
+    if (e == cudaSuccess) e = cudaEventRecord(h->pipe_in_done[set], h->pipe_in);
+    // compute: needs the inputs, and the set's output buffer must have been copied out (two calls ago)
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(stream, h->pipe_in_done[set], 0);
+    if (e == cudaSuccess && *ticket >= 2) e = cudaStreamWaitEvent(stream, h->pipe_out_done[set], 0);
+    if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "pipeline copy-in: %s", cudaGetErrorString(e));
+    moe_fp8_b200_args dev = *args;
+    dev.routing_logits = reinterpret_cast<const float*>(d_logits);
+    dev.hidden_states = d_hidden;
+    dev.hidden_states_scale = reinterpret_cast<const float*>(d_scale);
+    dev.output = d_out;
+    const int rc = enqueue_layer(h, dev, stream);
+    if (rc != MOE_FP8_B200_OK) return rc;
+    e = cudaEventRecord(h->pipe_compute_done[set], stream);
+    // copy-out
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(h->pipe_out, h->pipe_compute_done[set], 0);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(args->output, d_out, sizeof(__nv_bfloat16) * (size_t)T * kHidden, cudaMemcpyDeviceToHost, h->pipe_out);
+    if (e == cudaSuccess) e = cudaEventRecord(h->pipe_out_done[set], h->pipe_out);
+    if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "pipeline copy-out: %s", cudaGetErrorString(e));
+    return MOE_FP8_B200_OK;
+}
+
+int moe_fp8_b200_host_wait(moe_fp8_b200_handle h, int64_t ticket)
+{
+    if (!h) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
+    if (ticket < 0 || ticket >= h->pipe_seq)
+        return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "ticket %lld was never issued", (long long)ticket);
+    if (ticket + 2 < h->pipe_seq) return MOE_FP8_B200_OK;   // its staging set has been reused since: long finished
+    const cudaError_t e = cudaEventSynchronize(h->pipe_out_done[ticket & 1]);
+    if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "waiting for copy-out: %s", cudaGetErrorString(e));
     return MOE_FP8_B200_OK;
 }
 

@@ -257,6 +257,27 @@ class MoeLayer:
             self._raise(rc)
         return output
 
+    def run_host_async(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                       gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                       routed_scaling_factor, output, stream: Optional[int] = None) -> int:
+        """Pipelined run_host: enqueues copy-in, layer and copy-out and returns a ticket at once.
+        The host tensors must stay untouched until host_wait(ticket); at most two calls in flight."""
+        a = self._args(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                       gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                       routed_scaling_factor, output, host=True)
+        if stream is None:
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+        ticket = C.c_int64(-1)
+        rc = self._lib.moe_fp8_b200_run_host_async(self._h, C.byref(a), C.c_void_p(stream), C.byref(ticket))
+        if rc != _lib.OK:
+            self._raise(rc)
+        return int(ticket.value)
+
+    def host_wait(self, ticket: int):
+        rc = self._lib.moe_fp8_b200_host_wait(self._h, int(ticket))
+        if rc != _lib.OK:
+            self._raise(rc)
+
     def check(self, stream: Optional[int] = None):
         """Synchronise and raise if a kernel recorded a failure (e.g. a wait that ran out)."""
         if stream is None:

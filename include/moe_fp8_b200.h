@@ -146,6 +146,19 @@ MOE_FP8_B200_API int moe_fp8_b200_run(moe_fp8_b200_handle h, const moe_fp8_b200_
  * end-to-end form a host-resident caller of the reference operator sees. */
 MOE_FP8_B200_API int moe_fp8_b200_run_host(moe_fp8_b200_handle h, const moe_fp8_b200_args* args, void* stream);
 
+/* Pipelined form of moe_fp8_b200_run_host for a caller that feeds batch after batch from host
+ * memory: the call enqueues copy-in, the layer and copy-out on three streams and returns a
+ * ticket without waiting; two staging sets alternate, so the copy-in of call i+1 and the
+ * copy-out of call i-1 run while call i computes (PCIe is full duplex and needs no SM).  The
+ * host tensors of a call (inputs and output) must stay untouched until
+ * moe_fp8_b200_host_wait(handle, ticket) has returned for it, and at most two calls may be
+ * outstanding (wait for ticket i-1 before issuing call i+1).  Host memory should be pinned;
+ * pageable memory works but serialises.  `stream` carries the compute, as in run().  No
+ * counterpart in the reference, which takes device tensors only. */
+MOE_FP8_B200_API int moe_fp8_b200_run_host_async(moe_fp8_b200_handle h, const moe_fp8_b200_args* args, void* stream,
+                                                 int64_t* ticket);
+MOE_FP8_B200_API int moe_fp8_b200_host_wait(moe_fp8_b200_handle h, int64_t ticket);
+
 /* ---- expert-parallel run with the reduce-scatter fused into the combine step -----------
  * No counterpart in the reference (it has no multi-GPU code; its local_expert_offset
  * argument, kernel/moe_fp8.cu:2671, only says which 32 experts a rank holds).  `world` ranks

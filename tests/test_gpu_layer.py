@@ -387,3 +387,33 @@ def test_tvm_ffi_entry_point_matches_c_abi(pkg, layer32):
     mod.run(dev[0], dev[1], dev[2], dev[3], w1, s1, w2, s2, 0, RSF, out)
     torch.cuda.synchronize()
     assert torch.equal(out, want)
+
+
+def test_pipelined_host_entry_point(pkg, layer32):
+    """run_host_async / host_wait: five calls kept two deep in flight over rotating pinned buffers
+    give, call by call, what the synchronous device-pointer run gives for the same inputs."""
+    T = 300
+    weights = hp.gpu_shard(0, 32)
+    raw = [hp.cpu_inputs(T, seed=1700 + i) for i in range(3)]
+    bias = raw[0][1]
+    sets = [(r[0], bias, r[2], r[3]) for r in raw]
+    want = [hp.run_layer(layer32, s, weights, 0).cpu() for s in sets]
+    assert not torch.equal(want[0], want[1])
+    pinned = [[x.pin_memory() for x in (s[0], s[2], s[3])] for s in sets]
+    outs = [torch.zeros(T, H, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    bias_dev = bias.cuda()
+    tickets = []
+    for i in range(5):
+        if i >= 2:   # the buffer about to be reused holds call i-2's result
+            layer32.host_wait(tickets[i - 2])
+            assert torch.equal(outs[i % 2], want[(i - 2) % 3]), f"call {i - 2}"
+            outs[i % 2].zero_()
+        p = pinned[i % 3]
+        tickets.append(layer32.run_host_async(p[0], bias_dev, p[1], p[2], *weights, 0, RSF, outs[i % 2]))
+    for i in (3, 4):
+        layer32.host_wait(tickets[i])
+        assert torch.equal(outs[i % 2], want[i % 3]), f"call {i}"
+    layer32.host_wait(tickets[0])   # long finished: returns at once
+    layer32.check()
+    with pytest.raises(Exception):
+        layer32.host_wait(99)
