@@ -501,13 +501,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                 if (valid) {
                     uint4* dst = reinterpret_cast<uint4*>(ws.y + (size_t)grow * kHidden + tc.n * kTileN + 128 * h);
 #pragma unroll
-                    for (int v4 = 0; v4 < 16; ++v4) {
-                        uint4 pk;
-                        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+                    for (int v8 = 0; v8 < 8; ++v8) {
+                        uint4 pk[2];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            h2[i] = __floats2bfloat162_rn(acc[v4 * 8 + 2 * i], acc[v4 * 8 + 2 * i + 1]);
-                        dst[v4] = pk;
+                        for (int q = 0; q < 2; ++q) {
+                            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk[q]);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                h2[i] = __floats2bfloat162_rn(acc[v8 * 16 + q * 8 + 2 * i], acc[v8 * 16 + q * 8 + 2 * i + 1]);
+                        }
+                        st_global_32B(dst + 2 * v8, pk[0], pk[1]);
                     }
                 }
             }
