@@ -482,18 +482,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                 if (valid) {
                     uint4* dst = reinterpret_cast<uint4*>(ws.a2 + (size_t)grow * kInter + tc.n * kBlock + 64 * h);
 #pragma unroll
-                    for (int v4 = 0; v4 < 4; ++v4) {
-                        uint32_t wd[4];
+                    for (int v8 = 0; v8 < 2; ++v8) {
+                        uint4 pk[2];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int j = v4 * 16 + i * 4;
-                            const uint32_t lo = __nv_cvt_float2_to_fp8x2(
-                                make_float2(acc[j] * inv_scale, acc[j + 1] * inv_scale), __NV_SATFINITE, __NV_E4M3);
-                            const uint32_t hi = __nv_cvt_float2_to_fp8x2(
-                                make_float2(acc[j + 2] * inv_scale, acc[j + 3] * inv_scale), __NV_SATFINITE, __NV_E4M3);
-                            wd[i] = lo | (hi << 16);
+                        for (int q = 0; q < 2; ++q) {
+                            uint32_t wd[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int j = (v8 * 2 + q) * 16 + i * 4;
+                                const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+                                    make_float2(acc[j] * inv_scale, acc[j + 1] * inv_scale), __NV_SATFINITE, __NV_E4M3);
+                                const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+                                    make_float2(acc[j + 2] * inv_scale, acc[j + 3] * inv_scale), __NV_SATFINITE, __NV_E4M3);
+                                wd[i] = lo | (hi << 16);
+                            }
+                            pk[q] = make_uint4(wd[0], wd[1], wd[2], wd[3]);
                         }
-                        dst[v4] = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+                        st_global_32B(dst + 2 * v8, pk[0], pk[1]);
                     }
                     if (h == 0) ws.sfa2[(size_t)tc.n * ws.m_cap + grow] = scale;
                 }
