@@ -57,11 +57,25 @@ struct GemmShared {
     uint32_t tmem_base;
     int abort;
     int splitk_last;
+};
+// What follows the barriers depends on the instantiation: GEMM1 and the split-K kernels keep
+// small exchange arrays there, the plain GEMM2 its output staging for TMA stores.
+struct GemmScratch {
     alignas(16) float splitk_sum[kSplitKMaxRows][256];   // read and written as float4
     float amax[2][2][kTileM];
 };
+constexpr int kOutStageCols = 32;                                   // bf16 columns per staged piece (64 B rows)
+constexpr int kOutStageBytes = 32 * kOutStageCols * 2;              // one warp's 32 rows: 2 KB
+constexpr int kOutStageTotal = kEpilogueWarps * 2 * kOutStageBytes; // two pieces per warp: 32 KB
+constexpr size_t kGemmCoreBytes = 1024;                             // GemmShared, padded: the staging wants 1 KB alignment
+static_assert(sizeof(GemmShared) <= kGemmCoreBytes, "barrier block grew");
 
-constexpr size_t kGemmSmemBytes = 1024 + (size_t)kStages * kStageBytes + sizeof(GemmShared);
+template <int MODE, bool SPLITK>
+constexpr size_t gemm_smem_bytes() {
+    return 1024 + (size_t)kStages * kStageBytes + kGemmCoreBytes +
+           ((MODE == 2 && !SPLITK) ? (size_t)kOutStageTotal : sizeof(GemmScratch));
+}
+static_assert(gemm_smem_bytes<2, false>() <= 227 * 1024 && gemm_smem_bytes<1, true>() <= 227 * 1024, "shared memory");
 
 struct TileCoord {
     int e, n, row0, rows;
@@ -193,8 +207,8 @@ __device__ __forceinline__ float round_bf16(float x) {
 // (having it in the main kernel cost 5-7 % on mid-size batches through register pressure).
 template <int MODE, bool SPLITK>
 __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
-    const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, Workspace ws,
-    const float* __restrict__ w_scale, int silu_exact)
+    const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+    const __grid_constant__ CUtensorMap tmap_out, Workspace ws, const float* __restrict__ w_scale, int silu_exact)
 {
     constexpr int kKBlocks = (MODE == 1) ? kHiddenBlocks : kInterBlocks;
     constexpr int kTilesN = (MODE == 1) ? (kInter / kBlock) : (kHidden / kTileN);  // 16 / 28
@@ -203,6 +217,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     GemmShared* sh = reinterpret_cast<GemmShared*>(smem_raw + (base - raw_addr) + (size_t)kStages * kStageBytes);
+    uint8_t* after_core = reinterpret_cast<uint8_t*>(sh) + kGemmCoreBytes;   // 1 KB aligned
+    GemmScratch* sc = reinterpret_cast<GemmScratch*>(after_core);           // not in the plain GEMM2
+    (void)sc;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -225,6 +242,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
     if (warp == 0 && lane == 0) {
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
+        if (MODE == 2 && !SPLITK) prefetch_tmap(&tmap_out);
     }
     // Everything above is independent of earlier kernels; from here on their results are read.
     pdl_wait();
@@ -439,7 +457,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                 if (!ok) break;
                 if (!sh->splitk_last) continue;
                 __threadfence();
-                splitk_sum_partials(ws.splitk_partial, &sh->splitk_sum[0][0], tile_id, plan.split, tc.rows,
+                splitk_sum_partials(ws.splitk_partial, &sc->splitk_sum[0][0], tile_id, plan.split, tc.rows,
                                     (int)threadIdx.x - 4 * 32);
                 mbar_arrive(bar);
                 ok = mbar_wait(bar, splitk_uses & 1u, abort_flag);
@@ -447,7 +465,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 if (valid) {
-                    const float4* src = reinterpret_cast<const float4*>(&sh->splitk_sum[row][h * 128]);
+                    const float4* src = reinterpret_cast<const float4*>(&sc->splitk_sum[row][h * 128]);
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const float4 v = src[j];
@@ -470,13 +488,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                     amax = fmaxf(amax, fabsf(v));
                 }
                 const uint32_t tp = tile_iter & 1u;
-                sh->amax[tp][h][row] = amax;
+                sc->amax[tp][h][row] = amax;
                 mbar_arrive(smem_u32(&sh->amax_bar[tp]));
                 ok = mbar_wait(smem_u32(&sh->amax_bar[tp]), (tile_iter >> 1) & 1u, abort_flag);
                 ++tile_iter;
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                const float maxv = fmaxf(amax, sh->amax[tp][h ^ 1][row]);
+                const float maxv = fmaxf(amax, sc->amax[tp][h ^ 1][row]);
                 const float scale = (maxv > 0.0f) ? (maxv / 448.0f) : 1.0f;
                 const float inv_scale = 1.0f / scale;
                 if (valid) {
@@ -502,6 +520,38 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                     }
                     if (h == 0) ws.sfa2[(size_t)tc.n * ws.m_cap + grow] = scale;
                 }
+            } else if (MODE == 2 && !SPLITK) {
+                // Y goes out through shared memory and TMA: a thread owns one row, so direct stores
+                // touch 32 lines per warp instruction and keep the memory pipeline busy for longer
+                // than the MMA look-ahead covers.  Each warp stages its 32 rows in pieces of 32
+                // columns (64-byte rows, 64B-swizzled as the tensor map expects, which also keeps
+                // the staging writes conflict-free), two pieces alternating; rows past the tile's
+                // valid rows land in the expert's padding, which nobody reads.
+                if (warp_has_rows) {
+                    uint8_t* stg = after_core + ew * (2 * kOutStageBytes);
+#pragma unroll
+                    for (int p = 0; p < 128 / kOutStageCols; ++p) {
+                        uint8_t* buf = stg + (p & 1) * kOutStageBytes;
+                        if (lane == 0) bulk_wait_group_read<1>();   // the piece stored from this buffer two pieces ago
+                        __syncwarp();
+#pragma unroll
+                        for (int c4 = 0; c4 < 4; ++c4) {
+                            uint4 pk;
+                            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                h2[i] = __floats2bfloat162_rn(acc[p * kOutStageCols + c4 * 8 + 2 * i],
+                                                              acc[p * kOutStageCols + c4 * 8 + 2 * i + 1]);
+                            *reinterpret_cast<uint4*>(buf + lane * 64 + ((c4 ^ ((lane >> 1) & 3)) * 16)) = pk;
+                        }
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&tmap_out, smem_u32(buf), tc.n * kTileN + 128 * h + p * kOutStageCols, tc.row0 + q * 32);
+                            bulk_commit_group();
+                        }
+                    }
+                }
             } else {
                 if (valid) {
                     uint4* dst = reinterpret_cast<uint4*>(ws.y + (size_t)grow * kHidden + tc.n * kTileN + 128 * h);
@@ -509,16 +559,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                     for (int v8 = 0; v8 < 8; ++v8) {
                         uint4 pk[2];
 #pragma unroll
-                        for (int q = 0; q < 2; ++q) {
-                            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk[q]);
+                        for (int q2 = 0; q2 < 2; ++q2) {
+                            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk[q2]);
 #pragma unroll
                             for (int i = 0; i < 4; ++i)
-                                h2[i] = __floats2bfloat162_rn(acc[v8 * 16 + q * 8 + 2 * i], acc[v8 * 16 + q * 8 + 2 * i + 1]);
+                                h2[i] = __floats2bfloat162_rn(acc[v8 * 16 + q2 * 8 + 2 * i], acc[v8 * 16 + q2 * 8 + 2 * i + 1]);
                         }
                         st_global_32B(dst + 2 * v8, pk[0], pk[1]);
                     }
                 }
             }
+        }
+        if (MODE == 2 && !SPLITK) {
+            if (lane == 0) bulk_wait_group<0>();   // all of this warp's stores performed before the CTA leaves
+            __syncwarp();
         }
     }
 
@@ -597,35 +651,51 @@ int encode_rows_1k_map(void* out_map, const void* base, uint64_t row_bytes, uint
     return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+// bf16 [rows, cols] row-major output; box = 32 columns x 32 rows with the 64-byte swizzle (GEMM2's
+// staged stores).
+int encode_out_bf16_map(void* out_map, void* base, uint64_t cols, uint64_t rows)
+{
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return -1;
+    CUtensorMap* m = static_cast<CUtensorMap*>(out_map);
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kOutStageCols, 32};
+    const cuuint32_t es[2] = {1, 1};
+    const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
 size_t tensor_map_bytes() { return sizeof(CUtensorMap); }
 
 cudaError_t configure_gemm_kernels()
 {
     cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)kGemmSmemBytes);
+                                         (int)gemm_smem_bytes<1, false>());
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(grouped_gemm_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)kGemmSmemBytes);
+                                 (int)gemm_smem_bytes<2, false>());
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(grouped_gemm_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)kGemmSmemBytes);
+                                 (int)gemm_smem_bytes<1, true>());
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(grouped_gemm_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)kGemmSmemBytes);
+                                 (int)gemm_smem_bytes<2, true>());
     return e;
 }
 
 int gemm_tiles_n(int mode) { return mode == 1 ? kInter / kBlock : kHidden / kTileN; }
 
-cudaError_t launch_grouped_gemm(int mode, const void* tmap_a, const void* tmap_b, const Workspace& ws,
+cudaError_t launch_grouped_gemm(int mode, const void* tmap_a, const void* tmap_b, const void* tmap_out, const Workspace& ws,
                                 const float* w_scale, int silu_exact, int num_ctas, int split_k, cudaStream_t stream)
 {
     const CUtensorMap* ma = static_cast<const CUtensorMap*>(tmap_a);
     const CUtensorMap* mb = static_cast<const CUtensorMap*>(tmap_b);
+    const CUtensorMap* mo = static_cast<const CUtensorMap*>(tmap_out);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(num_ctas < 1 ? 1 : num_ctas);
     cfg.blockDim = dim3(kGemmThreads);
-    cfg.dynamicSmemBytes = kGemmSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -633,11 +703,13 @@ cudaError_t launch_grouped_gemm(int mode, const void* tmap_a, const void* tmap_b
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (mode == 1) {
-        if (split_k) return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<1, true>, *ma, *mb, ws, w_scale, silu_exact);
-        return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<1, false>, *ma, *mb, ws, w_scale, silu_exact);
+        cfg.dynamicSmemBytes = split_k ? gemm_smem_bytes<1, true>() : gemm_smem_bytes<1, false>();
+        if (split_k) return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<1, true>, *ma, *mb, *mo, ws, w_scale, silu_exact);
+        return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<1, false>, *ma, *mb, *mo, ws, w_scale, silu_exact);
     }
-    if (split_k) return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<2, true>, *ma, *mb, ws, w_scale, silu_exact);
-    return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<2, false>, *ma, *mb, ws, w_scale, silu_exact);
+    cfg.dynamicSmemBytes = split_k ? gemm_smem_bytes<2, true>() : gemm_smem_bytes<2, false>();
+    if (split_k) return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<2, true>, *ma, *mb, *mo, ws, w_scale, silu_exact);
+    return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<2, false>, *ma, *mb, *mo, ws, w_scale, silu_exact);
 }
 
 }  // namespace moe

@@ -23,9 +23,10 @@ cudaError_t launch_combine_push(const Workspace&, const ExchangeView&, int, cuda
 cudaError_t launch_reduce_owned(const Workspace&, const ExchangeView&, int, void*, cudaStream_t);
 int encode_kmajor_u8_map(void*, const void*, uint64_t, uint64_t, uint64_t, uint32_t);
 int encode_rows_1k_map(void*, const void*, uint64_t, uint64_t, uint32_t);
+int encode_out_bf16_map(void*, void*, uint64_t, uint64_t);
 size_t tensor_map_bytes();
 cudaError_t configure_gemm_kernels();
-cudaError_t launch_grouped_gemm(int, const void*, const void*, const Workspace&, const float*, int, int, int,
+cudaError_t launch_grouped_gemm(int, const void*, const void*, const void*, const Workspace&, const float*, int, int, int,
                                 cudaStream_t);
 int gemm_tiles_n(int mode);
 }  // namespace moe
@@ -108,6 +109,7 @@ struct moe_fp8_b200_ctx {
     Workspace ws{};
     alignas(64) unsigned char tmap_a1[128];
     alignas(64) unsigned char tmap_a2[128];
+    alignas(64) unsigned char tmap_y[128];    // GEMM2's staged output stores
     alignas(64) unsigned char tmap_w1[128];
     alignas(64) unsigned char tmap_w2[128];
     alignas(64) unsigned char tmap_dec_w1[128];   // the decode kernel's views of the same weights
@@ -269,11 +271,11 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
     if (e == cudaSuccess && stop >= 2) e = launch_permute(a.hidden_states, a.hidden_states_scale, h->ws, T, stream);
     mark(3);
     if (e == cudaSuccess && stop >= 3)
-        e = launch_grouped_gemm(1, h->tmap_a1, h->tmap_w1, h->ws, a.gemm1_weights_scale, h->opt_exact_silu,
+        e = launch_grouped_gemm(1, h->tmap_a1, h->tmap_w1, h->tmap_y, h->ws, a.gemm1_weights_scale, h->opt_exact_silu,
                                 ctas(1), split_k, stream);
     mark(4);
     if (e == cudaSuccess && stop >= 4)
-        e = launch_grouped_gemm(2, h->tmap_a2, h->tmap_w2, h->ws, a.gemm2_weights_scale, 0, ctas(2), split_k, stream);
+        e = launch_grouped_gemm(2, h->tmap_a2, h->tmap_w2, h->tmap_y, h->ws, a.gemm2_weights_scale, 0, ctas(2), split_k, stream);
     mark(5);
     if (e == cudaSuccess && stop >= 5 && finalize) {
         if (ex) {
@@ -402,6 +404,7 @@ int moe_fp8_b200_create(moe_fp8_b200_handle* out, int device, int max_tokens, in
         if (tensor_map_bytes() > sizeof(h->tmap_a1)) mr = -100;
         if (mr == 0) mr = encode_kmajor_u8_map(h->tmap_a1, w.a1, kHidden, L.m_cap, 0, kTileM);
         if (mr == 0) mr = encode_kmajor_u8_map(h->tmap_a2, w.a2, kInter, L.m_cap, 0, kTileM);
+        if (mr == 0) mr = encode_out_bf16_map(h->tmap_y, w.y, kHidden, L.m_cap);
     }
     if (e != cudaSuccess || mr != 0) {
         const int rc = (e != cudaSuccess)
