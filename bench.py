@@ -400,12 +400,8 @@ def run_ours(args, rank, world, local):
                 layer.host_wait(pipe["tickets"][-1])
     else:
         def e2e_step():
-            dev[0].copy_(pin[0], non_blocking=True)
-            dev[2].copy_(pin[1], non_blocking=True)
-            dev[3].copy_(pin[2], non_blocking=True)
-            res = step()
-            host_out[:res.shape[0]].copy_(res, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+            # every rank copies only its token slice over PCIe; NVLink all-gathers the rest
+            moe.run_host(pin[0], dev[1], pin[1], pin[2], w1, s1, w2, s2, RSF, host_out, mode=args.collective)
     e2e_sync_ms = None
     if args.skip_e2e:
         e2e_ms = float("nan")
@@ -414,7 +410,7 @@ def run_ours(args, rank, world, local):
         e2e_sync_ms = time_steps(e2e_sync_step, max(3, args.steps // 3), 2, world)
     else:
         e2e_ms = time_steps(e2e_step, max(3, args.steps // 2), 3, world)
-    h2d = sum(x.numel() * x.element_size() for x in pin)
+    h2d = sum(x.numel() * x.element_size() for x in pin) // world   # per rank: its token slice
     d2h = (host_out if (world == 1 or args.collective == "all_reduce") else scat).numel() * 2
     other_ms = None
     if world > 1:
@@ -446,8 +442,10 @@ def run_ours(args, rank, world, local):
                 "path": "moe_fp8_b200_run_host_async + host_wait (C ABI, pinned host buffers, two calls in flight: copy-in of step "
                         "i+1 and copy-out of step i-1 overlap the compute of step i); sync_call_ms_per_step = one blocking "
                         "moe_fp8_b200_run_host per step" if world == 1
-                        else ("pinned H2D + moe_fp8_b200_run_reduce_scatter (peer stores) + D2H" if args.collective == "fused"
-                              else f"pinned H2D + moe_fp8_b200_run + NCCL {args.collective} + D2H")},
+                        else ("ShardedMoe.run_host: pinned H2D of the rank's token slice + NCCL all-gather of the inputs + "
+                              + ("moe_fp8_b200_run_reduce_scatter (peer stores)" if args.collective == "fused"
+                                 else f"moe_fp8_b200_run + NCCL {args.collective}") + " + D2H of the rank's output slice; "
+                              "bytes are per rank")},
         "gpu_launches": (6 if (world > 1 and args.collective == "fused") else 5) * args.steps * world,
         "stage_ms": {k: round(max_over_ranks(v, world), 4) for k, v in stages.items()},
         "layer_tflops": round(rows_max * FLOPS_PER_ROW / (ms * 1e-3) / 1e12, 1),

@@ -79,6 +79,7 @@ class ShardedMoe:
         self.max_tokens = max_tokens
         self._exchange = None   # (symmetric buffer, handle, peer pointers, bytes), made on first fused run
         self._epoch = 0
+        self._host_stage = None   # device staging of run_host
 
     def _ensure_exchange(self):
         """Allocate and exchange the receive buffers (torch symmetric memory: plumbing only;
@@ -115,6 +116,56 @@ class ShardedMoe:
             routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
             gemm2_weights, gemm2_weights_scale, self.local_expert_offset, routed_scaling_factor, scatter_out,
             ptrs, nbytes, self.rank, self.world, self._epoch)
+
+    def run_host(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                 gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, routed_scaling_factor, output,
+                 mode: str = "fused"):
+        """The per-call tensors live in HOST memory (every rank sees the same pinned `routing_logits`
+        [T,256], `hidden_states` [T,7168], `hidden_states_scale` [56,T] and `output` [T,7168]).  A rank
+        copies only ITS token slice over PCIe, the slices are all-gathered over NVLink (every rank
+        routes all tokens), the layer runs with the reduce-scatter fused in, and the rank writes its
+        slice of the summed output back to `output[lo:hi]`.  T must be a multiple of the group size.
+        Synchronises before returning."""
+        T = int(routing_logits.shape[0])
+        W = self.world
+        if T % W:
+            raise ValueError(f"T = {T} must be a multiple of the group size {W}")
+        per = T // W
+        lo = self.rank * per
+        dev = torch.device("cuda", self.layer.device)
+        st = self._host_stage
+        if st is None or st["T"] != T:
+            st = dict(T=T,
+                      logits=torch.empty((T, NE), dtype=torch.float32, device=dev),
+                      hidden=torch.empty((T, 7168), dtype=torch.float8_e4m3fn, device=dev),
+                      scale_parts=torch.empty((W, 56, per), dtype=torch.float32, device=dev),
+                      scale=torch.empty((56, T), dtype=torch.float32, device=dev),
+                      out=torch.empty((per, 7168), dtype=torch.bfloat16, device=dev),
+                      full=torch.empty((T, 7168), dtype=torch.bfloat16, device=dev))
+            self._host_stage = st
+        g = self.group
+        # this rank's slice, straight into its place in the gathered tensors
+        st["logits"][lo:lo + per].copy_(routing_logits[lo:lo + per], non_blocking=True)
+        st["hidden"][lo:lo + per].view(torch.uint8).copy_(hidden_states[lo:lo + per].view(torch.uint8), non_blocking=True)
+        st["scale_parts"][self.rank].copy_(hidden_states_scale[:, lo:lo + per], non_blocking=True)
+        if W > 1:
+            dist.all_gather_into_tensor(st["logits"], st["logits"][lo:lo + per], group=g)
+            dist.all_gather_into_tensor(st["hidden"].view(torch.uint8), st["hidden"][lo:lo + per].view(torch.uint8), group=g)
+            dist.all_gather_into_tensor(st["scale_parts"], st["scale_parts"][self.rank], group=g)
+        st["scale"].view(56, W, per).copy_(st["scale_parts"].permute(1, 0, 2))
+        if mode == "fused" and W > 1:
+            res = self.run_fused(st["logits"], routing_bias, st["hidden"], st["scale"], gemm1_weights, gemm1_weights_scale,
+                                 gemm2_weights, gemm2_weights_scale, routed_scaling_factor, scatter_out=st["out"])
+        else:
+            res = self.run(st["logits"], routing_bias, st["hidden"], st["scale"], gemm1_weights, gemm1_weights_scale,
+                           gemm2_weights, gemm2_weights_scale, routed_scaling_factor, st["full"],
+                           mode="reduce_scatter" if mode == "fused" else mode, scatter_out=st["out"])
+        if mode == "all_reduce":
+            output.copy_(res, non_blocking=True)
+        else:
+            output[lo:lo + per].copy_(res[:per], non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+        return output
 
     def run(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
             gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, routed_scaling_factor, output,

@@ -69,6 +69,16 @@ def _worker(rank, world, port, T, q):
             got = moe.run(*dev, *w, 2.5, out, mode="fused")
             moe.layer.check()
             ok_fused = ok_fused and got.shape[0] == (T + world - 1) // world and torch.equal(got[:hi - lo], want[lo:hi])
+        # host-resident inputs: every rank copies its token slice, NVLink all-gathers the rest
+        if T % world == 0:
+            pin = [x.pin_memory() for x in (logits, hidden, hscale)]
+            host_out = torch.zeros(T, 7168, dtype=torch.bfloat16).pin_memory()
+            for mode in ("fused", "reduce_scatter"):
+                host_out.zero_()
+                dist.barrier()
+                moe.run_host(pin[0], dev[1], pin[1], pin[2], *w, 2.5, host_out, mode=mode)
+                moe.layer.check()
+                ok_fused = ok_fused and torch.equal(host_out[lo:hi], want[lo:hi].cpu())
         q.put((rank, ok_sum, ok_scatter and ok_fused, nonzero))
     finally:
         dist.destroy_process_group()
