@@ -406,7 +406,7 @@ def run_ours(args, rank, world, local):
     if args.skip_e2e:
         e2e_ms = float("nan")
     elif world == 1:
-        e2e_ms = time_steps(e2e_step, max(4, args.steps // 2), 3, world, drain=e2e_drain)
+        e2e_ms = time_steps(e2e_step, max(10, args.steps // 2), 3, world, drain=e2e_drain)
         e2e_sync_ms = time_steps(e2e_sync_step, max(3, args.steps // 3), 2, world)
     else:
         e2e_ms = time_steps(e2e_step, max(3, args.steps // 2), 3, world)
