@@ -409,7 +409,12 @@ def run_ours(args, rank, world, local):
         e2e_ms = time_steps(e2e_step, max(10, args.steps // 2), 3, world, drain=e2e_drain)
         e2e_sync_ms = time_steps(e2e_sync_step, max(3, args.steps // 3), 2, world)
     else:
-        e2e_ms = time_steps(e2e_step, max(3, args.steps // 2), 3, world)
+        try:
+            e2e_ms = time_steps(e2e_step, max(3, args.steps // 2), 3, world)
+        except Exception as ex:   # the device-resident number must not be lost to a host-path failure
+            sys.stderr.write(f"end-to-end leg failed on rank {rank}: {ex}\n")
+            e2e_ms = float("nan")
+            args.skip_e2e = True
     h2d = sum(x.numel() * x.element_size() for x in pin) // world   # per rank: its token slice
     d2h = (host_out if (world == 1 or args.collective == "all_reduce") else scat).numel() * 2
     other_ms = None
