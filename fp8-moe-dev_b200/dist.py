@@ -63,6 +63,22 @@ def combine_partials(partial: torch.Tensor, mode: str = "all_reduce", group=None
     raise ValueError(f"unknown mode {mode!r}")
 
 
+def gather_token_slices(logits: torch.Tensor, hidden_u8: torch.Tensor, scale_parts: torch.Tensor,
+                        scale_out: torch.Tensor, rank: int, world: int, group=None) -> None:
+    """Completes the replicated inputs from per-rank token slices, in place.  On entry rank r has
+    filled rows [r*per, (r+1)*per) of `logits` [T,256] and `hidden_u8` [T,7168] and its own
+    `scale_parts[r]` ([56, per]: its columns of the [56,T] scale matrix); on return every rank
+    holds all rows, and `scale_out` [56,T] holds the scales in the layer's layout.  Any backend."""
+    T = logits.shape[0]
+    per = T // world
+    lo = rank * per
+    if world > 1:
+        # flat views: every rank's piece is one contiguous run at offset rank * count (in-place gather)
+        for t, mine in ((logits, logits[lo:lo + per]), (hidden_u8, hidden_u8[lo:lo + per]), (scale_parts, scale_parts[rank])):
+            dist.all_gather_into_tensor(t.view(-1), mine.reshape(-1), group=group)
+    scale_out.view(scale_out.shape[0], world, per).copy_(scale_parts.permute(1, 0, 2))
+
+
 class ShardedMoe:
     """One rank's share of the 256-expert layer plus the cross-rank sum."""
 
@@ -148,11 +164,7 @@ class ShardedMoe:
         st["logits"][lo:lo + per].copy_(routing_logits[lo:lo + per], non_blocking=True)
         st["hidden"][lo:lo + per].view(torch.uint8).copy_(hidden_states[lo:lo + per].view(torch.uint8), non_blocking=True)
         st["scale_parts"][self.rank].copy_(hidden_states_scale[:, lo:lo + per], non_blocking=True)
-        if W > 1:
-            dist.all_gather_into_tensor(st["logits"], st["logits"][lo:lo + per], group=g)
-            dist.all_gather_into_tensor(st["hidden"].view(torch.uint8), st["hidden"][lo:lo + per].view(torch.uint8), group=g)
-            dist.all_gather_into_tensor(st["scale_parts"], st["scale_parts"][self.rank], group=g)
-        st["scale"].view(56, W, per).copy_(st["scale_parts"].permute(1, 0, 2))
+        gather_token_slices(st["logits"], st["hidden"].view(torch.uint8), st["scale_parts"], st["scale"], self.rank, W, g)
         if mode == "fused" and W > 1:
             res = self.run_fused(st["logits"], routing_bias, st["hidden"], st["scale"], gemm1_weights, gemm1_weights_scale,
                                  gemm2_weights, gemm2_weights_scale, routed_scaling_factor, scatter_out=st["out"])

@@ -100,3 +100,53 @@ def test_shard_sum_identity_on_the_oracle(oracle):
                [(int(pb[1][t, p]) + 32, float(pb[2][t, p])) for p in range(pb[0][t])]
         got = [(int(ple[t, p]), float(pw[t, p])) for p in range(pc[t])]
         assert got == want
+
+
+def _gather_worker(rank, world, port, T, q):
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    sys.path.insert(0, str(root))
+    import __graft_entry__ as entry
+    entry.load_package()
+    from fp8_moe_dev_b200.dist import gather_token_slices
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(99)
+        logits = torch.randn(T, 256, generator=g)
+        hidden = torch.randint(0, 256, (T, 64), generator=g, dtype=torch.uint8)   # narrow stand-in for [T, 7168]
+        scale = torch.rand(56, T, generator=g)
+        per = T // world
+        lo = rank * per
+        # what a rank has after copying only its token slice from host memory
+        my_logits = torch.full((T, 256), float("nan"))
+        my_hidden = torch.zeros(T, 64, dtype=torch.uint8)
+        parts = torch.full((world, 56, per), float("nan"))
+        my_logits[lo:lo + per] = logits[lo:lo + per]
+        my_hidden[lo:lo + per] = hidden[lo:lo + per]
+        parts[rank] = scale[:, lo:lo + per]
+        out_scale = torch.empty(56, T)
+        gather_token_slices(my_logits, my_hidden, parts, out_scale, rank, world)
+        ok = torch.equal(my_logits, logits) and torch.equal(my_hidden, hidden) and torch.equal(out_scale, scale)
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_token_slices_are_gathered_into_the_replicated_inputs():
+    """The multi-GPU host path: each rank brings its token slice, everybody ends with all tokens
+    and with the [56, T] scale matrix in the layer's layout (two gloo ranks)."""
+    world, T = 2, 24
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gather_worker, args=(r, world, port, T, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    res = dict(q.get(timeout=10) for _ in range(world))
+    assert res == {0: True, 1: True}
