@@ -399,9 +399,21 @@ def run_ours(args, rank, world, local):
             if pipe["tickets"]:
                 layer.host_wait(pipe["tickets"][-1])
     else:
+        host_out2 = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+
         def e2e_step():
-            # every rank copies only its token slice over PCIe; NVLink all-gathers the rest
-            moe.run_host(pin[0], dev[1], pin[1], pin[2], w1, s1, w2, s2, RSF, host_out, mode=args.collective)
+            # every rank copies only its token slice over PCIe, NVLink all-gathers the rest; two calls in
+            # flight, the output of step i-1 is awaited right after step i has been issued
+            i = pipe["i"]
+            pipe["tickets"].append(moe.run_host_async(pin[0], dev[1], pin[1], pin[2], w1, s1, w2, s2, RSF,
+                                                      host_out if i % 2 == 0 else host_out2, mode=args.collective))
+            if i >= 1:
+                moe.host_wait(pipe["tickets"][i - 1])
+            pipe["i"] = i + 1
+
+        def e2e_drain():
+            if pipe["tickets"]:
+                moe.host_wait(pipe["tickets"][-1])
     e2e_sync_ms = None
     if args.skip_e2e:
         e2e_ms = float("nan")
@@ -410,7 +422,7 @@ def run_ours(args, rank, world, local):
         e2e_sync_ms = time_steps(e2e_sync_step, max(3, args.steps // 3), 2, world)
     else:
         try:
-            e2e_ms = time_steps(e2e_step, max(3, args.steps // 2), 3, world)
+            e2e_ms = time_steps(e2e_step, max(10, args.steps // 2), 3, world, drain=e2e_drain)
         except Exception as ex:   # the device-resident number must not be lost to a host-path failure
             sys.stderr.write(f"end-to-end leg failed on rank {rank}: {ex}\n")
             e2e_ms = float("nan")
@@ -447,7 +459,7 @@ def run_ours(args, rank, world, local):
                 "path": "moe_fp8_b200_run_host_async + host_wait (C ABI, pinned host buffers, two calls in flight: copy-in of step "
                         "i+1 and copy-out of step i-1 overlap the compute of step i); sync_call_ms_per_step = one blocking "
                         "moe_fp8_b200_run_host per step" if world == 1
-                        else ("ShardedMoe.run_host: pinned H2D of the rank's token slice + NCCL all-gather of the inputs + "
+                        else ("ShardedMoe.run_host_async + host_wait (two calls in flight): pinned H2D of the rank's token slice + NCCL all-gather of the inputs + "
                               + ("moe_fp8_b200_run_reduce_scatter (peer stores)" if args.collective == "fused"
                                  else f"moe_fp8_b200_run + NCCL {args.collective}") + " + D2H of the rank's output slice; "
                               "bytes are per rank")},

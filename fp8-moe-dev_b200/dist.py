@@ -95,7 +95,8 @@ class ShardedMoe:
         self.max_tokens = max_tokens
         self._exchange = None   # (symmetric buffer, handle, peer pointers, bytes), made on first fused run
         self._epoch = 0
-        self._host_stage = None   # device staging of run_host
+        self._host_stage = None   # device staging of the host entry points (two sets)
+        self._host_seq = 0
 
     def _ensure_exchange(self):
         """Allocate and exchange the receive buffers (torch symmetric memory: plumbing only;
@@ -133,15 +134,40 @@ class ShardedMoe:
             gemm2_weights, gemm2_weights_scale, self.local_expert_offset, routed_scaling_factor, scatter_out,
             ptrs, nbytes, self.rank, self.world, self._epoch)
 
-    def run_host(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
-                 gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, routed_scaling_factor, output,
-                 mode: str = "fused"):
+    def _host_stage_set(self, T: int, which: int):
+        """Device staging of the host entry points: two sets, so that a call's copies can overlap
+        the neighbouring calls' compute."""
+        W = self.world
+        per = T // W
+        dev = torch.device("cuda", self.layer.device)
+        if self._host_stage is None or self._host_stage[0]["T"] != T:
+            def one():
+                return dict(T=T,
+                            logits=torch.empty((T, NE), dtype=torch.float32, device=dev),
+                            hidden=torch.empty((T, 7168), dtype=torch.float8_e4m3fn, device=dev),
+                            scale_parts=torch.empty((W, 56, per), dtype=torch.float32, device=dev),
+                            scale=torch.empty((56, T), dtype=torch.float32, device=dev),
+                            out=torch.empty((per, 7168), dtype=torch.bfloat16, device=dev),
+                            full=torch.empty((T, 7168), dtype=torch.bfloat16, device=dev),
+                            ev_in=torch.cuda.Event(), ev_compute=torch.cuda.Event(), ev_out=torch.cuda.Event())
+            torch.cuda.synchronize(dev)
+            self._host_stage = [one(), one()]
+            self._host_seq = 0
+            self._s_in = torch.cuda.Stream(dev)
+            self._s_out = torch.cuda.Stream(dev)
+        return self._host_stage[which]
+
+    def run_host_async(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                       gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, routed_scaling_factor, output,
+                       mode: str = "fused") -> int:
         """The per-call tensors live in HOST memory (every rank sees the same pinned `routing_logits`
         [T,256], `hidden_states` [T,7168], `hidden_states_scale` [56,T] and `output` [T,7168]).  A rank
         copies only ITS token slice over PCIe, the slices are all-gathered over NVLink (every rank
         routes all tokens), the layer runs with the reduce-scatter fused in, and the rank writes its
-        slice of the summed output back to `output[lo:hi]`.  T must be a multiple of the group size.
-        Synchronises before returning."""
+        slice of the summed output back to `output[lo:hi]` (`all_reduce`: all of `output`).  T must be
+        a multiple of the group size.  Returns a ticket at once; the host tensors must stay untouched
+        until `host_wait(ticket)`, and at most two calls may be in flight.  Copy-in, compute and
+        copy-out run on three streams, so consecutive calls overlap them."""
         T = int(routing_logits.shape[0])
         W = self.world
         if T % W:
@@ -149,22 +175,24 @@ class ShardedMoe:
         per = T // W
         lo = self.rank * per
         dev = torch.device("cuda", self.layer.device)
-        st = self._host_stage
-        if st is None or st["T"] != T:
-            st = dict(T=T,
-                      logits=torch.empty((T, NE), dtype=torch.float32, device=dev),
-                      hidden=torch.empty((T, 7168), dtype=torch.float8_e4m3fn, device=dev),
-                      scale_parts=torch.empty((W, 56, per), dtype=torch.float32, device=dev),
-                      scale=torch.empty((56, T), dtype=torch.float32, device=dev),
-                      out=torch.empty((per, 7168), dtype=torch.bfloat16, device=dev),
-                      full=torch.empty((T, 7168), dtype=torch.bfloat16, device=dev))
-            self._host_stage = st
-        g = self.group
-        # this rank's slice, straight into its place in the gathered tensors
-        st["logits"][lo:lo + per].copy_(routing_logits[lo:lo + per], non_blocking=True)
-        st["hidden"][lo:lo + per].view(torch.uint8).copy_(hidden_states[lo:lo + per].view(torch.uint8), non_blocking=True)
-        st["scale_parts"][self.rank].copy_(hidden_states_scale[:, lo:lo + per], non_blocking=True)
-        gather_token_slices(st["logits"], st["hidden"].view(torch.uint8), st["scale_parts"], st["scale"], self.rank, W, g)
+        self._host_stage_set(T, 0)
+        seq = self._host_seq
+        self._host_seq += 1
+        st = self._host_stage[seq & 1]
+        cur = torch.cuda.current_stream(dev)
+        with torch.cuda.stream(self._s_in):
+            if seq >= 2:
+                self._s_in.wait_event(st["ev_compute"])   # the set's inputs were read two calls ago
+            # this rank's slice, straight into its place in the gathered tensors
+            st["logits"][lo:lo + per].copy_(routing_logits[lo:lo + per], non_blocking=True)
+            st["hidden"][lo:lo + per].view(torch.uint8).copy_(hidden_states[lo:lo + per].view(torch.uint8), non_blocking=True)
+            st["scale_parts"][self.rank].copy_(hidden_states_scale[:, lo:lo + per], non_blocking=True)
+            st["ev_in"].record(self._s_in)
+        cur.wait_event(st["ev_in"])
+        if seq >= 2:
+            cur.wait_event(st["ev_out"])                  # the set's output was copied out two calls ago
+        gather_token_slices(st["logits"], st["hidden"].view(torch.uint8), st["scale_parts"], st["scale"], self.rank, W,
+                            self.group)
         if mode == "fused" and W > 1:
             res = self.run_fused(st["logits"], routing_bias, st["hidden"], st["scale"], gemm1_weights, gemm1_weights_scale,
                                  gemm2_weights, gemm2_weights_scale, routed_scaling_factor, scatter_out=st["out"])
@@ -172,12 +200,29 @@ class ShardedMoe:
             res = self.run(st["logits"], routing_bias, st["hidden"], st["scale"], gemm1_weights, gemm1_weights_scale,
                            gemm2_weights, gemm2_weights_scale, routed_scaling_factor, st["full"],
                            mode="reduce_scatter" if mode == "fused" else mode, scatter_out=st["out"])
-        if mode == "all_reduce":
-            output.copy_(res, non_blocking=True)
-        else:
-            output[lo:lo + per].copy_(res[:per], non_blocking=True)
-        torch.cuda.current_stream(dev).synchronize()
-        return output
+        st["ev_compute"].record(cur)
+        with torch.cuda.stream(self._s_out):
+            self._s_out.wait_event(st["ev_compute"])
+            if mode == "all_reduce":
+                output.copy_(res, non_blocking=True)
+            else:
+                output[lo:lo + per].copy_(res[:per], non_blocking=True)
+            st["ev_out"].record(self._s_out)
+        return seq
+
+    def host_wait(self, ticket: int) -> None:
+        """Blocks until the output of call `ticket` is in host memory."""
+        if self._host_stage is None or not 0 <= ticket < self._host_seq:
+            raise ValueError(f"ticket {ticket} was never issued")
+        if ticket + 2 < self._host_seq:
+            return   # its staging set has been reused since: long finished
+        self._host_stage[ticket & 1]["ev_out"].synchronize()
+
+    def run_host(self, *args, **kwargs):
+        """Blocking form of run_host_async."""
+        ticket = self.run_host_async(*args, **kwargs)
+        self.host_wait(ticket)
+        return args[9] if len(args) > 9 else kwargs.get("output")
 
     def run(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
             gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, routed_scaling_factor, output,

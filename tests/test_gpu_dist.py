@@ -79,6 +79,19 @@ def _worker(rank, world, port, T, q):
                 moe.run_host(pin[0], dev[1], pin[1], pin[2], *w, 2.5, host_out, mode=mode)
                 moe.layer.check()
                 ok_fused = ok_fused and torch.equal(host_out[lo:hi], want[lo:hi].cpu())
+            # the same kept two deep in flight over two output buffers
+            outs = [torch.zeros(T, 7168, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+            tickets = []
+            for i in range(4):
+                if i >= 2:
+                    moe.host_wait(tickets[i - 2])
+                    ok_fused = ok_fused and torch.equal(outs[i % 2][lo:hi], want[lo:hi].cpu())
+                    outs[i % 2].zero_()
+                tickets.append(moe.run_host_async(pin[0], dev[1], pin[1], pin[2], *w, 2.5, outs[i % 2], mode="fused"))
+            for i in (2, 3):
+                moe.host_wait(tickets[i])
+                ok_fused = ok_fused and torch.equal(outs[i % 2][lo:hi], want[lo:hi].cpu())
+            moe.layer.check()
         q.put((rank, ok_sum, ok_scatter and ok_fused, nonzero))
     finally:
         dist.destroy_process_group()
