@@ -292,9 +292,23 @@ def small_config_latencies(pkg, weights, bias_dev, reference_mod=None):
             run()
         torch.cuda.synchronize()
         wall = (time.perf_counter() - t0) / 100 * 1e6
+        timeline = None
+        if T <= 8:
+            # the decode kernel's own phase clock (CTA 0, ns), median over 20 eager runs
+            import numpy as np
+            names = ("tables", "phase1_gemm1_swiglu", "barrier1_wait", "phase2_requant_gemm2", "barrier2_wait", "combine")
+            acc = []
+            for _ in range(20):
+                run()
+                layer.check()
+                tl = layer.read("decode_timeline", 8).astype(np.int64)
+                acc.append(np.diff(tl[:7]))
+            med = np.median(np.array(acc), axis=0)
+            timeline = {n: round(float(v) / 1e3, 2) for n, v in zip(names, med)}
         out.append({"workload": f"T={T}, 32 experts, offset {off}", "latency_us": round(lat, 2),
                     "eager_wall_us_per_call": round(wall, 2),
                     "tokens_per_s": round(T / lat * 1e6, 1), "routed_rows": rows,
+                    "decode_kernel_timeline_us": timeline,
                     "eager_latency_us": round(eager, 2),
                     "how": f"median of {reps} CUDA-graph replays of the whole layer (routing included)"})
         layer.close()
