@@ -417,3 +417,28 @@ def test_pipelined_host_entry_point(pkg, layer32):
     layer32.check()
     with pytest.raises(Exception):
         layer32.host_wait(99)
+
+
+@pytest.mark.parametrize("T,offset,decode", [(3, 160, True), (8, 224, True), (9, 0, False), (17, 96, False),
+                                             (31, 32, False), (47, 128, False), (64, 192, False), (5, 64, False)])
+def test_layer_vs_oracle_across_the_path_boundaries(pkg, oracle, T, offset, decode):
+    """Batch sizes on both sides of the internal path choices (decode kernel up to 8 tokens, chain
+    with and without the small-batch GEMM instantiation, exact / pruning dispatch from 32 tokens on),
+    every shard offset once: same bounds against the oracle as the fixed cases above."""
+    lay = pkg.MoeLayer(64, 32, 0)
+    lay.set_decode_kernel(decode)
+    try:
+        inputs = hp.cpu_inputs(T, seed=3000 + T)
+        weights = hp.gpu_shard(offset, 32)
+        got = hp.run_layer(lay, inputs, weights, offset).float().cpu().numpy()
+        pc = lay.read("pair_count", T)
+    finally:
+        lay.close()
+    w1, s1, w2, s2 = weights
+    ref, rows = oracle.layer(inputs[0].numpy(), hp.np_u16(inputs[1]), hp.np_u8(inputs[2]), inputs[3].numpy(),
+                             hp.np_u8(w1), s1.cpu().numpy(), hp.np_u8(w2), s2.cpu().numpy(), offset, RSF)
+    assert np.isfinite(got).all() and int(pc.sum()) == rows
+    assert np.all(got[pc == 0] == 0)
+    if rows:
+        st = hp.error_stats(got, oracle.bf16_decode(ref))
+        assert st["rel_l2"] < 2e-2 and st["contest_ratio"] >= 0.999, st
