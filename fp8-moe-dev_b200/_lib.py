@@ -14,7 +14,7 @@ LIB_PATH = HERE / "libmoe_fp8_b200.so"
 OK = 0
 ERR_INVALID_ARGUMENT, ERR_CUDA, ERR_CAPACITY, ERR_DEVICE, ERR_UNSUPPORTED = -1, -2, -3, -4, -5
 OPT_REFERENCE_PRUNING, OPT_EXACT_SILU, OPT_STAGE_TIMING = 1, 2, 3
-OPT_STOP_AFTER_STAGE, OPT_DECODE_KERNEL = 4, 5
+OPT_STOP_AFTER_STAGE, OPT_DECODE_KERNEL, OPT_EXPERT_STRIDE = 4, 5, 6
 DECODE_MAX_TOKENS = 8
 
 BUF = dict(

@@ -41,6 +41,13 @@ struct DispatchPolicy {
     float drop_second_frac_2;    // prune: second dropped when w2 <= frac * sum (0 = never),
     float drop_second_frac_ge3;  //        separate fractions for 2 and for >=3 local experts
     int renorm;             // prune: kept weights rescaled by sum(local) / sum(kept)
+    // Which global experts are local.  stride <= 1: the contiguous block [local_expert_offset,
+    // local_expert_offset + E) as in the reference.  stride S > 1 (multi-GPU wrapper only): every
+    // S-th expert, global id g is local iff g % S == phase, with local index g / S; the policy above
+    // is still evaluated per 32-expert shard of GLOBAL ids, so the ranks' pairs together are exactly
+    // those of the reference's shard calls.
+    int expert_stride;
+    int expert_phase;
 };
 
 // Integer control block.  Zeroed when the handle is created; after that the last CTA of the

@@ -103,6 +103,7 @@ struct moe_fp8_b200_ctx {
     bool counters_dirty = false;
     int opt_stop_after = 0;   // diagnostics: enqueue only the first N stages (0 = all)
     int opt_decode = 1;       // single-kernel path for batches of at most kDecodeMaxTokens tokens
+    int opt_expert_stride = 1;   // > 1: strided expert placement (multi-GPU wrapper)
     int decode_ctas_per_sm = 0;
     uint8_t* base = nullptr;
     Layout layout{};
@@ -187,6 +188,11 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
         std::memset(&pol, 0, sizeof(pol));
         pol.keep_limit = 3;
     }
+    pol.expert_stride = h->opt_expert_stride;
+    pol.expert_phase = (int)a.local_expert_offset;
+    if (h->opt_expert_stride > 1 && a.local_expert_offset >= h->opt_expert_stride)
+        return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "with expert stride %d local_expert_offset is the phase and must be < %d",
+                    h->opt_expert_stride, h->opt_expert_stride);
     if (a.gemm1_weights != h->cached_w1) {
         const int r = encode_kmajor_u8_map(h->tmap_w1, a.gemm1_weights, kHidden, kGemm1Out, E, 128);
         if (r != 0) return fail(h, MOE_FP8_B200_ERR_CUDA, "cuTensorMapEncodeTiled(W1) failed: %d", r);
@@ -220,7 +226,7 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
         e = cudaMemsetAsync(h->ws.ctrl, 0, sizeof(Control), stream);
         h->counters_dirty = false;
     }
-    if (h->opt_decode && h->decode_ctas_per_sm > 0 && T <= kDecodeMaxTokens && finalize && !ex &&
+    if (h->opt_decode && h->decode_ctas_per_sm > 0 && T <= kDecodeMaxTokens && finalize && !ex && h->opt_expert_stride <= 1 &&
         h->opt_stop_after == 0) {
         // the whole layer as one cooperative kernel, one CTA per SM
         DecodeArgs d;
@@ -450,6 +456,13 @@ int moe_fp8_b200_set_option(moe_fp8_b200_handle h, int option, int value)
         case MOE_FP8_B200_OPT_EXACT_SILU: h->opt_exact_silu = value ? 1 : 0; return MOE_FP8_B200_OK;
         case MOE_FP8_B200_OPT_STOP_AFTER_STAGE: h->opt_stop_after = value; return MOE_FP8_B200_OK;
         case MOE_FP8_B200_OPT_DECODE_KERNEL: h->opt_decode = value ? 1 : 0; return MOE_FP8_B200_OK;
+        case MOE_FP8_B200_OPT_EXPERT_STRIDE:
+            if (value != 1 && !((value == 2 || value == 4 || value == 8) && h->num_local_experts * value == kNumExperts))
+                return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT,
+                            "expert stride %d needs 2, 4 or 8 and num_local_experts * stride == 256 (handle has %d)", value,
+                            h->num_local_experts);
+            h->opt_expert_stride = value;
+            return MOE_FP8_B200_OK;
         case MOE_FP8_B200_OPT_STAGE_TIMING:
             h->opt_stage_timing = value ? 1 : 0;
             h->timed_runs = 0;

@@ -108,9 +108,26 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_dispatch_kernel(
     }
 
     if (lane == 0) {
-        const int shards = num_local_experts / kShardExperts;
-        for (int sh = 0; sh < shards; ++sh) {
-            dispatch_one_shard(idx, wn, sh, local_expert_offset, pol, rsf, n_pairs, p_le, p_w);
+        if (pol.expert_stride <= 1) {
+            const int shards = num_local_experts / kShardExperts;
+            for (int sh = 0; sh < shards; ++sh) {
+                dispatch_one_shard(idx, wn, sh, local_expert_offset, pol, rsf, n_pairs, p_le, p_w);
+            }
+        } else {
+            // strided placement: the policy runs on every global shard, this rank keeps its experts
+            for (int sh = 0; sh < kNumExperts / kShardExperts; ++sh) {
+                int n_sh = 0;
+                int g_le[kTopK];
+                float g_w[kTopK];
+#pragma unroll
+                for (int i = 0; i < kTopK; ++i) { g_le[i] = 0; g_w[i] = 0.0f; }
+                dispatch_one_shard(idx, wn, sh, 0, pol, rsf, n_sh, g_le, g_w);
+#pragma unroll
+                for (int i = 0; i < kTopK; ++i) {
+                    if (i < n_sh && g_le[i] % pol.expert_stride == pol.expert_phase)
+                        emit_pair(p_le, p_w, n_pairs, g_le[i] / pol.expert_stride, g_w[i]);
+                }
+            }
         }
 #pragma unroll
         for (int i = 0; i < kTopK; ++i) {

@@ -33,6 +33,18 @@ def expert_range(rank: int, world: int) -> Tuple[int, int]:
     return rank * per, per
 
 
+def expert_ids(rank: int, world: int, placement: str = "contiguous"):
+    """Global ids of the experts `rank` holds, in local order.  "contiguous": the reference's blocks
+    (local_expert_offset = 256/world * rank); "strided": every world-th expert starting at `rank`, so
+    that each rank carries an equal share of every routing group."""
+    off, n = expert_range(rank, world)
+    if placement == "contiguous":
+        return list(range(off, off + n))
+    if placement == "strided":
+        return list(range(rank, NE, world))
+    raise ValueError(f"unknown placement {placement!r}")
+
+
 def token_range(rank: int, world: int, T: int) -> Tuple[int, int]:
     """Token slice [lo, hi) that `rank` owns after a reduce-scatter (T padded up to a multiple of world)."""
     per = (T + world - 1) // world
@@ -83,7 +95,7 @@ class ShardedMoe:
     """One rank's share of the 256-expert layer plus the cross-rank sum."""
 
     def __init__(self, max_tokens: int, rank: Optional[int] = None, world: Optional[int] = None,
-                 device: Optional[int] = None, group=None):
+                 device: Optional[int] = None, group=None, placement: str = "contiguous"):
         from .op import MoeLayer
         if rank is None:
             rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -91,7 +103,12 @@ class ShardedMoe:
             world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank, self.world, self.group = rank, world, group
         self.local_expert_offset, self.num_local_experts = expert_range(rank, world)
+        self.placement = placement
+        self.expert_ids = expert_ids(rank, world, placement)   # the weights passed to run() must be these, in order
         self.layer = MoeLayer(max_tokens, self.num_local_experts, device)
+        if placement == "strided" and world > 1:
+            self.layer.set_expert_stride(world)
+            self.local_expert_offset = rank   # the phase
         self.max_tokens = max_tokens
         self._exchange = None   # (symmetric buffer, handle, peer pointers, bytes), made on first fused run
         self._epoch = 0

@@ -111,6 +111,24 @@ def make_shard(local_expert_offset: int, num_local_experts: int, base_seed: int 
     return w1, s1, w2, s2
 
 
+def make_experts(expert_ids, base_seed: int = 1000, device="cpu", out_device=None):
+    """Stacked weights of the given global experts, in the given order."""
+    out_device = out_device or device
+    ids = list(expert_ids)
+    E = len(ids)
+    w1 = torch.empty(E, N1, H, dtype=torch.float8_e4m3fn, device=out_device)
+    s1 = torch.empty(E, N1 // BLK, H // BLK, dtype=torch.float32, device=out_device)
+    w2 = torch.empty(E, H, I, dtype=torch.float8_e4m3fn, device=out_device)
+    s2 = torch.empty(E, H // BLK, I // BLK, dtype=torch.float32, device=out_device)
+    for i, e in enumerate(ids):
+        q1, a1, q2, a2 = make_expert(e, base_seed, device)
+        w1[i].copy_(q1)
+        s1[i].copy_(a1)
+        w2[i].copy_(q2)
+        s2[i].copy_(a2)
+    return w1, s1, w2, s2
+
+
 def expected_rows_per_shard(T: int) -> float:
     """Mean routed rows of a 32-expert shard for uniform routing: 8 T 32 / 256."""
     return 8.0 * T * 32 / NE

@@ -101,6 +101,13 @@ class MoeLayer:
         if rc != _lib.OK:
             self._raise(rc)
 
+    def set_expert_stride(self, stride: int):
+        """Strided expert placement (multi-GPU wrapper): this handle's experts are the global ids g
+        with g % stride == local_expert_offset, stacked in increasing g; stride 1 = contiguous."""
+        rc = self._lib.moe_fp8_b200_set_option(self._h, _lib.OPT_EXPERT_STRIDE, int(stride))
+        if rc != _lib.OK:
+            self._raise(rc)
+
     STAGES = ("route_dispatch", "scan", "permute", "gemm1", "gemm2", "combine")
 
     def set_stage_timing(self, on: bool):

@@ -83,7 +83,15 @@ enum {
      * tables of the workspace (EXPERT_COUNT, TOPK_*, PAIR_*); 0 selects the chain, which also
      * leaves the packed rows, tiles and offsets behind for moe_fp8_b200_read_intermediate.
      * Unfinalised, stage-limited and multi-GPU-exchange runs always use the chain. */
-    MOE_FP8_B200_OPT_DECODE_KERNEL = 5
+    MOE_FP8_B200_OPT_DECODE_KERNEL = 5,
+    /* Expert placement for the multi-GPU wrapper (no counterpart in the reference, whose shards are
+     * contiguous blocks of 32 experts).  S = 1 (default): the handle's experts are the global ids
+     * [local_expert_offset, local_expert_offset + E).  S in {2, 4, 8} with E * S == 256: the handle's
+     * experts are every S-th global expert, g with g % S == local_expert_offset (which must then be
+     * < S), stacked in increasing g; the dispatch policy is still evaluated per 32-expert shard of
+     * global ids, so the S handles together produce exactly the pairs of the reference's shard calls
+     * while every handle carries an equal share of every routing group. */
+    MOE_FP8_B200_OPT_EXPERT_STRIDE = 6
 };
 #define MOE_FP8_B200_DECODE_MAX_TOKENS 8
 

@@ -442,3 +442,38 @@ def test_layer_vs_oracle_across_the_path_boundaries(pkg, oracle, T, offset, deco
     if rows:
         st = hp.error_stats(got, oracle.bf16_decode(ref))
         assert st["rel_l2"] < 2e-2 and st["contest_ratio"] >= 0.999, st
+
+
+def test_strided_expert_placement_sums_to_the_full_layer(pkg):
+    """Strided placement (multi-GPU wrapper): four handles holding every 4th expert produce, together,
+    the pairs of the 256-expert layer -- same per-shard policy, other owner -- so their outputs sum
+    to the one-handle result; rows are spread evenly over the handles."""
+    T, S = 160, 4
+    from fp8_moe_dev_b200 import gen
+    inputs = hp.cpu_inputs(T, seed=4000)
+    full = pkg.MoeLayer(T, 256, 0)
+    w_full = hp.gpu_shard(0, 256)
+    want = hp.run_layer(full, inputs, w_full, 0).float().cpu()
+    pc_full = int(full.read("pair_count", T).sum())
+    full.close()
+    del w_full
+    total = torch.zeros(T, H)
+    rows = []
+    for phase in range(S):
+        lay = pkg.MoeLayer(T, 256 // S, 0)
+        lay.set_expert_stride(S)
+        w = gen.make_experts(range(phase, 256, S), device="cuda", out_device="cuda")
+        total += hp.run_layer(lay, inputs, w, phase).float().cpu()
+        rows.append(int(lay.read("pair_count", T).sum()))
+        with pytest.raises(Exception):
+            hp.run_layer(lay, inputs, w, S)   # phase out of range
+        lay.close()
+        del w
+    assert sum(rows) == pc_full
+    assert max(rows) <= 1.25 * pc_full / S
+    st = hp.error_stats(total.numpy(), want.numpy())
+    assert st["rel_l2"] < 1e-2, st     # four bf16 partial outputs added in fp32 vs one bf16 output
+    bad = pkg.MoeLayer(T, 32, 0)
+    with pytest.raises(Exception):
+        bad.set_expert_stride(4)       # 32 * 4 != 256
+    bad.close()
