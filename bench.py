@@ -362,13 +362,36 @@ def run_ours(args, rank, world, local):
     from fp8_moe_dev_b200.dist import ShardedMoe, combine_partials
     T, offset, E, inputs, weights = make_workload(args.workload, rank, world)
     dev = [x.cuda() for x in inputs]
-    w1, s1, w2, s2 = weights
-    moe = ShardedMoe(T, rank, world, local) if world > 1 else None
-    layer = moe.layer if moe else pkg.MoeLayer(T, E, local)
     out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
-
     per = (T + world - 1) // world
     scat = torch.empty(per, H, dtype=torch.bfloat16, device="cuda")
+    moe, placement_ms = None, None
+    if world > 1:
+        # expert placement: the reference's contiguous blocks, or every world-th expert per rank (an equal
+        # share of every routing group on every rank, more rows to exchange); "auto" times both and keeps
+        # the faster one
+        from fp8_moe_dev_b200 import gen
+        cands = {}
+        for place in (("contiguous", "strided") if args.placement == "auto" else (args.placement,)):
+            m = ShardedMoe(T, rank, world, local, placement=place)
+            w = weights if place == "contiguous" else gen.make_experts(m.expert_ids, base_seed=1000, device="cuda",
+                                                                         out_device="cuda")
+            cands[place] = (m, w)
+        if len(cands) > 1:
+            placement_ms = {}
+            for place, (m, w) in cands.items():
+                placement_ms[place] = round(time_steps(lambda: m.run(*dev, *w, RSF, out, mode=args.collective,
+                                                                      scatter_out=scat), 5, 3, world), 4)
+            best = min(placement_ms, key=placement_ms.get)
+            for place in list(cands):
+                if place != best:
+                    cands[place][0].layer.close()
+                    del cands[place]
+            torch.cuda.empty_cache()
+        (place, (moe, weights)), = cands.items()
+        offset = moe.local_expert_offset
+    w1, s1, w2, s2 = weights
+    layer = moe.layer if moe else pkg.MoeLayer(T, E, local)
 
     def step(mode=args.collective):
         if mode == "fused" and moe:
@@ -465,6 +488,7 @@ def run_ours(args, rank, world, local):
                    "l2": f"inputs larger than L2 (weights {E * 44.04e-3:.1f} GB on this GPU), no flush",
                    "ideal_scaling_bound": round(rows_total / rows_max, 3) if rows_max else None,
                    "collective": None if world == 1 else args.collective,
+                   "expert_placement": None if world == 1 else moe.placement, "placement_trial_ms": placement_ms,
                    "other_collective_ms_per_step": other_ms},
         "clocks": clk.summary(),
         "e2e": None if args.skip_e2e else {"value": round(T / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
@@ -569,6 +593,9 @@ def main():
                          "inputs); all_reduce leaves every rank with all T tokens; fused gives the reduce_scatter "
                          "result with the exchange done by the combine kernel's own peer stores (the reference "
                          "arm uses NCCL reduce_scatter for it)")
+    ap.add_argument("--placement", choices=["auto", "contiguous", "strided"], default="auto",
+                    help="N > 1: which experts a rank holds -- the reference's contiguous blocks of 256/N, every N-th "
+                         "expert (balanced over the routing groups), or whichever is faster in a short trial")
     ap.add_argument("--skip-small", action="store_true", help="skip the T=1/16/1024 single-shard latencies")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the host fp32 baseline")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")

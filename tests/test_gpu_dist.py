@@ -92,6 +92,19 @@ def _worker(rank, world, port, T, q):
                 moe.host_wait(tickets[i])
                 ok_fused = ok_fused and torch.equal(outs[i % 2][lo:hi], want[lo:hi].cpu())
             moe.layer.check()
+        # strided expert placement: other owners, same pairs; the summed output agrees up to the
+        # rounding of the partial outputs, and the ranks' row counts add up to the same total
+        rows_c = torch.tensor([int(moe.layer.read("pair_count", T).sum())], device="cuda")
+        moe_s = ShardedMoe(T, placement="strided")
+        ws = gen.make_experts(moe_s.expert_ids, device="cuda", out_device="cuda")
+        got_s = moe_s.run(*dev, *ws, 2.5, out, mode="fused")
+        moe_s.layer.check()
+        rows_s = torch.tensor([int(moe_s.layer.read("pair_count", T).sum())], device="cuda")
+        dist.all_reduce(rows_c)
+        dist.all_reduce(rows_s)
+        a, b = got_s[:hi - lo].float(), want[lo:hi].float()
+        rel = float((a - b).norm() / (b.norm() + 1e-30))
+        ok_fused = ok_fused and int(rows_c) == int(rows_s) and rel < 1e-2
         q.put((rank, ok_sum, ok_scatter and ok_fused, nonzero))
     finally:
         dist.destroy_process_group()
