@@ -380,9 +380,18 @@ def run_ours(args, rank, world, local):
         if len(cands) > 1:
             placement_ms = {}
             for place, (m, w) in cands.items():
-                placement_ms[place] = round(time_steps(lambda: m.run(*dev, *w, RSF, out, mode=args.collective,
-                                                                      scatter_out=scat), 5, 3, world), 4)
+                try:
+                    placement_ms[place] = round(time_steps(lambda: m.run(*dev, *w, RSF, out, mode=args.collective,
+                                                                          scatter_out=scat), 5, 3, world), 4)
+                    m.layer.check()
+                except Exception as ex:   # a candidate that does not run is not a candidate
+                    sys.stderr.write(f"placement {place} failed on rank {rank}: {ex}\n")
+                    placement_ms[place] = float("inf")
+            # every rank must take the same decision: a failure anywhere disqualifies the candidate everywhere
+            for place in placement_ms:
+                placement_ms[place] = max_over_ranks(placement_ms[place], world)
             best = min(placement_ms, key=placement_ms.get)
+            placement_ms = {k: (None if v == float("inf") else v) for k, v in placement_ms.items()}
             for place in list(cands):
                 if place != best:
                     cands[place][0].layer.close()
