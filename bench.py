@@ -368,12 +368,13 @@ def run_ours(args, rank, world, local):
     moe, placement_ms = None, None
     if world > 1:
         # expert placement: the reference's contiguous blocks, or every world-th expert per rank (an equal
-        # share of every routing group on every rank, more rows to exchange); "auto" times both and keeps
-        # the faster one
+        # share of every routing group on every rank), or experts dealt by measured load; "auto" times
+        # them and keeps the fastest
         from fp8_moe_dev_b200 import gen
         cands = {}
-        for place in (("contiguous", "strided") if args.placement == "auto" else (args.placement,)):
-            m = ShardedMoe(T, rank, world, local, placement=place)
+        loads = pkg.expert_loads(dev[0], dev[1], RSF)   # calibration: routed rows per expert, first 4096 tokens
+        for place in (("contiguous", "balanced", "strided") if args.placement == "auto" else (args.placement,)):
+            m = ShardedMoe(T, rank, world, local, placement=place, loads=loads)
             w = weights if place == "contiguous" else gen.make_experts(m.expert_ids, base_seed=1000, device="cuda",
                                                                          out_device="cuda")
             cands[place] = (m, w)
@@ -602,9 +603,10 @@ def main():
                          "inputs); all_reduce leaves every rank with all T tokens; fused gives the reduce_scatter "
                          "result with the exchange done by the combine kernel's own peer stores (the reference "
                          "arm uses NCCL reduce_scatter for it)")
-    ap.add_argument("--placement", choices=["auto", "contiguous", "strided"], default="auto",
+    ap.add_argument("--placement", choices=["auto", "contiguous", "strided", "balanced"], default="auto",
                     help="N > 1: which experts a rank holds -- the reference's contiguous blocks of 256/N, every N-th "
-                         "expert (balanced over the routing groups), or whichever is faster in a short trial")
+                         "expert, experts dealt longest-first by the routed rows of the first 4096 tokens "
+                         "(balanced), or whichever is fastest in a short trial")
     ap.add_argument("--skip-small", action="store_true", help="skip the T=1/16/1024 single-shard latencies")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the host fp32 baseline")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")

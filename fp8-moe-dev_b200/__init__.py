@@ -2,4 +2,4 @@
 on top of the C ABI in include/moe_fp8_b200.h.  Import name: fp8_moe_dev_b200 (the folder
 name holds a hyphen, so the repo root's __graft_entry__.load_package() registers it)."""
 from . import _lib  # noqa: F401
-from .op import MoeError, MoeLayer, run  # noqa: F401
+from .op import MoeError, MoeLayer, expert_loads, run  # noqa: F401

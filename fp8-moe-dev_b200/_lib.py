@@ -29,7 +29,7 @@ EXPORTS = [
     "moe_fp8_b200_reference_policy", "moe_fp8_b200_stage_times", "moe_fp8_b200_route_noalloc",
     "moe_fp8_b200_exchange_bytes", "moe_fp8_b200_run_reduce_scatter", "moe_fp8_b200_quantize_hidden",
     "moe_fp8_b200_run_unfinalized", "moe_fp8_b200_finalize", "moe_fp8_b200_run_host_async",
-    "moe_fp8_b200_host_wait",
+    "moe_fp8_b200_host_wait", "moe_fp8_b200_set_expert_map",
 ]
 NOALLOC_MAX_TOKENS = 4096
 
@@ -100,6 +100,8 @@ def load() -> C.CDLL:
     lib.moe_fp8_b200_run_host_async.argtypes = [H, C.POINTER(Args), C.c_void_p, C.POINTER(C.c_int64)]
     lib.moe_fp8_b200_host_wait.restype = C.c_int
     lib.moe_fp8_b200_host_wait.argtypes = [H, C.c_int64]
+    lib.moe_fp8_b200_set_expert_map.restype = C.c_int
+    lib.moe_fp8_b200_set_expert_map.argtypes = [H, C.POINTER(C.c_int32)]
     lib.moe_fp8_b200_check.restype = C.c_int
     lib.moe_fp8_b200_check.argtypes = [H, C.c_void_p]
     lib.moe_fp8_b200_read_intermediate.restype = C.c_int

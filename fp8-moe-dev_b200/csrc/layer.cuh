@@ -43,9 +43,10 @@ struct DispatchPolicy {
     int renorm;             // prune: kept weights rescaled by sum(local) / sum(kept)
     // Which global experts are local.  stride <= 1: the contiguous block [local_expert_offset,
     // local_expert_offset + E) as in the reference.  stride S > 1 (multi-GPU wrapper only): every
-    // S-th expert, global id g is local iff g % S == phase, with local index g / S; the policy above
-    // is still evaluated per 32-expert shard of GLOBAL ids, so the ranks' pairs together are exactly
-    // those of the reference's shard calls.
+    // S-th expert, global id g is local iff g % S == phase, with local index g / S; stride -1: the
+    // table Workspace::expert_map (global id -> local index, -1 = not local).  In both of these the
+    // policy above is still evaluated per 32-expert shard of GLOBAL ids, so the ranks' pairs together
+    // are exactly those of the reference's shard calls.
     int expert_stride;
     int expert_phase;
 };
@@ -104,6 +105,7 @@ struct Workspace {
     int4* tile_info;        // [max_tiles] per 128-row tile: {local expert, first tile of that expert,
                             //             tiles of that expert, routed rows of that expert}
     int* num_tiles;         // [1]
+    int* expert_map;        // [256] global expert -> local index or -1 (table placement only)
     int* topk_idx;          // [T,8] global expert ids in selection order
     float* topk_weight;     // [T,8] normalised weights (before routed_scaling_factor)
     int* pair_count;        // [T]   kept (token, local expert) pairs

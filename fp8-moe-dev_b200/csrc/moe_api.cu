@@ -60,7 +60,7 @@ struct Carve {
 };
 
 struct Layout {
-    size_t ctrl, expert_offset, tile_info, num_tiles, topk_idx, topk_weight, pair_count, pair_code,
+    size_t ctrl, expert_offset, tile_info, num_tiles, expert_map, topk_idx, topk_weight, pair_count, pair_code,
         pair_weight, row_token, a1, sfa1, a2, sfa2, y, splitk, total;
     int m_cap, max_tiles;
 };
@@ -75,6 +75,7 @@ Layout make_layout(int T, int E)
     L.expert_offset = c.take(sizeof(int) * (kMaxLocalExperts + 1));
     L.tile_info = c.take(sizeof(int4) * L.max_tiles);
     L.num_tiles = c.take(sizeof(int) * 4);
+    L.expert_map = c.take(sizeof(int) * kNumExperts);
     L.topk_idx = c.take(sizeof(int) * (size_t)T * kTopK);
     L.topk_weight = c.take(sizeof(float) * (size_t)T * kTopK);
     L.pair_count = c.take(sizeof(int) * (size_t)T);
@@ -190,6 +191,7 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
     }
     pol.expert_stride = h->opt_expert_stride;
     pol.expert_phase = (int)a.local_expert_offset;
+    if (h->opt_expert_stride < 0) pol.expert_phase = 0;
     if (h->opt_expert_stride > 1 && a.local_expert_offset >= h->opt_expert_stride)
         return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "with expert stride %d local_expert_offset is the phase and must be < %d",
                     h->opt_expert_stride, h->opt_expert_stride);
@@ -226,7 +228,7 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
         e = cudaMemsetAsync(h->ws.ctrl, 0, sizeof(Control), stream);
         h->counters_dirty = false;
     }
-    if (h->opt_decode && h->decode_ctas_per_sm > 0 && T <= kDecodeMaxTokens && finalize && !ex && h->opt_expert_stride <= 1 &&
+    if (h->opt_decode && h->decode_ctas_per_sm > 0 && T <= kDecodeMaxTokens && finalize && !ex && h->opt_expert_stride == 1 &&
         h->opt_stop_after == 0) {
         // the whole layer as one cooperative kernel, one CTA per SM
         DecodeArgs d;
@@ -399,6 +401,7 @@ int moe_fp8_b200_create(moe_fp8_b200_handle* out, int device, int max_tokens, in
     w.sfa2 = reinterpret_cast<float*>(h->base + L.sfa2);
     w.y = reinterpret_cast<__nv_bfloat16*>(h->base + L.y);
     w.splitk_partial = reinterpret_cast<float*>(h->base + L.splitk);
+    w.expert_map = reinterpret_cast<int*>(h->base + L.expert_map);
     w.m_cap = L.m_cap;
     w.max_tiles = L.max_tiles;
     // Small control arrays start defined; the large row buffers are written before use.
@@ -568,6 +571,29 @@ int moe_fp8_b200_finalize(moe_fp8_b200_handle h, int num_tokens, void* output, v
         return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "output is NULL or not 16-byte aligned");
     const cudaError_t e = launch_combine(h->ws, output, num_tokens, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "combine launch failed: %s", cudaGetErrorString(e));
+    return MOE_FP8_B200_OK;
+}
+
+int moe_fp8_b200_set_expert_map(moe_fp8_b200_handle h, const int32_t* local_slot)
+{
+    if (!h) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
+    if (!local_slot) {
+        h->opt_expert_stride = 1;
+        return MOE_FP8_B200_OK;
+    }
+    int seen[kMaxLocalExperts] = {0};
+    for (int g = 0; g < kNumExperts; ++g) {
+        const int s = local_slot[g];
+        if (s < -1 || s >= h->num_local_experts || (s >= 0 && seen[s]++))
+            return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "expert map: slot %d of global expert %d is out of range or used twice", s, g);
+    }
+    for (int s = 0; s < h->num_local_experts; ++s)
+        if (!seen[s]) return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "expert map: local slot %d has no expert", s);
+    cudaError_t e = cudaSetDevice(h->device);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(h->ws.expert_map, local_slot, sizeof(int) * kNumExperts, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "expert map upload: %s", cudaGetErrorString(e));
+    h->opt_expert_stride = -1;
     return MOE_FP8_B200_OK;
 }
 

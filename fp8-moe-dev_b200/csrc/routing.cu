@@ -108,13 +108,13 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_dispatch_kernel(
     }
 
     if (lane == 0) {
-        if (pol.expert_stride <= 1) {
+        if (pol.expert_stride == 0 || pol.expert_stride == 1) {
             const int shards = num_local_experts / kShardExperts;
             for (int sh = 0; sh < shards; ++sh) {
                 dispatch_one_shard(idx, wn, sh, local_expert_offset, pol, rsf, n_pairs, p_le, p_w);
             }
         } else {
-            // strided placement: the policy runs on every global shard, this rank keeps its experts
+            // strided or table placement: the policy runs on every global shard, this rank keeps its experts
             for (int sh = 0; sh < kNumExperts / kShardExperts; ++sh) {
                 int n_sh = 0;
                 int g_le[kTopK];
@@ -124,8 +124,12 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_dispatch_kernel(
                 dispatch_one_shard(idx, wn, sh, 0, pol, rsf, n_sh, g_le, g_w);
 #pragma unroll
                 for (int i = 0; i < kTopK; ++i) {
-                    if (i < n_sh && g_le[i] % pol.expert_stride == pol.expert_phase)
-                        emit_pair(p_le, p_w, n_pairs, g_le[i] / pol.expert_stride, g_w[i]);
+                    if (i < n_sh) {
+                        const int local = pol.expert_stride > 1
+                                              ? (g_le[i] % pol.expert_stride == pol.expert_phase ? g_le[i] / pol.expert_stride : -1)
+                                              : __ldg(ws.expert_map + g_le[i]);
+                        if (local >= 0) emit_pair(p_le, p_w, n_pairs, local, g_w[i]);
+                    }
                 }
             }
         }

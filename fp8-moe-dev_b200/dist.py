@@ -45,6 +45,26 @@ def expert_ids(rank: int, world: int, placement: str = "contiguous"):
     raise ValueError(f"unknown placement {placement!r}")
 
 
+def balanced_expert_ids(loads, world: int):
+    """Places the 256 experts on `world` ranks, 256/world each, so that the ranks' total loads are
+    as equal as a greedy longest-first assignment makes them: experts in decreasing load, each to the
+    least loaded rank that still has a free slot.  `loads`: 256 per-expert row counts of a
+    calibration batch.  Returns one sorted id list per rank (the same on every rank: ties by id)."""
+    loads = [float(x) for x in loads]
+    if len(loads) != NE:
+        raise ValueError("loads must have 256 entries")
+    expert_range(0, world)   # validates world
+    cap = NE // world
+    order = sorted(range(NE), key=lambda e: (-loads[e], e))
+    total = [0.0] * world
+    ids = [[] for _ in range(world)]
+    for e in order:
+        r = min((r for r in range(world) if len(ids[r]) < cap), key=lambda r: (total[r], r))
+        ids[r].append(e)
+        total[r] += loads[e]
+    return [sorted(x) for x in ids]
+
+
 def token_range(rank: int, world: int, T: int) -> Tuple[int, int]:
     """Token slice [lo, hi) that `rank` owns after a reduce-scatter (T padded up to a multiple of world)."""
     per = (T + world - 1) // world
@@ -95,7 +115,7 @@ class ShardedMoe:
     """One rank's share of the 256-expert layer plus the cross-rank sum."""
 
     def __init__(self, max_tokens: int, rank: Optional[int] = None, world: Optional[int] = None,
-                 device: Optional[int] = None, group=None, placement: str = "contiguous"):
+                 device: Optional[int] = None, group=None, placement: str = "contiguous", loads=None):
         from .op import MoeLayer
         if rank is None:
             rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -104,11 +124,16 @@ class ShardedMoe:
         self.rank, self.world, self.group = rank, world, group
         self.local_expert_offset, self.num_local_experts = expert_range(rank, world)
         self.placement = placement
-        self.expert_ids = expert_ids(rank, world, placement)   # the weights passed to run() must be these, in order
+        # the weights passed to run() must be these experts, in this order
+        self.expert_ids = (balanced_expert_ids(loads, world)[rank] if placement == "balanced"
+                           else expert_ids(rank, world, placement))
         self.layer = MoeLayer(max_tokens, self.num_local_experts, device)
         if placement == "strided" and world > 1:
             self.layer.set_expert_stride(world)
             self.local_expert_offset = rank   # the phase
+        elif placement == "balanced" and world > 1:
+            self.layer.set_expert_map(self.expert_ids)   # placed by measured load (`loads`: 256 row counts)
+            self.local_expert_offset = 0
         self.max_tokens = max_tokens
         self._exchange = None   # (symmetric buffer, handle, peer pointers, bytes), made on first fused run
         self._epoch = 0

@@ -108,6 +108,19 @@ class MoeLayer:
         if rc != _lib.OK:
             self._raise(rc)
 
+    def set_expert_map(self, expert_ids):
+        """Table placement: this handle's weight tensors hold the global experts `expert_ids`, in that
+        order (None: back to the contiguous block at local_expert_offset)."""
+        if expert_ids is None:
+            rc = self._lib.moe_fp8_b200_set_expert_map(self._h, None)
+        else:
+            table = (C.c_int32 * NE)(*([-1] * NE))
+            for slot, g in enumerate(expert_ids):
+                table[int(g)] = slot
+            rc = self._lib.moe_fp8_b200_set_expert_map(self._h, table)
+        if rc != _lib.OK:
+            self._raise(rc)
+
     STAGES = ("route_dispatch", "scan", "permute", "gemm1", "gemm2", "combine")
 
     def set_stage_timing(self, on: bool):
@@ -315,6 +328,26 @@ class MoeLayer:
 # ----------------------------------------------------------------------------------------
 # The reference-shaped entry point: one grow-only handle per (device, expert count), like
 # the reference's thread-local workspace (kernel/moe_fp8.cu:2677-2689).
+def expert_loads(routing_logits, routing_bias, routed_scaling_factor: float = 1.0, reference_pruning: bool = True):
+    """Routed rows per global expert (256 counts, a CPU list) for the first <= 4096 tokens of a
+    batch: the calibration input of the load-aware expert placement.  Runs the library's routing
+    kernel alone (no weights needed)."""
+    T = min(int(routing_logits.shape[0]), _lib.NOALLOC_MAX_TOKENS)
+    lg = routing_logits[:T].contiguous()
+    dev = lg.device
+    idx = torch.empty((max(T, 1), 8), dtype=torch.int32, device=dev)
+    w = torch.empty((max(T, 1), 8), dtype=torch.float32, device=dev)
+    cnt = torch.zeros((NE,), dtype=torch.int32, device=dev)
+    err = C.create_string_buffer(256)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    rc = _lib.load().moe_fp8_b200_route_noalloc(lg.data_ptr(), routing_bias.data_ptr(), T, 0, NE, float(routed_scaling_factor),
+                                                int(reference_pruning), idx.data_ptr(), w.data_ptr(), cnt.data_ptr(),
+                                                C.c_void_p(stream), err, len(err))
+    if rc != _lib.OK:
+        raise MoeError(rc, err.value.decode())
+    return [int(x) for x in cnt.cpu().tolist()]
+
+
 _layers: Dict[Tuple[int, int], MoeLayer] = {}
 
 

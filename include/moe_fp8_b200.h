@@ -199,6 +199,13 @@ MOE_FP8_B200_API size_t moe_fp8_b200_exchange_bytes(int num_tokens, int world);
 MOE_FP8_B200_API int moe_fp8_b200_run_reduce_scatter(moe_fp8_b200_handle h, const moe_fp8_b200_args* args,
                                                      const moe_fp8_b200_exchange* exchange, void* stream);
 
+/* Table form of the expert placement (see MOE_FP8_B200_OPT_EXPERT_STRIDE): local_slot[g] is the
+ * index inside this handle's weight tensors of global expert g, or -1 if another handle holds it;
+ * every slot 0 .. num_local_experts-1 must appear exactly once.  Lets the multi-GPU wrapper place
+ * experts by measured load.  local_expert_offset is ignored while a table is set; passing NULL
+ * returns to the contiguous placement.  Host pointer; synchronises the device once. */
+MOE_FP8_B200_API int moe_fp8_b200_set_expert_map(moe_fp8_b200_handle h, const int32_t* local_slot);
+
 /* ---- the operators either side of the layer ---------------------------------------------
  * Quantise-on-entry: bf16 activations x [num_tokens, 7168] (device) -> e4m3 q [num_tokens, 7168]
  * and scales fp32 [56, num_tokens], i.e. exactly the hidden_states / hidden_states_scale pair

@@ -150,3 +150,23 @@ def test_token_slices_are_gathered_into_the_replicated_inputs():
         assert p.exitcode == 0
     res = dict(q.get(timeout=10) for _ in range(world))
     assert res == {0: True, 1: True}
+
+
+def test_balanced_expert_placement(pkg):
+    """Longest-first placement by load: every rank gets 256/world experts, every expert exactly one
+    rank, and the heaviest rank stays close to the mean even for heavy-tailed loads."""
+    from fp8_moe_dev_b200.dist import balanced_expert_ids, expert_ids
+    g = torch.Generator().manual_seed(5)
+    loads = (torch.rand(256, generator=g) ** -0.5 * 100).clamp(max=2500).tolist()   # heavy tail: a few experts 10x the median
+    for world in (1, 2, 4, 8):
+        ids = balanced_expert_ids(loads, world)
+        assert [len(x) for x in ids] == [256 // world] * world
+        assert sorted(sum(ids, [])) == list(range(256))
+        tot = [sum(loads[e] for e in x) for x in ids]
+        assert max(tot) <= 1.08 * sum(tot) / world
+        if world == 8:
+            contiguous = [sum(loads[e] for e in expert_ids(r, world)) for r in range(world)]
+            assert max(tot) < max(contiguous)
+    assert balanced_expert_ids(loads, 4) == balanced_expert_ids(list(loads), 4)   # deterministic
+    with pytest.raises(ValueError):
+        balanced_expert_ids(loads[:100], 4)

@@ -105,6 +105,19 @@ def _worker(rank, world, port, T, q):
         a, b = got_s[:hi - lo].float(), want[lo:hi].float()
         rel = float((a - b).norm() / (b.norm() + 1e-30))
         ok_fused = ok_fused and int(rows_c) == int(rows_s) and rel < 1e-2
+        # experts placed by measured load
+        import fp8_moe_dev_b200 as pkg2
+        loads = pkg2.expert_loads(dev[0], dev[1], 2.5)
+        moe_b = ShardedMoe(T, placement="balanced", loads=loads)
+        wb = gen.make_experts(moe_b.expert_ids, device="cuda", out_device="cuda")
+        got_b = moe_b.run(*dev, *wb, 2.5, out, mode="fused")
+        moe_b.layer.check()
+        rows_b = torch.tensor([int(moe_b.layer.read("pair_count", T).sum())], device="cuda")
+        mine_b = int(rows_b)
+        dist.all_reduce(rows_b)
+        a = got_b[:hi - lo].float()
+        rel = float((a - b).norm() / (b.norm() + 1e-30))
+        ok_fused = ok_fused and int(rows_b) == int(rows_c) and rel < 1e-2 and abs(mine_b - int(rows_b) / world) <= 0.06 * int(rows_b) + 8
         q.put((rank, ok_sum, ok_scatter and ok_fused, nonzero))
     finally:
         dist.destroy_process_group()

@@ -477,3 +477,40 @@ def test_strided_expert_placement_sums_to_the_full_layer(pkg):
     with pytest.raises(Exception):
         bad.set_expert_stride(4)       # 32 * 4 != 256
     bad.close()
+
+
+def test_load_aware_expert_placement_sums_to_the_full_layer(pkg):
+    """Table placement from measured loads: four handles, experts dealt longest-first by the routed
+    rows of the batch itself, sum to the 256-expert result and carry nearly equal numbers of rows."""
+    T, S = 192, 4
+    from fp8_moe_dev_b200 import gen
+    from fp8_moe_dev_b200.dist import balanced_expert_ids
+    inputs = hp.cpu_inputs(T, seed=4100)
+    loads = pkg.expert_loads(inputs[0].cuda(), inputs[1].cuda(), RSF)
+    full = pkg.MoeLayer(T, 256, 0)
+    w_full = hp.gpu_shard(0, 256)
+    want = hp.run_layer(full, inputs, w_full, 0).float().cpu()
+    assert loads == [int(x) for x in full.read("expert_count", 256)]
+    pc_full = int(full.read("pair_count", T).sum())
+    full.close()
+    del w_full
+    ids = balanced_expert_ids(loads, S)
+    total = torch.zeros(T, H)
+    rows = []
+    for r in range(S):
+        lay = pkg.MoeLayer(T, 256 // S, 0)
+        lay.set_expert_map(ids[r])
+        w = gen.make_experts(ids[r], device="cuda", out_device="cuda")
+        total += hp.run_layer(lay, inputs, w, 0).float().cpu()
+        rows.append(int(lay.read("pair_count", T).sum()))
+        assert rows[-1] == sum(loads[e] for e in ids[r])
+        lay.close()
+        del w
+    assert sum(rows) == pc_full and max(rows) <= 1.05 * pc_full / S + 8
+    st = hp.error_stats(total.numpy(), want.numpy())
+    assert st["rel_l2"] < 1e-2, st
+    bad = pkg.MoeLayer(T, 64, 0)
+    with pytest.raises(Exception):
+        bad.set_expert_map(list(range(10)))     # 64 slots need 64 experts
+    bad.set_expert_map(None)
+    bad.close()
