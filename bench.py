@@ -373,7 +373,7 @@ def run_ours(args, rank, world, local):
         from fp8_moe_dev_b200 import gen
         cands = {}
         loads = pkg.expert_loads(dev[0], dev[1], RSF)   # calibration: routed rows per expert, first 4096 tokens
-        for place in (("contiguous", "balanced", "strided") if args.placement == "auto" else (args.placement,)):
+        for place in (("contiguous", "balanced") if args.placement == "auto" else (args.placement,)):
             m = ShardedMoe(T, rank, world, local, placement=place, loads=loads)
             w = weights if place == "contiguous" else gen.make_experts(m.expert_ids, base_seed=1000, device="cuda",
                                                                          out_device="cuda")
@@ -606,7 +606,7 @@ def main():
     ap.add_argument("--placement", choices=["auto", "contiguous", "strided", "balanced"], default="auto",
                     help="N > 1: which experts a rank holds -- the reference's contiguous blocks of 256/N, every N-th "
                          "expert, experts dealt longest-first by the routed rows of the first 4096 tokens "
-                         "(balanced), or whichever is fastest in a short trial")
+                         "(balanced), or the faster of contiguous and balanced in a short trial (auto; strided never won one)")
     ap.add_argument("--skip-small", action="store_true", help="skip the T=1/16/1024 single-shard latencies")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the host fp32 baseline")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
