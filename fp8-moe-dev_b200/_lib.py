@@ -14,7 +14,7 @@ LIB_PATH = HERE / "libmoe_fp8_b200.so"
 OK = 0
 ERR_INVALID_ARGUMENT, ERR_CUDA, ERR_CAPACITY, ERR_DEVICE, ERR_UNSUPPORTED = -1, -2, -3, -4, -5
 OPT_REFERENCE_PRUNING, OPT_EXACT_SILU, OPT_STAGE_TIMING = 1, 2, 3
-OPT_STOP_AFTER_STAGE, OPT_DECODE_KERNEL, OPT_EXPERT_STRIDE = 4, 5, 6
+OPT_STOP_AFTER_STAGE, OPT_DECODE_KERNEL, OPT_EXPERT_STRIDE, OPT_WAIT_LIMIT_US = 4, 5, 6, 7
 DECODE_MAX_TOKENS = 8
 
 BUF = dict(
@@ -29,7 +29,8 @@ EXPORTS = [
     "moe_fp8_b200_reference_policy", "moe_fp8_b200_stage_times", "moe_fp8_b200_route_noalloc",
     "moe_fp8_b200_exchange_bytes", "moe_fp8_b200_run_reduce_scatter", "moe_fp8_b200_quantize_hidden",
     "moe_fp8_b200_run_unfinalized", "moe_fp8_b200_finalize", "moe_fp8_b200_run_host_async",
-    "moe_fp8_b200_host_wait", "moe_fp8_b200_set_expert_map",
+    "moe_fp8_b200_host_wait", "moe_fp8_b200_set_expert_map", "moe_fp8_b200_inject_device_status",
+    "moe_fp8_b200_exchange_regions",
 ]
 NOALLOC_MAX_TOKENS = 4096
 
@@ -47,7 +48,7 @@ class Args(C.Structure):
 class Exchange(C.Structure):
     """moe_fp8_b200_exchange"""
     _fields_ = [("peer_buffers", C.c_void_p * 8), ("buffer_bytes", C.c_size_t), ("rank", C.c_int32),
-                ("world", C.c_int32), ("epoch", C.c_uint32)]
+                ("world", C.c_int32), ("epoch", C.c_uint32), ("capacity_tokens", C.c_int32)]
 
 
 class Unfinalized(C.Structure):
@@ -88,6 +89,8 @@ def load() -> C.CDLL:
         fn.argtypes = [H, C.POINTER(Args), C.c_void_p]
     lib.moe_fp8_b200_exchange_bytes.restype = C.c_size_t
     lib.moe_fp8_b200_exchange_bytes.argtypes = [C.c_int, C.c_int]
+    lib.moe_fp8_b200_exchange_regions.restype = C.c_int
+    lib.moe_fp8_b200_exchange_regions.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
     lib.moe_fp8_b200_run_reduce_scatter.restype = C.c_int
     lib.moe_fp8_b200_run_reduce_scatter.argtypes = [H, C.POINTER(Args), C.POINTER(Exchange), C.c_void_p]
     lib.moe_fp8_b200_quantize_hidden.restype = C.c_int
@@ -102,6 +105,8 @@ def load() -> C.CDLL:
     lib.moe_fp8_b200_host_wait.argtypes = [H, C.c_int64]
     lib.moe_fp8_b200_set_expert_map.restype = C.c_int
     lib.moe_fp8_b200_set_expert_map.argtypes = [H, C.POINTER(C.c_int32)]
+    lib.moe_fp8_b200_inject_device_status.restype = C.c_int
+    lib.moe_fp8_b200_inject_device_status.argtypes = [H, C.c_int, C.c_uint, C.c_void_p]
     lib.moe_fp8_b200_check.restype = C.c_int
     lib.moe_fp8_b200_check.argtypes = [H, C.c_void_p]
     lib.moe_fp8_b200_read_intermediate.restype = C.c_int

@@ -171,6 +171,11 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_layer_kernel(
     const int T = a.T, E = a.num_local_experts;
     const bool clocked = blockIdx.x == 0 && tid == 0;
     auto stamp = [&](int i) { if (clocked) ws.ctrl->dec_time[i] = global_timer_ns(); };
+    // A failure that an earlier launch recorded stays in the status word until the host has read it
+    // (moe_fp8_b200_check clears it together with any arrival counts that launch left on the grid
+    // barriers).  Until then this kernel does nothing: with stale counts its barriers would open early.
+    // Every CTA reads the same word; within one launch it can only change after a full wait limit.
+    if (__ldcg(&ws.ctrl->status) != kStatusOk) return;
     stamp(0);
     volatile int* abort_flag = &sh->abort;
 
@@ -356,7 +361,6 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_layer_kernel(
         if (p < sh->pair_count[t]) sh->pair_row[t][p] = sh->act_row0[sh->expert_slot[sh->pair_le[t][p]]] + sh->pair_slot[t][p];
     }
     if (blockIdx.x == 0) {   // the tables other entry points and the tests read
-        if (tid == 0) { ws.ctrl->status = kStatusOk; ws.ctrl->status_detail = 0; }
         if (tid < T) ws.pair_count[tid] = sh->pair_count[tid];
         if (tid < T * kTopK) {
             const int t = tid / kTopK, p = tid % kTopK;

@@ -81,8 +81,11 @@ enum KernelStatus : int {
 // Cross-GPU exchange of the fused combine + reduce-scatter (expert-parallel ranks of one NVSwitch
 // box).  Every rank owns one receive buffer of identical layout in peer-mapped memory:
 //   [world sources] u32 (first 256 bytes)                    epoch of the last complete push
-//   [2 parities][world sources][tokens_per_rank][7168] bf16   partial rows, written by the source
-//   [2 parities][world sources][present_stride]       u8     1 if the source sent that row
+//   [2 parities][world sources][slot_rows][7168] bf16   partial rows, written by the source
+//   [2 parities][world sources][present_stride]  u8     1 if the source sent that row
+// slot_rows = ceil(capacity / world) comes from the buffer's token capacity, not from the call's T: a
+// call with fewer tokens uses the first ceil(T / world) rows of every slot, and the regions of the two
+// parities stay disjoint whatever sequence of T the ranks run.
 // Rank r owns tokens [r * tokens_per_rank, (r + 1) * tokens_per_rank).  Data are double-buffered
 // by epoch parity; a source may push epoch e + 2 only after it has reduced epoch e + 1, which
 // implies that every owner has finished reading epoch e (its push of e + 1 follows its own
@@ -91,9 +94,12 @@ constexpr int kMaxRanks = 8;
 struct ExchangeView {
     uint8_t* peer[kMaxRanks];   // receive buffer of every rank, mapped into this process
     int rank, world;
-    int tokens_per_rank;        // ceil(T / world)
-    int present_stride;         // tokens_per_rank rounded up to 16
+    int tokens_per_rank;        // ceil(T / world): who owns which token of THIS call
+    int slot_rows;              // rows of one source's slot = ceil(capacity / world): fixed per buffer, so that
+                                // the two parity regions never move when T changes from call to call
+    int present_stride;         // slot_rows rounded up to 16
     uint32_t epoch;
+    uint32_t wait_limit_us;     // bound of the owner's wait for its peers' flags
     size_t data_offset;         // rows start here (the flags occupy the bytes before)
     size_t rows_bytes_per_parity, present_bytes_per_parity;
 };

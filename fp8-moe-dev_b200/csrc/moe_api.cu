@@ -105,6 +105,8 @@ struct moe_fp8_b200_ctx {
     int opt_stop_after = 0;   // diagnostics: enqueue only the first N stages (0 = all)
     int opt_decode = 1;       // single-kernel path for batches of at most kDecodeMaxTokens tokens
     int opt_expert_stride = 1;   // > 1: strided expert placement (multi-GPU wrapper)
+    bool expert_map_set = false; // table placement (set_expert_map) overrides the stride while set
+    int opt_wait_limit_us = 1000000;   // bound of the exchange's wait for peer flags
     int decode_ctas_per_sm = 0;
     uint8_t* base = nullptr;
     Layout layout{};
@@ -189,12 +191,9 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
         std::memset(&pol, 0, sizeof(pol));
         pol.keep_limit = 3;
     }
-    pol.expert_stride = h->opt_expert_stride;
-    pol.expert_phase = (int)a.local_expert_offset;
-    if (h->opt_expert_stride < 0) pol.expert_phase = 0;
-    if (h->opt_expert_stride > 1 && a.local_expert_offset >= h->opt_expert_stride)
-        return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "with expert stride %d local_expert_offset is the phase and must be < %d",
-                    h->opt_expert_stride, h->opt_expert_stride);
+    const int placement = h->expert_map_set ? -1 : h->opt_expert_stride;   // -1 table, 1 contiguous, S strided
+    pol.expert_stride = placement;
+    pol.expert_phase = placement < 0 ? 0 : (int)a.local_expert_offset;
     if (a.gemm1_weights != h->cached_w1) {
         const int r = encode_kmajor_u8_map(h->tmap_w1, a.gemm1_weights, kHidden, kGemm1Out, E, 128);
         if (r != 0) return fail(h, MOE_FP8_B200_ERR_CUDA, "cuTensorMapEncodeTiled(W1) failed: %d", r);
@@ -228,7 +227,7 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
         e = cudaMemsetAsync(h->ws.ctrl, 0, sizeof(Control), stream);
         h->counters_dirty = false;
     }
-    if (h->opt_decode && h->decode_ctas_per_sm > 0 && T <= kDecodeMaxTokens && finalize && !ex && h->opt_expert_stride == 1 &&
+    if (h->opt_decode && h->decode_ctas_per_sm > 0 && T <= kDecodeMaxTokens && finalize && !ex && placement == 1 &&
         h->opt_stop_after == 0) {
         // the whole layer as one cooperative kernel, one CTA per SM
         DecodeArgs d;
@@ -314,9 +313,21 @@ int validate(moe_fp8_b200_handle h, const moe_fp8_b200_args* a, bool need_output
         !a->gemm1_weights || !a->gemm1_weights_scale || !a->gemm2_weights || !a->gemm2_weights_scale ||
         (need_output && !a->output))
         return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "a tensor pointer is NULL");
-    if (a->local_expert_offset < 0 || a->local_expert_offset >= kNumExperts)
-        return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "local_expert_offset %lld outside [0, 256)",
-                    (long long)a->local_expert_offset);
+    // Contiguous placement: the handle's experts are whole 32-expert shards of the reference
+    // (kernel/moe_fp8.cu:462-463 filters [offset, offset + 32)), so the offset is a multiple of 32 and the
+    // block ends inside the 256 experts.  Strided placement: the offset is the phase.  Table: ignored.
+    if (h->expert_map_set) {
+    } else if (h->opt_expert_stride > 1) {
+        if (a->local_expert_offset < 0 || a->local_expert_offset >= h->opt_expert_stride)
+            return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT,
+                        "with expert stride %d local_expert_offset is the phase and must be in [0, %d)",
+                        h->opt_expert_stride, h->opt_expert_stride);
+    } else if (a->local_expert_offset < 0 || a->local_expert_offset % kShardExperts != 0 ||
+               a->local_expert_offset + h->num_local_experts > kNumExperts) {
+        return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT,
+                    "local_expert_offset %lld must be a multiple of 32 with offset + %d local experts <= 256",
+                    (long long)a->local_expert_offset, h->num_local_experts);
+    }
     if (((uintptr_t)a->hidden_states & 15u) || ((uintptr_t)a->gemm1_weights & 15u) ||
         ((uintptr_t)a->gemm2_weights & 15u) || ((uintptr_t)a->output & 15u))
         return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "hidden_states, weights and output must be 16-byte aligned");
@@ -466,6 +477,10 @@ int moe_fp8_b200_set_option(moe_fp8_b200_handle h, int option, int value)
                             h->num_local_experts);
             h->opt_expert_stride = value;
             return MOE_FP8_B200_OK;
+        case MOE_FP8_B200_OPT_WAIT_LIMIT_US:
+            if (value < 1) return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "wait limit must be at least 1 us");
+            h->opt_wait_limit_us = value;
+            return MOE_FP8_B200_OK;
         case MOE_FP8_B200_OPT_STAGE_TIMING:
             h->opt_stage_timing = value ? 1 : 0;
             h->timed_runs = 0;
@@ -484,13 +499,14 @@ int moe_fp8_b200_run(moe_fp8_b200_handle h, const moe_fp8_b200_args* args, void*
 
 namespace {
 constexpr size_t kExchangeFlagBytes = 256;
-void exchange_layout(int T, int world, ExchangeView& v)
+// Layout of a receive buffer for up to `capacity` tokens per call; depends on (capacity, world) only.
+void exchange_layout(int capacity, int world, ExchangeView& v)
 {
     v.world = world;
-    v.tokens_per_rank = (T + world - 1) / world;
-    v.present_stride = (v.tokens_per_rank + 15) / 16 * 16;
+    v.slot_rows = (capacity + world - 1) / world;
+    v.present_stride = (v.slot_rows + 15) / 16 * 16;
     v.data_offset = kExchangeFlagBytes;
-    v.rows_bytes_per_parity = (size_t)world * v.tokens_per_rank * kHidden * sizeof(__nv_bfloat16);
+    v.rows_bytes_per_parity = (size_t)world * v.slot_rows * kHidden * sizeof(__nv_bfloat16);
     v.present_bytes_per_parity = align_up((size_t)world * v.present_stride, 256);
 }
 }  // namespace
@@ -501,6 +517,21 @@ size_t moe_fp8_b200_exchange_bytes(int num_tokens, int world)
     ExchangeView v;
     exchange_layout(num_tokens, world, v);
     return v.data_offset + 2 * v.rows_bytes_per_parity + 2 * v.present_bytes_per_parity;
+}
+
+int moe_fp8_b200_exchange_regions(int capacity_tokens, int world, size_t out_offsets[4], size_t out_sizes[2])
+{
+    if (capacity_tokens < 0 || (world != 1 && world != 2 && world != 4 && world != 8) || !out_offsets || !out_sizes)
+        return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
+    ExchangeView v;
+    exchange_layout(capacity_tokens, world, v);
+    out_offsets[0] = v.data_offset;
+    out_offsets[1] = v.data_offset + v.rows_bytes_per_parity;
+    out_offsets[2] = v.data_offset + 2 * v.rows_bytes_per_parity;
+    out_offsets[3] = out_offsets[2] + v.present_bytes_per_parity;
+    out_sizes[0] = v.rows_bytes_per_parity;
+    out_sizes[1] = v.present_bytes_per_parity;
+    return MOE_FP8_B200_OK;
 }
 
 int moe_fp8_b200_run_reduce_scatter(moe_fp8_b200_handle h, const moe_fp8_b200_args* args,
@@ -515,12 +546,18 @@ int moe_fp8_b200_run_reduce_scatter(moe_fp8_b200_handle h, const moe_fp8_b200_ar
         return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "rank %d outside [0, %d)", x->rank, x->world);
     if (x->epoch == 0) return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "epoch must start at 1");
     if (args->num_tokens == 0) return MOE_FP8_B200_OK;
+    const int capacity = x->capacity_tokens > 0 ? x->capacity_tokens : h->max_tokens;
+    if (args->num_tokens > capacity)
+        return fail(h, MOE_FP8_B200_ERR_CAPACITY, "num_tokens %d exceeds the exchange buffers' capacity of %d tokens",
+                    args->num_tokens, capacity);
     ExchangeView view;
-    exchange_layout(args->num_tokens, x->world, view);
-    const size_t need = moe_fp8_b200_exchange_bytes(args->num_tokens, x->world);
+    exchange_layout(capacity, x->world, view);
+    view.tokens_per_rank = (args->num_tokens + x->world - 1) / x->world;
+    view.wait_limit_us = (uint32_t)h->opt_wait_limit_us;
+    const size_t need = moe_fp8_b200_exchange_bytes(capacity, x->world);
     if (x->buffer_bytes < need)
-        return fail(h, MOE_FP8_B200_ERR_CAPACITY, "exchange buffers hold %zu bytes, %d tokens on %d ranks need %zu",
-                    x->buffer_bytes, args->num_tokens, x->world, need);
+        return fail(h, MOE_FP8_B200_ERR_CAPACITY, "exchange buffers hold %zu bytes, a capacity of %d tokens on %d ranks needs %zu",
+                    x->buffer_bytes, capacity, x->world, need);
     for (int i = 0; i < kMaxRanks; ++i) {
         view.peer[i] = i < x->world ? static_cast<uint8_t*>(x->peer_buffers[i]) : nullptr;
         if (i < x->world && (!view.peer[i] || ((uintptr_t)view.peer[i] & 255u)))
@@ -577,8 +614,8 @@ int moe_fp8_b200_finalize(moe_fp8_b200_handle h, int num_tokens, void* output, v
 int moe_fp8_b200_set_expert_map(moe_fp8_b200_handle h, const int32_t* local_slot)
 {
     if (!h) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
-    if (!local_slot) {
-        h->opt_expert_stride = 1;
+    if (!local_slot) {   // back to what MOE_FP8_B200_OPT_EXPERT_STRIDE says (contiguous unless set otherwise)
+        h->expert_map_set = false;
         return MOE_FP8_B200_OK;
     }
     int seen[kMaxLocalExperts] = {0};
@@ -593,7 +630,7 @@ int moe_fp8_b200_set_expert_map(moe_fp8_b200_handle h, const int32_t* local_slot
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e == cudaSuccess) e = cudaMemcpy(h->ws.expert_map, local_slot, sizeof(int) * kNumExperts, cudaMemcpyHostToDevice);
     if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "expert map upload: %s", cudaGetErrorString(e));
-    h->opt_expert_stride = -1;
+    h->expert_map_set = true;
     return MOE_FP8_B200_OK;
 }
 
@@ -604,15 +641,19 @@ int moe_fp8_b200_run_host(moe_fp8_b200_handle h, const moe_fp8_b200_args* args, 
     const int T = args->num_tokens;
     if (T == 0) return MOE_FP8_B200_OK;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    const size_t b_logits = align_up(sizeof(float) * (size_t)T * kNumExperts, 256);
-    const size_t b_hidden = align_up((size_t)T * kHidden, 256);
-    const size_t b_scale = align_up(sizeof(float) * (size_t)kHiddenBlocks * T, 256);
-    const size_t b_out = align_up(sizeof(__nv_bfloat16) * (size_t)T * kHidden, 256);
-    const size_t need = b_logits + b_hidden + b_scale + b_out;
-    if (need > h->stage_bytes) {
-        if (h->stage) { cudaStreamSynchronize(stream); cudaFree(h->stage); h->stage = nullptr; h->stage_bytes = 0; }
+    // staging sized once, on the first call, for the handle's max_tokens: no later call allocates or frees
+    const size_t Tm = (size_t)h->max_tokens;
+    const size_t b_logits = align_up(sizeof(float) * Tm * kNumExperts, 256);
+    const size_t b_hidden = align_up(Tm * kHidden, 256);
+    const size_t b_scale = align_up(sizeof(float) * (size_t)kHiddenBlocks * Tm, 256);
+    const size_t b_out = align_up(sizeof(__nv_bfloat16) * Tm * kHidden, 256);
+    if (!h->stage) {
+        const size_t need = b_logits + b_hidden + b_scale + b_out;
         const cudaError_t e = cudaMalloc(&h->stage, need);
-        if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "cudaMalloc(staging %zu): %s", need, cudaGetErrorString(e));
+        if (e != cudaSuccess) {
+            h->stage = nullptr;
+            return fail(h, MOE_FP8_B200_ERR_CUDA, "cudaMalloc(staging %zu): %s", need, cudaGetErrorString(e));
+        }
         h->stage_bytes = need;
     }
     uint8_t* d_logits = h->stage;
@@ -665,25 +706,33 @@ int moe_fp8_b200_run_host_async(moe_fp8_b200_handle h, const moe_fp8_b200_args* 
     const size_t b_out = align_up(sizeof(__nv_bfloat16) * Tm * kHidden, 256);
     if (!h->pipe_stage[0]) {   // sized once for max_tokens: no allocation between pipelined calls
         const size_t need = b_logits + b_hidden + b_scale + b_out;
-        for (int i = 0; i < 2; ++i) {
-            e = cudaMalloc(&h->pipe_stage[i], need);
-            if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "cudaMalloc(pipeline staging %zu): %s", need, cudaGetErrorString(e));
+        for (int i = 0; i < 2 && e == cudaSuccess; ++i) e = cudaMalloc(&h->pipe_stage[i], need);
+        if (e != cudaSuccess) {   // all or nothing: a half-made pair would be taken for a whole one next time
+            for (int i = 0; i < 2; ++i) {
+                if (h->pipe_stage[i]) cudaFree(h->pipe_stage[i]);
+                h->pipe_stage[i] = nullptr;
+            }
+            return fail(h, MOE_FP8_B200_ERR_CUDA, "cudaMalloc(pipeline staging 2 x %zu): %s", need, cudaGetErrorString(e));
         }
         h->pipe_bytes = need;
     }
-    const int set = (int)(h->pipe_seq & 1);
-    *ticket = h->pipe_seq;
-    ++h->pipe_seq;
+    // The ticket is handed out (and the sequence advanced) only once the whole call has been enqueued:
+    // a call that fails on the way leaves no ticket behind.
+    const int64_t seq = h->pipe_seq;
+    const int set = (int)(seq & 1);
     if (T == 0) {   // nothing to move; keep the set's events meaningful for host_wait
         e = cudaEventRecord(h->pipe_out_done[set], h->pipe_out);
-        return e == cudaSuccess ? MOE_FP8_B200_OK : fail(h, MOE_FP8_B200_ERR_CUDA, "event record: %s", cudaGetErrorString(e));
+        if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "event record: %s", cudaGetErrorString(e));
+        *ticket = seq;
+        h->pipe_seq = seq + 1;
+        return MOE_FP8_B200_OK;
     }
     uint8_t* d_logits = h->pipe_stage[set];
     uint8_t* d_hidden = d_logits + b_logits;
     uint8_t* d_scale = d_hidden + b_hidden;
     uint8_t* d_out = d_scale + b_scale;
     // copy-in: the set's inputs were last read by the compute of two calls ago
-    if (*ticket >= 2) e = cudaStreamWaitEvent(h->pipe_in, h->pipe_compute_done[set], 0);
+    if (seq >= 2) e = cudaStreamWaitEvent(h->pipe_in, h->pipe_compute_done[set], 0);
     if (e == cudaSuccess)
         e = cudaMemcpyAsync(d_logits, args->routing_logits, sizeof(float) * (size_t)T * kNumExperts, cudaMemcpyHostToDevice, h->pipe_in);
     if (e == cudaSuccess) e = cudaMemcpyAsync(d_hidden, args->hidden_states, (size_t)T * kHidden, cudaMemcpyHostToDevice, h->pipe_in);
@@ -692,7 +741,7 @@ int moe_fp8_b200_run_host_async(moe_fp8_b200_handle h, const moe_fp8_b200_args* 
     if (e == cudaSuccess) e = cudaEventRecord(h->pipe_in_done[set], h->pipe_in);
     // compute: needs the inputs, and the set's output buffer must have been copied out (two calls ago)
     if (e == cudaSuccess) e = cudaStreamWaitEvent(stream, h->pipe_in_done[set], 0);
-    if (e == cudaSuccess && *ticket >= 2) e = cudaStreamWaitEvent(stream, h->pipe_out_done[set], 0);
+    if (e == cudaSuccess && seq >= 2) e = cudaStreamWaitEvent(stream, h->pipe_out_done[set], 0);
     if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "pipeline copy-in: %s", cudaGetErrorString(e));
     moe_fp8_b200_args dev = *args;
     dev.routing_logits = reinterpret_cast<const float*>(d_logits);
@@ -708,6 +757,8 @@ int moe_fp8_b200_run_host_async(moe_fp8_b200_handle h, const moe_fp8_b200_args* 
         e = cudaMemcpyAsync(args->output, d_out, sizeof(__nv_bfloat16) * (size_t)T * kHidden, cudaMemcpyDeviceToHost, h->pipe_out);
     if (e == cudaSuccess) e = cudaEventRecord(h->pipe_out_done[set], h->pipe_out);
     if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "pipeline copy-out: %s", cudaGetErrorString(e));
+    *ticket = seq;
+    h->pipe_seq = seq + 1;
     return MOE_FP8_B200_OK;
 }
 
@@ -716,7 +767,8 @@ int moe_fp8_b200_host_wait(moe_fp8_b200_handle h, int64_t ticket)
     if (!h) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
     if (ticket < 0 || ticket >= h->pipe_seq)
         return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "ticket %lld was never issued", (long long)ticket);
-    if (ticket + 2 < h->pipe_seq) return MOE_FP8_B200_OK;   // its staging set has been reused since: long finished
+    // The set's event is re-recorded by every later call that uses the set, in the same stream as the
+    // ticket's own copy-out: waiting for its latest record therefore also covers an older ticket.
     const cudaError_t e = cudaEventSynchronize(h->pipe_out_done[ticket & 1]);
     if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "waiting for copy-out: %s", cudaGetErrorString(e));
     return MOE_FP8_B200_OK;
@@ -730,7 +782,13 @@ int moe_fp8_b200_check(moe_fp8_b200_handle h, void* stream)
     int st[2] = {0, 0};
     e = cudaMemcpy(st, &h->ws.ctrl->status, sizeof(st), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "status read: %s", cudaGetErrorString(e));
-    if (st[0] != kStatusOk) h->counters_dirty = true;   // a cut-short run may have left counters behind
+    if (st[0] != kStatusOk) {
+        // The word is sticky on the device (kernels only ever move it from 0 to the first failure); it
+        // is cleared here, once reported.  A cut-short run may have left counters behind: the next run
+        // clears the whole control block first.
+        h->counters_dirty = true;
+        cudaMemset(&h->ws.ctrl->status, 0, 2 * sizeof(int));
+    }
     if (st[0] != kStatusOk)
         return fail(h, MOE_FP8_B200_ERR_DEVICE, "device status %d (detail %d): %s", st[0], st[1],
                     st[0] == kStatusGemm1Timeout   ? "GEMM1 gave up on a bounded wait"
@@ -739,6 +797,18 @@ int moe_fp8_b200_check(moe_fp8_b200_handle h, void* stream)
                     : st[0] == kStatusExchangeTimeout ? "a peer rank's rows did not arrive within the wait limit"
                     : st[0] == kStatusDecodeTimeout   ? "the decode kernel gave up on a grid barrier"
                                                    : "unknown");
+    return MOE_FP8_B200_OK;
+}
+
+int moe_fp8_b200_inject_device_status(moe_fp8_b200_handle h, int status, unsigned stale_barrier_arrivals, void* stream)
+{
+    if (!h) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(&h->ws.ctrl->status, &status, sizeof(int), cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(&h->ws.ctrl->dec_count, &stale_barrier_arrivals, sizeof(unsigned), cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "status injection: %s", cudaGetErrorString(e));
     return MOE_FP8_B200_OK;
 }
 

@@ -59,6 +59,16 @@ cudaError_t scratch_for_current_device(unsigned char** out)
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
     std::lock_guard<std::mutex> lock(g_mutex);
+    if (g_scratch_ptr[dev] != nullptr) {
+        // A cudaDeviceReset since the look-up would have unloaded the module the address came from:
+        // keep the remembered address only while the runtime still knows it as memory of this device.
+        cudaPointerAttributes at;
+        if (cudaPointerGetAttributes(&at, g_scratch_ptr[dev]) != cudaSuccess || at.type != cudaMemoryTypeDevice ||
+            at.device != dev) {
+            cudaGetLastError();
+            g_scratch_ptr[dev] = nullptr;
+        }
+    }
     if (g_scratch_ptr[dev] == nullptr) {
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_route_scratch);
@@ -67,6 +77,15 @@ cudaError_t scratch_for_current_device(unsigned char** out)
     }
     *out = g_scratch_ptr[dev];
     return cudaSuccess;
+}
+
+// True when `p` is device memory of device `dev` (or memory every device can reach: managed).
+bool on_device(const void* p, int dev)
+{
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (at.type == cudaMemoryTypeManaged) return true;
+    return at.type == cudaMemoryTypeDevice && at.device == dev;
 }
 
 }  // namespace
@@ -86,12 +105,24 @@ extern "C" int moe_fp8_b200_route_noalloc(const float* routing_logits, const voi
     }
     if (num_local_experts != 32 && num_local_experts != 64 && num_local_experts != 128 && num_local_experts != 256)
         return report(err, err_len, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "num_local_experts must be 32, 64, 128 or 256");
-    if (local_expert_offset < 0 || local_expert_offset >= kNumExperts)
-        return report(err, err_len, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "local_expert_offset outside [0, 256)");
+    // whole 32-expert shards of the reference inside the 256 experts, as in moe_fp8_b200_run
+    if (local_expert_offset < 0 || local_expert_offset % kShardExperts != 0 ||
+        local_expert_offset + num_local_experts > kNumExperts)
+        return report(err, err_len, MOE_FP8_B200_ERR_INVALID_ARGUMENT,
+                      "local_expert_offset must be a multiple of 32 with offset + num_local_experts <= 256");
     if (num_tokens == 0) return MOE_FP8_B200_OK;
     if (!routing_logits || !routing_bias || !topk_idx_out || !topk_weight_out || !expert_count_out)
         return report(err, err_len, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "a pointer argument is NULL");
 
+    // The scratch and the launch belong to the CURRENT device: tensors of another GPU are refused
+    // rather than read through whatever peer mapping may exist.
+    int cur = 0;
+    if (cudaGetDevice(&cur) != cudaSuccess)
+        return report(err, err_len, MOE_FP8_B200_ERR_CUDA, "cudaGetDevice failed");
+    if (!on_device(routing_logits, cur) || !on_device(routing_bias, cur) || !on_device(topk_idx_out, cur) ||
+        !on_device(topk_weight_out, cur) || !on_device(expert_count_out, cur))
+        return report(err, err_len, MOE_FP8_B200_ERR_INVALID_ARGUMENT,
+                      "a tensor does not live on the current CUDA device (make the tensors' GPU current before the call)");
     unsigned char* scratch = nullptr;
     cudaError_t e = scratch_for_current_device(&scratch);
     if (e != cudaSuccess)

@@ -53,10 +53,9 @@ __device__ __forceinline__ void scan_tiles_block(const Workspace& ws, int num_lo
         ws.expert_offset[num_local_experts] = total * kTileM;
         ws.num_tiles[0] = total;
         ws.ctrl->blocks_done = 0;
-        if (overflow) {
-            ws.ctrl->status = kStatusRowOverflow;
+        // the status word is sticky: the first failure stays until the host has read it
+        if (overflow && atomicCAS(&ws.ctrl->status, kStatusOk, kStatusRowOverflow) == kStatusOk)
             ws.ctrl->status_detail = warp_base + incl;
-        }
     }
     if (!overflow && e < num_local_experts) {
         const int4 info = make_int4(e, base, k, m);
@@ -86,10 +85,6 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_dispatch_kernel(
     float p_w[kTopK];
 #pragma unroll
     for (int i = 0; i < kTopK; ++i) { p_le[i] = 0; p_rank[i] = 0; p_w[i] = 0.0f; }
-    if (do_scan && blockIdx.x == 0 && threadIdx.x == 0) {
-        ws.ctrl->status = kStatusOk;
-        ws.ctrl->status_detail = 0;
-    }
     if (t < T) {
 
     int idx[kTopK];
@@ -390,7 +385,7 @@ __global__ void __launch_bounds__(kCombineThreads, 2) combine_push_kernel(Worksp
                 }
             }
             uint4* dst = reinterpret_cast<uint4*>(dst_base + (size_t)parity * ex.rows_bytes_per_parity +
-                                                  ((size_t)ex.rank * ex.tokens_per_rank + tl) * (kHidden * 2));
+                                                  ((size_t)ex.rank * ex.slot_rows + tl) * (kHidden * 2));
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint4 packed;
@@ -438,11 +433,12 @@ __global__ void __launch_bounds__(kCombineThreads) reduce_owned_kernel(Workspace
         const uint32_t* flags = reinterpret_cast<const uint32_t*>(mine_base);
         int ok = 1;
         const uint64_t t0 = global_timer_ns();
+        const uint64_t limit_ns = (uint64_t)ex.wait_limit_us * 1000ull;
         for (int src = 0; src < ex.world; ++src) {
             uint32_t it = 0;
             // epochs only grow; the signed difference also survives wrap-around
             while ((int32_t)(ld_acquire_sys_u32(flags + src) - ex.epoch) < 0) {
-                if ((++it & 0x3ffu) == 0u && global_timer_ns() - t0 > kWaitLimitNs) { ok = 0; break; }
+                if ((++it & 0x3fu) == 0u && global_timer_ns() - t0 > limit_ns) { ok = 0; break; }
             }
             if (!ok) break;
         }
@@ -462,7 +458,7 @@ __global__ void __launch_bounds__(kCombineThreads) reduce_owned_kernel(Workspace
         for (int src = 0; src < ex.world; ++src) {
             if (present[(size_t)src * ex.present_stride] == 0) continue;
             const uint4* row = reinterpret_cast<const uint4*>(mine + (size_t)parity * ex.rows_bytes_per_parity +
-                                                              ((size_t)src * ex.tokens_per_rank + tl) * (kHidden * 2));
+                                                              ((size_t)src * ex.slot_rows + tl) * (kHidden * 2));
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 const uint4 raw = row[threadIdx.x + c * kCombineThreads];

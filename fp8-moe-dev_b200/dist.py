@@ -174,7 +174,7 @@ class ShardedMoe:
         return self.layer.run_reduce_scatter(
             routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
             gemm2_weights, gemm2_weights_scale, self.local_expert_offset, routed_scaling_factor, scatter_out,
-            ptrs, nbytes, self.rank, self.world, self._epoch)
+            ptrs, nbytes, self.rank, self.world, self._epoch, capacity_tokens=self.max_tokens)
 
     def _host_stage_set(self, T: int, which: int):
         """Device staging of the host entry points: two sets, so that a call's copies can overlap

@@ -101,6 +101,27 @@ class MoeLayer:
         if rc != _lib.OK:
             self._raise(rc)
 
+    def set_stop_after_stage(self, stages: int):
+        """Diagnostics: enqueue only the first `stages` stages of the chain (1 = routing, dispatch and the
+        offset scan; 2 = + permute; 3 = + GEMM1; 4 = + GEMM2; 0 = everything)."""
+        rc = self._lib.moe_fp8_b200_set_option(self._h, _lib.OPT_STOP_AFTER_STAGE, int(stages))
+        if rc != _lib.OK:
+            self._raise(rc)
+
+    def set_wait_limit_us(self, us: int):
+        """Bound of the fused reduce-scatter's wait for peer rows (default 1 s)."""
+        rc = self._lib.moe_fp8_b200_set_option(self._h, _lib.OPT_WAIT_LIMIT_US, int(us))
+        if rc != _lib.OK:
+            self._raise(rc)
+
+    def inject_device_status(self, status: int, stale_barrier_arrivals: int = 0):
+        """Host-side failure injection for tests of the error path (see the header)."""
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._lib.moe_fp8_b200_inject_device_status(self._h, int(status), int(stale_barrier_arrivals),
+                                                         C.c_void_p(stream))
+        if rc != _lib.OK:
+            self._raise(rc)
+
     def set_expert_stride(self, stride: int):
         """Strided expert placement (multi-GPU wrapper): this handle's experts are the global ids g
         with g % stride == local_expert_offset, stacked in increasing g; stride 1 = contiguous."""
@@ -187,7 +208,7 @@ class MoeLayer:
     def run_reduce_scatter(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
                            gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
                            routed_scaling_factor, owned_output, peer_buffers, buffer_bytes: int, rank: int,
-                           world: int, epoch: int, stream: Optional[int] = None):
+                           world: int, epoch: int, stream: Optional[int] = None, capacity_tokens: int = 0):
         """Expert-parallel run with the cross-rank sum fused into the combine step:
         `owned_output` [ceil(T / world), 7168] receives this rank's token slice of the summed
         output.  `peer_buffers` are the ranks' receive buffers as mapped into this process."""
@@ -200,6 +221,7 @@ class MoeLayer:
         for i, ptr in enumerate(peer_buffers):
             x.peer_buffers[i] = int(ptr)
         x.buffer_bytes, x.rank, x.world, x.epoch = int(buffer_bytes), int(rank), int(world), int(epoch) & 0xFFFFFFFF
+        x.capacity_tokens = int(capacity_tokens)
         if stream is None:
             stream = torch.cuda.current_stream(self.device).cuda_stream
         rc = self._lib.moe_fp8_b200_run_reduce_scatter(self._h, C.byref(a), C.byref(x), C.c_void_p(stream))
@@ -331,21 +353,25 @@ class MoeLayer:
 def expert_loads(routing_logits, routing_bias, routed_scaling_factor: float = 1.0, reference_pruning: bool = True):
     """Routed rows per global expert (256 counts, a CPU list) for the first <= 4096 tokens of a
     batch: the calibration input of the load-aware expert placement.  Runs the library's routing
-    kernel alone (no weights needed)."""
+    kernel alone (no weights needed).  The dispatch policy is keyed on the batch size, so the
+    counts are those of a batch of min(T, 4096) tokens: for a longer batch they are taken under the
+    4096-token policy (keep at most 3 per shard and renormalise, no drop-third rule), which slightly
+    over-counts the rows of a T >= 10000 run but ranks the experts the same way."""
     T = min(int(routing_logits.shape[0]), _lib.NOALLOC_MAX_TOKENS)
     lg = routing_logits[:T].contiguous()
     dev = lg.device
-    idx = torch.empty((max(T, 1), 8), dtype=torch.int32, device=dev)
-    w = torch.empty((max(T, 1), 8), dtype=torch.float32, device=dev)
-    cnt = torch.zeros((NE,), dtype=torch.int32, device=dev)
-    err = C.create_string_buffer(256)
-    stream = torch.cuda.current_stream(dev).cuda_stream
-    rc = _lib.load().moe_fp8_b200_route_noalloc(lg.data_ptr(), routing_bias.data_ptr(), T, 0, NE, float(routed_scaling_factor),
-                                                int(reference_pruning), idx.data_ptr(), w.data_ptr(), cnt.data_ptr(),
-                                                C.c_void_p(stream), err, len(err))
-    if rc != _lib.OK:
-        raise MoeError(rc, err.value.decode())
-    return [int(x) for x in cnt.cpu().tolist()]
+    with torch.cuda.device(dev):   # the entry point works on the current device
+        idx = torch.empty((max(T, 1), 8), dtype=torch.int32, device=dev)
+        w = torch.empty((max(T, 1), 8), dtype=torch.float32, device=dev)
+        cnt = torch.zeros((NE,), dtype=torch.int32, device=dev)
+        err = C.create_string_buffer(256)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rc = _lib.load().moe_fp8_b200_route_noalloc(lg.data_ptr(), routing_bias.data_ptr(), T, 0, NE,
+                                                    float(routed_scaling_factor), int(reference_pruning), idx.data_ptr(),
+                                                    w.data_ptr(), cnt.data_ptr(), C.c_void_p(stream), err, len(err))
+        if rc != _lib.OK:
+            raise MoeError(rc, err.value.decode())
+        return [int(x) for x in cnt.cpu().tolist()]
 
 
 _layers: Dict[Tuple[int, int], MoeLayer] = {}

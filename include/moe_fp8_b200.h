@@ -53,7 +53,8 @@ typedef struct {
     const float* gemm1_weights_scale;   /* fp32 [E_local, 32, 56] */
     const void* gemm2_weights;          /* e4m3 [E_local, 7168, 2048] */
     const float* gemm2_weights_scale;   /* fp32 [E_local, 56, 16] */
-    int64_t local_expert_offset;        /* first global expert held here (32 * rank) */
+    int64_t local_expert_offset;        /* first global expert held here (32 * rank): a multiple of 32 with
+                                         * offset + E_local <= 256, anything else is refused */
     double routed_scaling_factor;
     void* output;                       /* bf16 [T, 7168], fully overwritten */
     int32_t num_tokens;                 /* T; 0 is a no-op (kernel/moe_fp8.cu:2671-2672) */
@@ -91,7 +92,12 @@ enum {
      * < S), stacked in increasing g; the dispatch policy is still evaluated per 32-expert shard of
      * global ids, so the S handles together produce exactly the pairs of the reference's shard calls
      * while every handle carries an equal share of every routing group. */
-    MOE_FP8_B200_OPT_EXPERT_STRIDE = 6
+    MOE_FP8_B200_OPT_EXPERT_STRIDE = 6,
+    /* Bound, in microseconds, of the wait of moe_fp8_b200_run_reduce_scatter's owner step for its peers'
+     * rows (default 1 000 000).  When it runs out the kernel completes with zero rows, the device status
+     * word records it and moe_fp8_b200_check returns MOE_FP8_B200_ERR_DEVICE; the GPU never hangs on a
+     * peer that does not arrive.  The waits inside the GEMM and decode kernels keep their fixed 1 s. */
+    MOE_FP8_B200_OPT_WAIT_LIMIT_US = 7
 };
 #define MOE_FP8_B200_DECODE_MAX_TOKENS 8
 
@@ -128,7 +134,8 @@ MOE_FP8_B200_API size_t moe_fp8_b200_workspace_bytes(int max_tokens, int num_loc
 MOE_FP8_B200_API int moe_fp8_b200_row_capacity(int max_tokens, int num_local_experts);
 
 /* Allocates the workspace on `device` (every cudaMalloc of the library happens here,
- * except the staging buffers of run_host, which its first call allocates).  num_local_experts in {32, 64, 128, 256}.  Replaces the thread-local
+ * except the staging buffers of run_host and run_host_async, which the first call of each allocates
+ * once, sized for max_tokens).  num_local_experts in {32, 64, 128, 256}.  Replaces the thread-local
  * Workspace of kernel/moe_fp8.cu:2349-2461, 2677-2689. */
 MOE_FP8_B200_API int moe_fp8_b200_create(moe_fp8_b200_handle* out, int device, int max_tokens, int num_local_experts);
 
@@ -179,20 +186,32 @@ MOE_FP8_B200_API int moe_fp8_b200_host_wait(moe_fp8_b200_handle h, int64_t ticke
  *
  * peer_buffers[i] is rank i's receive buffer as mapped into THIS process (peer access or an
  * IPC / symmetric-memory mapping; peer_buffers[rank] is the local one); every buffer holds at
- * least moe_fp8_b200_exchange_bytes(T, world) bytes, is 256-byte aligned and was zeroed once
- * before the first call.  `epoch` starts at 1 and grows by exactly 1 on every call, on every
- * rank alike (all ranks make the same sequence of calls with the same T).  The waits on peers
- * are bounded (1 s): a rank that never arrives leaves MOE_FP8_B200_ERR_DEVICE in
- * moe_fp8_b200_check, not a hung GPU. */
+ * least moe_fp8_b200_exchange_bytes(capacity, world) bytes, is 256-byte aligned and was zeroed
+ * once before the first call.  The layout inside a buffer depends on its token capacity and on
+ * `world` only, never on a call's T, so consecutive calls may use different T (all ranks the same
+ * T in the same call) without a barrier between them; `capacity_tokens` must be the same on every
+ * rank (0 = the handle's max_tokens, which then must be the same on every rank).  `epoch` starts
+ * at 1 and grows by exactly 1 on every call, on every rank alike.  The waits on peers are bounded
+ * (MOE_FP8_B200_OPT_WAIT_LIMIT_US, default 1 s): a rank that never arrives leaves
+ * MOE_FP8_B200_ERR_DEVICE in moe_fp8_b200_check, not a hung GPU. */
 typedef struct moe_fp8_b200_exchange {
     void* peer_buffers[8];
     size_t buffer_bytes;   /* size of each buffer */
     int32_t rank;
     int32_t world;         /* 1, 2, 4 or 8 */
     uint32_t epoch;
+    int32_t capacity_tokens; /* token capacity the buffers were sized for; 0 = the handle's max_tokens */
 } moe_fp8_b200_exchange;
 
-MOE_FP8_B200_API size_t moe_fp8_b200_exchange_bytes(int num_tokens, int world);
+/* Bytes of one receive buffer for calls of up to `capacity_tokens` tokens. */
+MOE_FP8_B200_API size_t moe_fp8_b200_exchange_bytes(int capacity_tokens, int world);
+
+/* Where the regions of a receive buffer lie (bytes from its start): out_offsets = {rows of parity 0,
+ * rows of parity 1, presence bytes of parity 0, of parity 1}, out_sizes = {bytes of one row region, of
+ * one presence region}.  A function of (capacity_tokens, world) alone -- the property the exchange's
+ * "no back-signal" argument rests on when T varies between calls.  Host only. */
+MOE_FP8_B200_API int moe_fp8_b200_exchange_regions(int capacity_tokens, int world, size_t out_offsets[4],
+                                                   size_t out_sizes[2]);
 
 /* args->output receives this rank's owned rows only: [ceil(T / world), 7168] bf16 (rows past
  * T, on the last ranks, are not written).  Everything else as moe_fp8_b200_run. */
@@ -203,7 +222,8 @@ MOE_FP8_B200_API int moe_fp8_b200_run_reduce_scatter(moe_fp8_b200_handle h, cons
  * index inside this handle's weight tensors of global expert g, or -1 if another handle holds it;
  * every slot 0 .. num_local_experts-1 must appear exactly once.  Lets the multi-GPU wrapper place
  * experts by measured load.  local_expert_offset is ignored while a table is set; passing NULL
- * returns to the contiguous placement.  Host pointer; synchronises the device once. */
+ * drops the table and returns to the placement MOE_FP8_B200_OPT_EXPERT_STRIDE names (contiguous
+ * unless that option was set).  Host pointer; synchronises the device once. */
 MOE_FP8_B200_API int moe_fp8_b200_set_expert_map(moe_fp8_b200_handle h, const int32_t* local_slot);
 
 /* ---- the operators either side of the layer ---------------------------------------------
@@ -238,9 +258,20 @@ MOE_FP8_B200_API int moe_fp8_b200_run_unfinalized(moe_fp8_b200_handle h, const m
                                                   moe_fp8_b200_unfinalized* views, void* stream);
 MOE_FP8_B200_API int moe_fp8_b200_finalize(moe_fp8_b200_handle h, int num_tokens, void* output, void* stream);
 
-/* Synchronises `stream` and returns MOE_FP8_B200_ERR_DEVICE if any kernel of earlier
- * runs recorded a failure in the device status word. */
+/* Synchronises `stream` and returns MOE_FP8_B200_ERR_DEVICE if any kernel of any run since the last
+ * check recorded a failure in the device status word.  The word is sticky: kernels only ever move it
+ * from 0 to the first failure, a later run does not erase it, and this call clears it once it has
+ * reported it (the next run then also clears any counters the failed run left behind).  While a
+ * failure is pending the decode kernel (batches of at most 8 tokens) does nothing. */
 MOE_FP8_B200_API int moe_fp8_b200_check(moe_fp8_b200_handle h, void* stream);
+
+/* Failure injection FROM THE HOST, for tests of the error path (nothing on the GPU faults, traps or
+ * hangs): writes `status` into the device status word as if a kernel had recorded it, and
+ * `stale_barrier_arrivals` into the arrival counter of the decode kernel's first grid barrier as a
+ * launch that gave up half-way would leave it.  Synchronises `stream`.  No counterpart in the
+ * reference, whose errors go to stderr only. */
+MOE_FP8_B200_API int moe_fp8_b200_inject_device_status(moe_fp8_b200_handle h, int status,
+                                                       unsigned stale_barrier_arrivals, void* stream);
 
 /* Mean device time in ms of the six stages (routing+dispatch, offset scan, permute, GEMM1,
  * GEMM2, combine) over the runs recorded since stage timing was switched on (at most the
@@ -283,6 +314,10 @@ MOE_FP8_B200_API int moe_fp8_b200_reference_policy(int num_tokens, int32_t out_f
  * Limits and rules:
  *  - num_tokens above MOE_FP8_B200_NOALLOC_MAX_TOKENS is refused with
  *    MOE_FP8_B200_ERR_CAPACITY (err, if given, receives the text).
+ *  - The call works on the CURRENT CUDA device: its scratch and its launch are that device's, and
+ *    tensors that live on another GPU are refused with MOE_FP8_B200_ERR_INVALID_ARGUMENT.
+ *  - local_expert_offset is a multiple of 32 with offset + num_local_experts <= 256, as in
+ *    moe_fp8_b200_run.
  *  - The first call on each GPU looks up the scratch array's device address; make that
  *    first call with the GPU current and before any stream capture begins.
  *  - Every call on a GPU uses the same scratch and the scratch keeps the last call's

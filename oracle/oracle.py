@@ -153,6 +153,18 @@ def expert_rows(hidden, hidden_scale, tokens, w1, s1, w2, s2, faithful=True, exa
     return (y, d, a2, sf) if want_all else y
 
 
+def combine(y, pair_count, row_of_pair, pair_w):
+    """out[t] = bf16(sum_p y[row_of_pair[t, p]] * pair_w[t, p]), fp32 FMA in pair order -> bf16 codes [T, 7168]."""
+    y = _c(y, np.float32)
+    pair_count = _c(pair_count, np.int32)
+    row_of_pair = _c(row_of_pair, np.int32)
+    pair_w = _c(pair_w, np.float32)
+    T = pair_count.shape[0]
+    out = np.empty((T, H), np.uint16)
+    lib().oracle_combine(_p(y), _p(pair_count), _p(row_of_pair), _p(pair_w), C.c_int(T), _p(out))
+    return out
+
+
 def layer(logits, bias_bf16, hidden, hidden_scale, w1, s1, w2, s2, local_expert_offset, rsf, mode="faithful",
           reference_pruning=True, exact_silu=False):
     """Whole layer on the host.  mode "faithful" = the reference pipeline's rounding points,

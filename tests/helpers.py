@@ -12,7 +12,7 @@ import __graft_entry__ as entry
 
 ROOT = Path(__file__).resolve().parent.parent
 REF_LIB = ROOT / "oracle" / "_ref" / "libref_moe.so"
-DIAG_DIR = ROOT / "gpurun_out" / "diag"
+DIAG_DIR = Path(os.environ["MOE_TEST_DIAG_DIR"]) if os.environ.get("MOE_TEST_DIAG_DIR") else None
 H, I, N1, NE, TOPK = 7168, 2048, 4096, 256, 8
 RSF = 2.5
 
@@ -26,7 +26,9 @@ def np_u8(t: torch.Tensor) -> np.ndarray:
 
 
 def save_diag(name: str, **arrays):
-    """Keep arrays of a failing comparison for offline reading."""
+    """Keep arrays of a failing comparison for offline reading (only when MOE_TEST_DIAG_DIR names a folder)."""
+    if DIAG_DIR is None:
+        return
     try:
         DIAG_DIR.mkdir(parents=True, exist_ok=True)
         np.savez_compressed(DIAG_DIR / f"{name}.npz", **arrays)
@@ -123,9 +125,9 @@ def reference_routing(logits: torch.Tensor, bias: torch.Tensor):
     return idx.cpu().numpy(), w.cpu().numpy()
 
 
-def reference_dispatch(logits: torch.Tensor, bias: torch.Tensor, offset: int, rsf: float = RSF):
-    """The reference's dispatch tables for this T: dict(variant, expert_count [32], pairs = per-token
-    list of (local expert, weight) in stored order, offsets [33], padded [32])."""
+def reference_dispatch_arrays(logits: torch.Tensor, bias: torch.Tensor, offset: int, rsf: float = RSF):
+    """The reference's dispatch tables for this T as arrays: dict(variant, expert_count [32], pair_n [T],
+    pair_le [T,8], pair_w fp32 [T,8] in stored order, offsets [33], padded [32], expert_token_list [32,T])."""
     T = logits.shape[0]
     lg, bs = logits.cuda().contiguous(), bias.cuda().contiguous()
     i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device="cuda")
@@ -140,13 +142,36 @@ def reference_dispatch(logits: torch.Tensor, bias: torch.Tensor, offset: int, rs
                                         vp(offs), vp(padded), vp(scratch), C.c_void_p(0))
     torch.cuda.synchronize()
     assert rc >= 0, rc
-    tlc_h, pcode_h, pw_h = tlc.cpu().numpy(), pcode.cpu().numpy(), pweight.cpu().numpy()
+    pair_n = np.minimum(tlc.cpu().numpy(), TOPK).astype(np.int32)
+    pair_le = (pcode.cpu().numpy().view(np.uint32) >> 24).astype(np.int32)
+    return dict(variant=rc, expert_count=ecount.cpu().numpy(), pair_n=pair_n, pair_le=pair_le,
+                pair_w=pweight.cpu().numpy(), offsets=offs.cpu().numpy(), padded=padded.cpu().numpy(),
+                expert_token_list=elist.cpu().numpy())
+
+
+def reference_dispatch(logits: torch.Tensor, bias: torch.Tensor, offset: int, rsf: float = RSF):
+    """As reference_dispatch_arrays, with `pairs` = per-token list of (local expert, weight) in stored order."""
+    d = reference_dispatch_arrays(logits, bias, offset, rsf)
     pairs = []
-    for t in range(T):
-        n = min(int(tlc_h[t]), TOPK)
-        pairs.append([(int(np.uint32(pcode_h[t, p]) >> 24), np.float32(pw_h[t, p])) for p in range(n)])
-    return dict(variant=rc, expert_count=ecount.cpu().numpy(), pairs=pairs, offsets=offs.cpu().numpy(),
-                padded=padded.cpu().numpy(), expert_token_list=elist.cpu().numpy())
+    for t in range(logits.shape[0]):
+        pairs.append([(int(d["pair_le"][t, p]), np.float32(d["pair_w"][t, p])) for p in range(int(d["pair_n"][t]))])
+    d["pairs"] = pairs
+    return d
+
+
+def pairs_digest(pair_n: np.ndarray, pair_le: np.ndarray, pair_w: np.ndarray) -> str:
+    """Order-independent digest of a dispatch result: sha256 over the (token, local expert, weight bits)
+    triples of all kept pairs, sorted by token, then expert, then bits."""
+    import hashlib
+    pair_n = np.asarray(pair_n).astype(np.int64)
+    T = pair_n.shape[0]
+    keep = np.arange(TOPK)[None, :] < pair_n[:, None]
+    tok = np.broadcast_to(np.arange(T, dtype=np.int64)[:, None], (T, TOPK))[keep]
+    le = np.asarray(pair_le).astype(np.int64)[keep]
+    bits = np.ascontiguousarray(pair_w, dtype=np.float32).view(np.uint32).astype(np.int64)[keep]
+    order = np.lexsort((bits, le, tok))
+    packed = np.stack([tok[order], le[order], bits[order]], axis=1)
+    return hashlib.sha256(np.ascontiguousarray(packed).tobytes()).hexdigest()[:32]
 
 
 # ------------------------------------------------------------------ metrics
@@ -164,15 +189,20 @@ def error_stats(got: np.ndarray, want: np.ndarray) -> dict:
     )
 
 
-def gpu_pairs(layer, T: int):
-    """Per-token [(local expert, slot, weight)] of the last run, expert_count, expert_offset."""
-    pc = layer.read("pair_count", T)
+def gpu_pair_arrays(layer, T: int):
+    """(pair_n [T], pair_le [T,8], slot [T,8], pair_w fp32 [T,8]) of the last run."""
+    pc = layer.read("pair_count", T).astype(np.int32)
     code = layer.read("pair_code", T * TOPK).reshape(T, TOPK)
     pw = layer.read("pair_weight", T * TOPK).reshape(T, TOPK)
-    pairs = [[(int(code[t, p] >> 24), int(code[t, p] & 0xFFFFFF), np.float32(pw[t, p])) for p in range(int(pc[t]))]
+    return pc, (code >> 24).astype(np.int32), (code & 0xFFFFFF).astype(np.int32), pw
+
+
+def gpu_pairs(layer, T: int):
+    """Per-token [(local expert, slot, weight)] of the last run, expert_count, expert_offset."""
+    pc, le, slot, pw = gpu_pair_arrays(layer, T)
+    pairs = [[(int(le[t, p]), int(slot[t, p]), np.float32(pw[t, p])) for p in range(int(pc[t]))]
              for t in range(T)]
     return pairs, layer.read("expert_count", layer.num_local_experts), layer.read("expert_offset",
                                                                                   layer.num_local_experts + 1)
 
 
-_ = os

@@ -130,6 +130,29 @@ def test_exchange_buffer_sizing(pkg):
     assert lib.moe_fp8_b200_exchange_bytes(-1, 2) == 0
 
 
+def test_exchange_regions_do_not_depend_on_the_call(pkg):
+    """The receive buffer's regions are fixed by (capacity, world): the two parities' rows and presence
+    bytes are disjoint, inside the buffer, and a call with fewer tokens than the capacity writes inside
+    the region of its own parity (it uses the first ceil(T / world) rows of every source's slot)."""
+    lib = pkg._lib.load()
+    for world in (2, 4, 8):
+        for cap in (96, 1000, 12288):
+            off = (C.c_size_t * 4)()
+            size = (C.c_size_t * 2)()
+            assert lib.moe_fp8_b200_exchange_regions(cap, world, off, size) == 0
+            total = lib.moe_fp8_b200_exchange_bytes(cap, world)
+            assert off[0] >= 4 * world and off[1] == off[0] + size[0] and off[2] == off[1] + size[0]
+            assert off[3] == off[2] + size[1] and off[3] + size[1] <= total
+            slot_rows = (cap + world - 1) // world
+            assert size[0] == world * slot_rows * 7168 * 2
+            for T in (1, 33, cap // 2, cap):
+                per = (T + world - 1) // world
+                # last byte a source can write for this T: slot of the last source, row per - 1
+                last = ((world - 1) * slot_rows + per) * 7168 * 2
+                assert last <= size[0], (world, cap, T)
+    assert lib.moe_fp8_b200_exchange_regions(128, 3, (C.c_size_t * 4)(), (C.c_size_t * 2)()) == -1
+
+
 def test_python_binding_constants_match_the_header(pkg):
     txt = (ROOT / "include" / "moe_fp8_b200.h").read_text()
     consts = dict(re.findall(r"(MOE_FP8_B200_(?:OPT|BUF|ERR)\w+)\s*=\s*(-?\d+)", txt))
@@ -139,6 +162,8 @@ def test_python_binding_constants_match_the_header(pkg):
     assert int(consts["MOE_FP8_B200_OPT_STAGE_TIMING"]) == L.OPT_STAGE_TIMING
     assert int(consts["MOE_FP8_B200_OPT_STOP_AFTER_STAGE"]) == L.OPT_STOP_AFTER_STAGE
     assert int(consts["MOE_FP8_B200_OPT_DECODE_KERNEL"]) == L.OPT_DECODE_KERNEL
+    assert int(consts["MOE_FP8_B200_OPT_EXPERT_STRIDE"]) == L.OPT_EXPERT_STRIDE
+    assert int(consts["MOE_FP8_B200_OPT_WAIT_LIMIT_US"]) == L.OPT_WAIT_LIMIT_US
     for name, val in L.BUF.items():
         assert int(consts["MOE_FP8_B200_BUF_" + name.upper()]) == val, name
     assert int(re.search(r"MOE_FP8_B200_DECODE_MAX_TOKENS\s+(\d+)", txt).group(1)) == L.DECODE_MAX_TOKENS

@@ -138,3 +138,70 @@ def test_two_gpu_expert_parallel_sum(T):
         assert p.exitcode == 0
     res = sorted(q.get(timeout=10) for _ in range(world))
     assert res == [(0, True, True, True), (1, True, True, True)], res
+
+
+def _worker_varying_t(rank, world, port, q):
+    """One ShardedMoe sized for 96 tokens, fused calls with T = 96, 33, 96, 40, 96, 8 and no barrier or
+    host synchronisation between them; the ranks are skewed against each other by device-side sleeps, so
+    that one rank's push of the next epoch overlaps the other's reduce of the current one."""
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    sys.path.insert(0, str(root))
+    sys.path.insert(0, str(root / "tests"))
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    entry.load_package()
+    from fp8_moe_dev_b200 import gen
+    from fp8_moe_dev_b200.dist import ShardedMoe, token_range
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        Tmax = 96
+        seq = [96, 33, 96, 40, 96, 8]
+        moe = ShardedMoe(Tmax)
+        w = gen.make_shard(moe.local_expert_offset, moe.num_local_experts, device="cuda", out_device="cuda")
+        cases, want = {}, {}
+        for T in sorted(set(seq)):
+            logits, bias = gen.make_routing(T, seed=100 + T)
+            hidden, hscale = gen.make_hidden(T, seed=200 + T)
+            cases[T] = [x.cuda() for x in (logits, bias, hidden, hscale)]
+            out = torch.empty(T, 7168, dtype=torch.bfloat16, device="cuda")
+            lo, hi = token_range(rank, world, T)
+            want[T] = moe.run(*cases[T], *w, 2.5, out, mode="reduce_scatter")[:hi - lo].clone()
+        torch.cuda.synchronize()
+        dist.barrier()
+        got = []
+        for i, T in enumerate(seq):
+            if (i + rank) % 2 == 0:
+                torch.cuda._sleep(3_000_000)      # about 2 ms: lets the other rank run ahead
+            scat = torch.empty((T + world - 1) // world, 7168, dtype=torch.bfloat16, device="cuda")
+            moe.run_fused(*cases[T], *w, 2.5, scatter_out=scat)
+            got.append(scat)
+        moe.layer.check()
+        ok = True
+        for T, g in zip(seq, got):
+            lo, hi = token_range(rank, world, T)
+            ok = ok and torch.equal(g[:hi - lo], want[T])
+        q.put((rank, ok))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_fused_exchange_with_varying_batch_sizes():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_varying_t, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(600)
+        assert p.exitcode == 0
+    res = sorted(q.get(timeout=10) for _ in range(world))
+    assert res == [(0, True), (1, True)], res

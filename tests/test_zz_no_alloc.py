@@ -70,3 +70,18 @@ def test_sizes_beyond_the_scratch_are_refused(pkg):
     assert int(cnt[0]) == -1, "a refused call must not touch its outputs"
     rc, msg, _, _, _ = route_noalloc(pkg, logits[:8], bias, 0, 48, 1.0)
     assert rc == pkg._lib.ERR_INVALID_ARGUMENT and msg
+    # shards are whole blocks of 32 experts inside the 256: an offset between blocks or a block that
+    # hangs over the end matches no reference call
+    for offset, E in ((16, 32), (240, 32), (224, 64), (-32, 32)):
+        rc, msg, _, _, cnt = route_noalloc(pkg, logits[:8], bias, offset, E, 1.0)
+        assert rc == pkg._lib.ERR_INVALID_ARGUMENT and "multiple of 32" in msg, (offset, E)
+    # host memory is not the current device's memory
+    lib = pkg._lib.load()
+    host = torch.zeros(8, 256)
+    idx = torch.zeros(8, TOPK, dtype=torch.int32, device="cuda")
+    w = torch.zeros(8, TOPK, device="cuda")
+    cnt = torch.zeros(32, dtype=torch.int32, device="cuda")
+    err = C.create_string_buffer(256)
+    rc = lib.moe_fp8_b200_route_noalloc(host.data_ptr(), bias.data_ptr(), 8, 0, 32, 1.0, 1, idx.data_ptr(), w.data_ptr(),
+                                        cnt.data_ptr(), torch.cuda.current_stream().cuda_stream, err, len(err))
+    assert rc == pkg._lib.ERR_INVALID_ARGUMENT and b"current CUDA device" in err.value
