@@ -161,6 +161,15 @@ def sum_over_ranks(x: float, world: int) -> float:
     return float(t.item())
 
 
+def workload_config(name: str, experts_per_gpu: int) -> dict:
+    """What was measured, in the same words for both arms (everything specific to an arm goes elsewhere)."""
+    T, skew, experts_total, desc = WORKLOADS[name]
+    return {"workload": name, "description": desc, "tokens": T, "experts_total": experts_total,
+            "experts_per_gpu": experts_per_gpu, "routing": "skewed (Zipf-like)" if skew else "uniform",
+            "reference_pruning": True,
+            "l2": f"inputs larger than L2 (weights {experts_per_gpu * 44.04e-3:.1f} GB per GPU), no flush"}
+
+
 def make_workload(name: str, rank: int, world: int):
     entry.load_package()
     from fp8_moe_dev_b200 import gen
@@ -305,9 +314,19 @@ def small_config_latencies(pkg, weights, bias_dev, reference_mod=None):
                 acc.append(np.diff(tl[:7]))
             med = np.median(np.array(acc), axis=0)
             timeline = {n: round(float(v) / 1e3, 2) for n, v in zip(names, med)}
+        active = int((layer.read("expert_count", 32) > 0).sum())
+        wbytes = active * (N1 * H + H * I)
+        gbs = wbytes / (lat * 1e-6) / 1e9
+        pk = peaks()
         out.append({"workload": f"T={T}, 32 experts, offset {off}", "latency_us": round(lat, 2),
                     "eager_wall_us_per_call": round(wall, 2),
-                    "tokens_per_s": round(T / lat * 1e6, 1), "routed_rows": rows,
+                    "tokens_per_s": round(T / lat * 1e6, 1), "routed_rows": rows, "active_experts": active,
+                    "weight_bytes": wbytes,
+                    "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                                 "frac": round(gbs / pk["hbm_gbs"], 4),
+                                 "note": "algorithmic bytes = weights of the experts that received a row (44.04 MB "
+                                         "each), each read once per call; whole-layer latency, routing included; "
+                                         f"peak = copy bandwidth of MEASURED_PEAKS.json ({pk['source']})"},
                     "decode_kernel_timeline_us": timeline,
                     "eager_latency_us": round(eager, 2),
                     "how": f"median of {reps} CUDA-graph replays of the whole layer (routing included)"})
@@ -335,6 +354,41 @@ def adjacent_ops(layer, T, dev, weights, offset):
                                              "unit": "GB/s", "frac": round(gbs / pk["hbm_gbs"], 4)},
                                 "note": "working set (3 B/element) fits L2 only below ~5800 tokens"},
             "run_unfinalized": {"tokens": T, "latency_us": round(ut[len(ut) // 2], 1)}}
+
+
+def parity_vs_reference(got_rows, token_ids, inputs_dev, T, world, n_sample=256):
+    """Outside the timed region: the rows `got_rows` (bf16 [n, 7168], this rank's output for the tokens
+    `token_ids`) against the reference operator -- the fp32 sum of its eight 32-expert `run` calls on the
+    same inputs, weights regenerated shard by shard -- for up to n_sample / world of those tokens.
+    Returns the gate quantities of the parity tests; reduced over ranks by the caller."""
+    sys.path.insert(0, str(ROOT / "tests"))
+    import helpers as hp
+    from fp8_moe_dev_b200 import gen
+    try:
+        mod = hp.reference_module()
+    except Exception as ex:
+        return {"unavailable": f"reference library not loadable: {ex}"[:200]}
+    n = min(max(1, n_sample // world), len(token_ids))
+    pick = torch.linspace(0, len(token_ids) - 1, n).round().long()
+    toks = token_ids[pick].cuda()
+    total = torch.zeros(n, H, device="cuda")
+    rows_ref = 0
+    logits, bias, hidden, hscale = inputs_dev
+    part = torch.zeros(T, H, dtype=torch.bfloat16, device="cuda")
+    keep_alive = []   # the reference caches a transposed copy of the weight scales BY POINTER: every shard's
+    for s_ in range(NE // 32):   # scale tensors must keep their own addresses while it is in use
+        w = gen.make_shard(32 * s_, 32, base_seed=1000, device="cuda", out_device="cuda")
+        keep_alive.append((w[1], w[3]))
+        mod.run(logits, bias, hidden, hscale, *w, 32 * s_, RSF, part)
+        torch.cuda.synchronize()
+        total += part[toks].float()
+        rows_ref += int(hp.reference_dispatch_arrays(logits, bias, 32 * s_)["pair_n"].sum())
+        del w
+    got = got_rows[pick.cuda()].float()
+    diff = (got - total).abs()
+    return {"tokens_compared": n, "ratio": float((diff <= 1.0 + 0.3 * total.abs()).float().mean()),
+            "rel_l2": float((got - total).norm() / (total.norm() + 1e-30)), "max_abs": float(diff.max()),
+            "mean_abs": float(diff.mean()), "rows_ref": rows_ref}
 
 
 def cpu_baseline(inputs, weights, sample_tokens=64):
@@ -372,7 +426,10 @@ def run_ours(args, rank, world, local):
         # them and keeps the fastest
         from fp8_moe_dev_b200 import gen
         cands = {}
-        loads = pkg.expert_loads(dev[0], dev[1], RSF)   # calibration: routed rows per expert, first 4096 tokens
+        # calibration of the load-aware placement: routed rows per expert of ANOTHER batch (same
+        # distribution and routing bias, different seed), never of the batch that is timed
+        cal_logits, _ = gen.make_routing(4096, seed=12345, skew=WORKLOADS[args.workload][1])
+        loads = pkg.expert_loads(cal_logits.cuda(), dev[1], RSF)
         for place in (("contiguous", "balanced") if args.placement == "auto" else (args.placement,)):
             m = ShardedMoe(T, rank, world, local, placement=place, loads=loads)
             w = weights if place == "contiguous" else gen.make_experts(m.expert_ids, base_seed=1000, device="cuda",
@@ -382,8 +439,10 @@ def run_ours(args, rank, world, local):
             placement_ms = {}
             for place, (m, w) in cands.items():
                 try:
+                    # both candidates are timed like the headline (same steps and warm-up), so that the
+                    # contiguous figure stands beside the chosen one as a number of the same kind
                     placement_ms[place] = round(time_steps(lambda: m.run(*dev, *w, RSF, out, mode=args.collective,
-                                                                          scatter_out=scat), 5, 3, world), 4)
+                                                                          scatter_out=scat), args.steps, args.warmup, world), 4)
                     m.layer.check()
                 except Exception as ex:   # a candidate that does not run is not a candidate
                     sys.stderr.write(f"placement {place} failed on rank {rank}: {ex}\n")
@@ -409,6 +468,7 @@ def run_ours(args, rank, world, local):
         layer.run(*dev, w1, s1, w2, s2, offset, RSF, out)
         return combine_partials(out, mode, scatter_out=scat)
 
+    contiguous_ms = placement_ms.get("contiguous") if placement_ms else None
     step()
     layer.check()
     rows_local = int(layer.read("pair_count", T).sum())
@@ -421,6 +481,8 @@ def run_ours(args, rank, world, local):
     stages, timed_runs = layer.stage_times()
     layer.set_stage_timing(False)
     layer.check()
+    if moe is not None and moe.placement == "contiguous":
+        contiguous_ms = ms
 
     # end to end: per-step inputs start in pinned host memory, the result ends in host memory
     pin = [x.pin_memory() for x in (inputs[0], inputs[2], inputs[3])]
@@ -482,6 +544,31 @@ def run_ours(args, rank, world, local):
                     for m in ("fused", "reduce_scatter", "all_reduce") if m != args.collective}
         layer.check()
 
+    # parity with the reference operator on the very tensors that were timed (outside the timed region)
+    parity = None
+    if not args.skip_parity:
+        result = step()
+        layer.check()
+        if world == 1:
+            rows_got, ids = out, torch.arange(T)
+        else:
+            lo = min(rank * per, T)
+            hi = min(lo + per, T)
+            rows_got = (result if args.collective != "all_reduce" else out[lo:hi])[:hi - lo]
+            ids = torch.arange(lo, hi)
+        par = parity_vs_reference(rows_got, ids, dev, T, world)
+        if "unavailable" in par:
+            parity = par
+        else:
+            parity = {"vs": "fp32 sum of the reference's eight 32-expert run() calls, same inputs",
+                      "tokens_compared": int(sum_over_ranks(par["tokens_compared"], world)),
+                      "ratio_atol1_rtol0.3": round(-max_over_ranks(-par["ratio"], world), 6),
+                      "rel_l2": round(max_over_ranks(par["rel_l2"], world), 6),
+                      "max_abs": round(max_over_ranks(par["max_abs"], world), 5),
+                      "mean_abs": round(max_over_ranks(par["mean_abs"], world), 6),
+                      "rows_ours": rows_total, "rows_ref": par["rows_ref"],
+                      "reduction": "min ratio / max error over ranks; each rank compares tokens of its own output slice"}
+
     pk = peaks()
     g1_ms = max_over_ranks(stages["gemm1"], world)
     g1_flops = rows_max * GEMM1_FLOPS_PER_ROW  # the slowest rank's launch
@@ -492,14 +579,19 @@ def run_ours(args, rank, world, local):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
         "latency_us": round(ms * 1e3, 1), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "e4m3 x e4m3 -> f32 accumulate, bf16 out", "data": "synthetic",
-        "config": {"workload": args.workload, "description": WORKLOADS[args.workload][3], "tokens": T,
-                   "experts_total": WORKLOADS[args.workload][2], "experts_per_gpu": E, "routed_rows_total": rows_total,
-                   "routed_rows_max_rank": rows_max, "reference_pruning": True,
-                   "l2": f"inputs larger than L2 (weights {E * 44.04e-3:.1f} GB on this GPU), no flush",
-                   "ideal_scaling_bound": round(rows_total / rows_max, 3) if rows_max else None,
-                   "collective": None if world == 1 else args.collective,
-                   "expert_placement": None if world == 1 else moe.placement, "placement_trial_ms": placement_ms,
-                   "other_collective_ms_per_step": other_ms},
+        "config": workload_config(args.workload, E),
+        "run": {"routed_rows_total": rows_total, "routed_rows_max_rank": rows_max,
+                "ideal_scaling_bound": round(rows_total / rows_max, 3) if rows_max else None,
+                "collective": None if world == 1 else args.collective,
+                "expert_placement": None if world == 1 else moe.placement,
+                "expert_placement_note": None if world == 1 else
+                    "contiguous = blocks of 256/N experts per rank (local_expert_offset = 256/N * rank, the "
+                    "partition the layer's interface names); balanced = experts dealt by the routed rows of a "
+                    "calibration batch drawn with another seed; auto keeps the faster of the two in a short trial",
+                "placement_trial_ms": placement_ms, "contiguous_ms_per_step": contiguous_ms,
+                "contiguous_tokens_per_s": round(T / contiguous_ms * 1e3, 1) if contiguous_ms else None,
+                "other_collective_ms_per_step": other_ms},
+        "parity": parity,
         "clocks": clk.summary(),
         "e2e": None if args.skip_e2e else {"value": round(T / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -522,7 +614,8 @@ def run_ours(args, rank, world, local):
                      "frac_of_nominal": round(achieved / FP8_NOMINAL_TFLOPS, 4),
                      "flops_per_launch": g1_flops, "avg_launch_ms": round(g1_ms, 4), "timed_launches": timed_runs,
                      "traffic": (NCU_GEMM1_DRAM_BYTES_32_EXPERTS_T12288 * E / 32) if T >= 8192 else None,
-                     "traffic_note": "ncu dram bytes of GEMM1 at T=12288 / 32 experts (912 MB) x experts/32"},
+                     "traffic_note": "SCALED, not measured at this size: ncu dram bytes of GEMM1 at T=12288 on one "
+                                     "32-expert shard (912 MB, weights 97 % of it and read once) x experts/32"},
     }
     if rank == 0 and world == 1:
         if not args.skip_small:
@@ -550,7 +643,8 @@ def run_reference(args, rank, world, local):
         return {"impl": "reference", "metric": "moe_layer_tokens_per_s", "value": cb["value"], "unit": "tokens/s",
                 "n_gpus": world, "steps": 1, "warmup": 0, "ms_per_step": None, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": args.workload, "note": f"reference GPU library unavailable ({ex}); CPU port timed"},
+                "config": workload_config(args.workload, E),
+                "run": {"note": f"reference GPU library unavailable ({ex}); CPU port timed"},
                 "cpu_baseline": cb,
                 "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     dev = [x.cuda() for x in inputs]
@@ -579,10 +673,11 @@ def run_reference(args, rank, world, local):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
             "latency_us": round(ms * 1e3, 1), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "e4m3 x e4m3 -> f32 accumulate, bf16 out", "data": "synthetic",
-            "config": {"workload": args.workload, "description": WORKLOADS[args.workload][3], "tokens": T,
-                       "experts_total": WORKLOADS[args.workload][2], "experts_per_gpu": E,
-                       "how": f"{shards} sequential reference calls of 32 experts per rank on identical pointers "
-                              "(its pointer-keyed caches may hit), bf16 adds, same NCCL all-reduce"},
+            "config": workload_config(args.workload, E),
+            "run": {"how": f"{shards} sequential reference calls of 32 experts per rank on identical pointers "
+                           "(its pointer-keyed caches may hit), bf16 adds, then NCCL "
+                           + ("reduce_scatter" if args.collective == "fused" else args.collective),
+                    "expert_placement": "contiguous"},
             "clocks": clk.summary(),
             "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": 0, "kind": "reference",
                              "sample": "the reference's own GPU build (oracle/_ref/libref_moe.so) on the same "
@@ -610,6 +705,7 @@ def main():
     ap.add_argument("--skip-small", action="store_true", help="skip the T=1/16/1024 single-shard latencies")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the host fp32 baseline")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
+    ap.add_argument("--skip-parity", action="store_true", help="skip the comparison with the reference operator")
     args = ap.parse_args()
     if not args.skip_e2e:
         args.warmup = max(args.warmup, 3)

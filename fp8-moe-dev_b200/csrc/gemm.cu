@@ -18,10 +18,17 @@
 //   warp 1      MMA issuer: 4 x tcgen05.mma (M128 N256 K32, e4m3 -> fp32) per K block into one
 //               of two 256-column TMEM accumulator stages, overwrite mode on the first
 //   warp 2      TMEM allocation / release
-//   warps 4-11  promotion + epilogue: after each K block, tcgen05.ld of the raw block product,
-//               multiply by the row scale x weight-block scale, add into fp32 registers (the
-//               scales are arbitrary fp32 values, so the block-scaled MMA kinds cannot be used);
-//               each thread owns one row and 128 of the tile's 256 columns
+//   warps 4-11  promotion: after each K block, tcgen05.ld of the raw block product, multiply by
+//               the row scale x weight-block scale, add into fp32 registers (the scales are
+//               arbitrary fp32 values, so the block-scaled MMA kinds cannot be used); each thread
+//               owns one row and 128 of the tile's 256 columns.  When a tile's K loop ends they
+//               round the accumulators to bf16 into a 64 KB shared-memory tile and go straight on
+//               to the next tile's K loop
+//   warps 2-3   tile epilogue, off the promotion warps' critical path: from the bf16 tile either
+//               SwiGLU + 1x128 requantisation + stores (GEMM1, a warp per row, the row's 128
+//               output bytes in one coalesced store) or four TMA tile stores (GEMM2)
+// (The split-K instantiation for batches of at most four tokens keeps the epilogue in the
+// promotion warps: its tiles hold at most four rows.)
 // Every mbarrier wait is bounded; a wait that runs out sets the CTA's abort flag, all roles
 // unwind, TMEM is released and the error is reported through Control::status.
 #include <cuda.h>
@@ -33,7 +40,6 @@
 namespace moe {
 
 constexpr int kGemmThreads = 384;
-constexpr int kStages = 4;
 constexpr int kTileN = 256;
 constexpr int kATileBytes = kTileM * kBlock;   // 16384
 constexpr int kBTileBytes = kTileN * kBlock;   // 32768
@@ -47,13 +53,16 @@ constexpr int kSplitKMaxSplit = 14;  // 56 K blocks / 4
 
 static_assert(kHiddenBlocks / 4 <= kSplitKMaxSplit, "split-K register array too small");
 
+constexpr int kMaxStages = 4;
 struct GemmShared {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint64_t amax_bar[2];
     uint64_t splitk_bar;
+    uint64_t tile_full;    // the bf16 tile in shared memory is complete (8 promotion warps arrive)
+    uint64_t tile_empty;   // the epilogue warps are done with it
     uint32_t tmem_base;
     int abort;
     int splitk_last;
@@ -64,16 +73,25 @@ struct GemmScratch {
     alignas(16) float splitk_sum[kSplitKMaxRows][256];   // read and written as float4
     float amax[2][2][kTileM];
 };
-constexpr int kOutStageCols = 32;                                   // bf16 columns per staged piece (64 B rows)
-constexpr int kOutStageBytes = 32 * kOutStageCols * 2;              // one warp's 32 rows: 2 KB
-constexpr int kOutStageTotal = kEpilogueWarps * 2 * kOutStageBytes; // two pieces per warp: 32 KB
-constexpr size_t kGemmCoreBytes = 1024;                             // GemmShared, padded: the staging wants 1 KB alignment
+// The finished tile on its way to the epilogue warps: 128 rows x 256 bf16 columns as four panels of
+// 64 columns.  A panel is 128 rows of 128 bytes in the 128-byte swizzle (16-byte chunk index XOR
+// row mod 8): what a TMA tile store with SWIZZLE_128B reads, and conflict-free both for the
+// promotion threads (one row each) and for the epilogue warps (one row per warp).
+constexpr int kPanelCols = 64;
+constexpr int kPanelBytes = kTileM * kPanelCols * 2;                // 16 KB
+constexpr int kTilePanels = kTileN / kPanelCols;                    // 4
+constexpr int kTileStageBytes = kTilePanels * kPanelBytes;          // 64 KB
+constexpr size_t kGemmCoreBytes = 1024;                             // GemmShared, padded: the panels want 1 KB alignment
 static_assert(sizeof(GemmShared) <= kGemmCoreBytes, "barrier block grew");
+
+// Operand ring depth: four stages for the split-K kernel, three where 64 KB go to the tile hand-off.
+template <bool SPLITK>
+__host__ __device__ constexpr int gemm_stages() { return SPLITK ? 4 : 3; }
 
 template <int MODE, bool SPLITK>
 constexpr size_t gemm_smem_bytes() {
-    return 1024 + (size_t)kStages * kStageBytes + kGemmCoreBytes +
-           ((MODE == 2 && !SPLITK) ? (size_t)kOutStageTotal : sizeof(GemmScratch));
+    return 1024 + (size_t)gemm_stages<SPLITK>() * kStageBytes + kGemmCoreBytes +
+           (SPLITK ? sizeof(GemmScratch) : (size_t)kTileStageBytes);
 }
 static_assert(gemm_smem_bytes<2, false>() <= 227 * 1024 && gemm_smem_bytes<1, true>() <= 227 * 1024, "shared memory");
 
@@ -212,14 +230,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
 {
     constexpr int kKBlocks = (MODE == 1) ? kHiddenBlocks : kInterBlocks;
     constexpr int kTilesN = (MODE == 1) ? (kInter / kBlock) : (kHidden / kTileN);  // 16 / 28
+    constexpr int kStages = gemm_stages<SPLITK>();
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     GemmShared* sh = reinterpret_cast<GemmShared*>(smem_raw + (base - raw_addr) + (size_t)kStages * kStageBytes);
     uint8_t* after_core = reinterpret_cast<uint8_t*>(sh) + kGemmCoreBytes;   // 1 KB aligned
-    GemmScratch* sc = reinterpret_cast<GemmScratch*>(after_core);           // not in the plain GEMM2
+    GemmScratch* sc = reinterpret_cast<GemmScratch*>(after_core);           // split-K kernels only
     (void)sc;
+    uint8_t* tile_stage = after_core;                                       // others: the bf16 tile (64 KB)
+    (void)tile_stage;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -236,6 +257,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
             mbar_init(smem_u32(&sh->amax_bar[s]), kEpilogueThreads);
         }
         mbar_init(smem_u32(&sh->splitk_bar), kEpilogueThreads);
+        mbar_init(smem_u32(&sh->tile_full), kEpilogueWarps);
+        mbar_init(smem_u32(&sh->tile_empty), MODE == 1 ? 2 : 1);
         sh->abort = 0;
         fence_mbar_init();
     }
@@ -338,6 +361,73 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                     }
                 }
             }
+        } else if (!SPLITK && warp >= 2) {
+            // ------------------------------------------------------------ tile epilogue
+            // Runs one tile behind the promotion warps, while they are in the next tile's K loop.
+            const int ew = warp - 2;
+            uint32_t ti = 0;
+            bool ok = MODE == 1 || ew == 0;   // GEMM2's stores need one thread only
+            for (int u = blockIdx.x; ok && u < plan.units; u += gridDim.x, ++ti) {
+                const TileCoord tc = decode_tile(ws, u, kTilesN);
+                ok = mbar_wait(smem_u32(&sh->tile_full), ti & 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if (MODE == 2) {
+                    // Y: four 128-row x 64-column tile stores.  Rows past the tile's valid rows land in
+                    // the expert's padding, which nobody reads.
+                    if (lane == 0) {
+#pragma unroll
+                        for (int p = 0; p < kTilePanels; ++p)
+                            tma_store_2d(&tmap_out, smem_u32(tile_stage + p * kPanelBytes), tc.n * kTileN + p * kPanelCols,
+                                         tc.row0);
+                        bulk_commit_group();
+                        bulk_wait_group_read<0>();   // the panels have been read: they may be overwritten
+                        mbar_arrive(smem_u32(&sh->tile_empty));
+                    }
+                    __syncwarp();
+                } else {
+                    // GEMM1: D was rounded to bf16 on its way here (the reference materialises it in
+                    // bf16).  One row per warp pass, lane l owns SwiGLU columns 4l..4l+3 of the tile's
+                    // 128-column block: x1 from panels 0-1 (linear branch), x2 from panels 2-3 (gated
+                    // branch); v = silu(x2) * x1 in fp32, row absmax by shuffles, scale = amax / 448
+                    // (1 for an all-zero block), e4m3 codes -> 128 coalesced bytes per row.
+                    const int r_end = tc.rows < (ew + 1) * (kTileM / 2) ? tc.rows : (ew + 1) * (kTileM / 2);
+                    const uint32_t pan = (uint32_t)(lane >> 4) * kPanelBytes;
+                    const uint32_t chunk = (uint32_t)(lane & 15) >> 1, sub = (uint32_t)(lane & 1) * 8u;
+                    for (int r = ew * (kTileM / 2); r < r_end; ++r) {
+                        const uint8_t* src = tile_stage + pan + r * 128 + ((chunk ^ (uint32_t)(r & 7)) << 4) + sub;
+                        const uint2 l1 = *reinterpret_cast<const uint2*>(src);
+                        const uint2 l2 = *reinterpret_cast<const uint2*>(src + 2 * kPanelBytes);
+                        const float x1[4] = {__uint_as_float(l1.x << 16), __uint_as_float(l1.x & 0xffff0000u),
+                                             __uint_as_float(l1.y << 16), __uint_as_float(l1.y & 0xffff0000u)};
+                        const float x2[4] = {__uint_as_float(l2.x << 16), __uint_as_float(l2.x & 0xffff0000u),
+                                             __uint_as_float(l2.y << 16), __uint_as_float(l2.y & 0xffff0000u)};
+                        float v[4];
+                        float amax = 0.0f;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float silu = silu_exact ? x2[j] / (1.0f + __expf(-x2[j]))
+                                                          : x2[j] * (0.5f * (x2[j] * rsqrtf(fmaf(x2[j], x2[j], 4.0f)) + 1.0f));
+                            v[j] = silu * x1[j];
+                            amax = fmaxf(amax, fabsf(v[j]));
+                        }
+#pragma unroll
+                        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+                        const float scale = (amax > 0.0f) ? (amax / 448.0f) : 1.0f;
+                        const float inv_scale = 1.0f / scale;
+                        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0] * inv_scale, v[1] * inv_scale),
+                                                                     __NV_SATFINITE, __NV_E4M3);
+                        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2] * inv_scale, v[3] * inv_scale),
+                                                                     __NV_SATFINITE, __NV_E4M3);
+                        const int grow = tc.row0 + r;
+                        reinterpret_cast<uint32_t*>(ws.a2 + (size_t)grow * kInter + tc.n * kBlock)[lane] = lo | (hi << 16);
+                        if (lane == 0) ws.sfa2[(size_t)tc.n * ws.m_cap + grow] = scale;
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&sh->tile_empty));
+                }
+            }
+            if (MODE == 2 && ew == 0 && lane == 0) bulk_wait_group<0>();   // stores performed before the CTA leaves
         }
     } else {
         // ---------------------------------------------------------------- promotion + epilogue
@@ -423,6 +513,41 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
             }
             if (!ok) break;
 
+            if (!SPLITK) {
+                // Hand the tile to the epilogue warps: accumulators rounded to bf16 (what both the
+                // GEMM1 and the GEMM2 result are rounded to anyway) into the shared-memory panels, a
+                // thread's first 64 columns into panel pa, its other 64 into panel pb.  The panels
+                // were released a whole K loop ago, so the wait below does not block in practice.
+                if (tile_iter > 0) {
+                    ok = mbar_wait(smem_u32(&sh->tile_empty), (tile_iter - 1) & 1u, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                }
+                if (warp_has_rows) {
+                    const int pa = (MODE == 1) ? h : 2 * h;
+                    const int pb = (MODE == 1) ? 2 + h : 2 * h + 1;
+                    uint8_t* ra = tile_stage + pa * kPanelBytes + row * 128;
+                    uint8_t* rb = tile_stage + pb * kPanelBytes + row * 128;
+                    const uint32_t sw = (uint32_t)(row & 7);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        uint4 pk;
+                        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) h2[i] = __floats2bfloat162_rn(acc[8 * c + 2 * i], acc[8 * c + 2 * i + 1]);
+                        *reinterpret_cast<uint4*>(ra + (((uint32_t)c ^ sw) << 4)) = pk;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            h2[i] = __floats2bfloat162_rn(acc[64 + 8 * c + 2 * i], acc[64 + 8 * c + 2 * i + 1]);
+                        *reinterpret_cast<uint4*>(rb + (((uint32_t)c ^ sw) << 4)) = pk;
+                    }
+                    if (MODE == 2) fence_proxy_async_smem();   // the TMA stores read these writes
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&sh->tile_full));
+                ++tile_iter;
+                continue;
+            }
             const bool valid = row < tc.rows;
             if (SPLITK && plan.split > 1) {
                 // Split-K reduction (batches of at most kSplitKMaxRows tokens, so a tile has at most
@@ -520,38 +645,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                     }
                     if (h == 0) ws.sfa2[(size_t)tc.n * ws.m_cap + grow] = scale;
                 }
-            } else if (MODE == 2 && !SPLITK) {
-                // Y goes out through shared memory and TMA: a thread owns one row, so direct stores
-                // touch 32 lines per warp instruction and keep the memory pipeline busy for longer
-                // than the MMA look-ahead covers.  Each warp stages its 32 rows in pieces of 32
-                // columns (64-byte rows, 64B-swizzled as the tensor map expects, which also keeps
-                // the staging writes conflict-free), two pieces alternating; rows past the tile's
-                // valid rows land in the expert's padding, which nobody reads.
-                if (warp_has_rows) {
-                    uint8_t* stg = after_core + ew * (2 * kOutStageBytes);
-#pragma unroll
-                    for (int p = 0; p < 128 / kOutStageCols; ++p) {
-                        uint8_t* buf = stg + (p & 1) * kOutStageBytes;
-                        if (lane == 0) bulk_wait_group_read<1>();   // the piece stored from this buffer two pieces ago
-                        __syncwarp();
-#pragma unroll
-                        for (int c4 = 0; c4 < 4; ++c4) {
-                            uint4 pk;
-                            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                h2[i] = __floats2bfloat162_rn(acc[p * kOutStageCols + c4 * 8 + 2 * i],
-                                                              acc[p * kOutStageCols + c4 * 8 + 2 * i + 1]);
-                            *reinterpret_cast<uint4*>(buf + lane * 64 + ((c4 ^ ((lane >> 1) & 3)) * 16)) = pk;
-                        }
-                        fence_proxy_async_smem();
-                        __syncwarp();
-                        if (lane == 0) {
-                            tma_store_2d(&tmap_out, smem_u32(buf), tc.n * kTileN + 128 * h + p * kOutStageCols, tc.row0 + q * 32);
-                            bulk_commit_group();
-                        }
-                    }
-                }
             } else {
                 if (valid) {
                     uint4* dst = reinterpret_cast<uint4*>(ws.y + (size_t)grow * kHidden + tc.n * kTileN + 128 * h);
@@ -569,10 +662,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                     }
                 }
             }
-        }
-        if (MODE == 2 && !SPLITK) {
-            if (lane == 0) bulk_wait_group<0>();   // all of this warp's stores performed before the CTA leaves
-            __syncwarp();
         }
     }
 
@@ -651,8 +740,8 @@ int encode_rows_1k_map(void* out_map, const void* base, uint64_t row_bytes, uint
     return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
-// bf16 [rows, cols] row-major output; box = 32 columns x 32 rows with the 64-byte swizzle (GEMM2's
-// staged stores).
+// bf16 [rows, cols] row-major output; box = 64 columns x 128 rows with the 128-byte swizzle (one panel
+// of GEMM2's finished tile).
 int encode_out_bf16_map(void* out_map, void* base, uint64_t cols, uint64_t rows)
 {
     EncodeTiledFn fn = get_encode_fn();
@@ -660,10 +749,10 @@ int encode_out_bf16_map(void* out_map, void* base, uint64_t cols, uint64_t rows)
     CUtensorMap* m = static_cast<CUtensorMap*>(out_map);
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {cols * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kOutStageCols, 32};
+    const cuuint32_t box[2] = {(cuuint32_t)kPanelCols, (cuuint32_t)kTileM};
     const cuuint32_t es[2] = {1, 1};
     const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 

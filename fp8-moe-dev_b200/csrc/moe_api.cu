@@ -762,6 +762,16 @@ int moe_fp8_b200_run_host_async(moe_fp8_b200_handle h, const moe_fp8_b200_args* 
     return MOE_FP8_B200_OK;
 }
 
+int moe_fp8_b200_copy_rows_h2d(void* dst_device, size_t dst_pitch, const void* src_host, size_t src_pitch,
+                               size_t row_bytes, size_t rows, void* stream)
+{
+    if (!dst_device || !src_host || row_bytes > dst_pitch || row_bytes > src_pitch) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
+    if (rows == 0 || row_bytes == 0) return MOE_FP8_B200_OK;
+    const cudaError_t e = cudaMemcpy2DAsync(dst_device, dst_pitch, src_host, src_pitch, row_bytes, rows,
+                                            cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? MOE_FP8_B200_OK : MOE_FP8_B200_ERR_CUDA;
+}
+
 int moe_fp8_b200_host_wait(moe_fp8_b200_handle h, int64_t ticket)
 {
     if (!h) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;

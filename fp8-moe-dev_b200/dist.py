@@ -225,16 +225,25 @@ class ShardedMoe:
         with torch.cuda.stream(self._s_in):
             if seq >= 2:
                 self._s_in.wait_event(st["ev_compute"])   # the set's inputs were read two calls ago
-            # this rank's slice, straight into its place in the gathered tensors
+            # this rank's slice, straight into its place in the gathered tensors: two contiguous runs of
+            # rows, and the rank's columns of the [56, T] scale matrix as ONE strided copy (a plain
+            # tensor copy of that view would pack it through pageable memory and block the host)
             st["logits"][lo:lo + per].copy_(routing_logits[lo:lo + per], non_blocking=True)
             st["hidden"][lo:lo + per].view(torch.uint8).copy_(hidden_states[lo:lo + per].view(torch.uint8), non_blocking=True)
-            st["scale_parts"][self.rank].copy_(hidden_states_scale[:, lo:lo + per], non_blocking=True)
+            part = st["scale_parts"][self.rank]
+            rc = self.layer._lib.moe_fp8_b200_copy_rows_h2d(
+                part.data_ptr(), per * 4, hidden_states_scale.data_ptr() + lo * 4, T * 4, per * 4, 56,
+                self._s_in.cuda_stream)
+            if rc != 0:
+                raise RuntimeError(f"moe_fp8_b200_copy_rows_h2d failed: {rc}")
+            # the all-gather that replicates the inputs runs behind the copies on the copy-in stream, so
+            # that it overlaps the previous call's compute instead of standing in front of this call's
+            gather_token_slices(st["logits"], st["hidden"].view(torch.uint8), st["scale_parts"], st["scale"],
+                                self.rank, W, self.group)
             st["ev_in"].record(self._s_in)
         cur.wait_event(st["ev_in"])
         if seq >= 2:
             cur.wait_event(st["ev_out"])                  # the set's output was copied out two calls ago
-        gather_token_slices(st["logits"], st["hidden"].view(torch.uint8), st["scale_parts"], st["scale"], self.rank, W,
-                            self.group)
         if mode == "fused" and W > 1:
             res = self.run_fused(st["logits"], routing_bias, st["hidden"], st["scale"], gemm1_weights, gemm1_weights_scale,
                                  gemm2_weights, gemm2_weights_scale, routed_scaling_factor, scatter_out=st["out"])
@@ -256,8 +265,8 @@ class ShardedMoe:
         """Blocks until the output of call `ticket` is in host memory."""
         if self._host_stage is None or not 0 <= ticket < self._host_seq:
             raise ValueError(f"ticket {ticket} was never issued")
-        if ticket + 2 < self._host_seq:
-            return   # its staging set has been reused since: long finished
+        # the set's event is re-recorded by every later call on the set, in the stream of the ticket's own
+        # copy-out: its latest record also covers the older ticket
         self._host_stage[ticket & 1]["ev_out"].synchronize()
 
     def run_host(self, *args, **kwargs):

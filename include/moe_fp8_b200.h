@@ -174,6 +174,13 @@ MOE_FP8_B200_API int moe_fp8_b200_run_host_async(moe_fp8_b200_handle h, const mo
                                                  int64_t* ticket);
 MOE_FP8_B200_API int moe_fp8_b200_host_wait(moe_fp8_b200_handle h, int64_t ticket);
 
+/* Strided host-to-device copy of `rows` pieces of `row_bytes` bytes (one cudaMemcpy2DAsync on `stream`):
+ * what a rank of the multi-GPU wrapper uses to fetch ITS token columns [lo, lo + n) of the host-resident
+ * hidden_states_scale [56, T] -- a strided view that a plain copy would first have to pack on the host.
+ * The source should be pinned.  No counterpart in the reference (device tensors only). */
+MOE_FP8_B200_API int moe_fp8_b200_copy_rows_h2d(void* dst_device, size_t dst_pitch, const void* src_host,
+                                                size_t src_pitch, size_t row_bytes, size_t rows, void* stream);
+
 /* ---- expert-parallel run with the reduce-scatter fused into the combine step -----------
  * No counterpart in the reference (it has no multi-GPU code; its local_expert_offset
  * argument, kernel/moe_fp8.cu:2671, only says which 32 experts a rank holds).  `world` ranks
