@@ -495,34 +495,35 @@ def run_ours(args, rank, world, local):
 
         def e2e_step():
             # pipelined host path, two calls in flight: every step copies its inputs from pinned host
-            # memory and lands its output in host memory; the output of step i-1 is awaited (read)
-            # right after step i has been issued
+            # memory and lands its output in host memory.  Step i first waits for (reads) the output of
+            # step i-2, whose host buffer it reuses, then issues its own call: while step i-1 computes,
+            # step i's inputs come in and step i-2's output has gone out.
             i = pipe["i"]
+            if i >= 2:
+                layer.host_wait(pipe["tickets"][i - 2])
             pipe["tickets"].append(layer.run_host_async(pin[0], dev[1], pin[1], pin[2], w1, s1, w2, s2, offset, RSF,
                                                         host_out if i % 2 == 0 else host_out2))
-            if i >= 1:
-                layer.host_wait(pipe["tickets"][i - 1])
             pipe["i"] = i + 1
 
         def e2e_drain():
-            if pipe["tickets"]:
-                layer.host_wait(pipe["tickets"][-1])
+            for t in pipe["tickets"][-2:]:
+                layer.host_wait(t)
     else:
         host_out2 = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
 
         def e2e_step():
             # every rank copies only its token slice over PCIe, NVLink all-gathers the rest; two calls in
-            # flight, the output of step i-1 is awaited right after step i has been issued
+            # flight: step i waits for the output of step i-2 (whose host buffer it reuses), then issues
             i = pipe["i"]
+            if i >= 2:
+                moe.host_wait(pipe["tickets"][i - 2])
             pipe["tickets"].append(moe.run_host_async(pin[0], dev[1], pin[1], pin[2], w1, s1, w2, s2, RSF,
                                                       host_out if i % 2 == 0 else host_out2, mode=args.collective))
-            if i >= 1:
-                moe.host_wait(pipe["tickets"][i - 1])
             pipe["i"] = i + 1
 
         def e2e_drain():
-            if pipe["tickets"]:
-                moe.host_wait(pipe["tickets"][-1])
+            for t in pipe["tickets"][-2:]:
+                moe.host_wait(t)
     e2e_sync_ms = None
     if args.skip_e2e:
         e2e_ms = float("nan")

@@ -141,7 +141,7 @@ def test_two_gpu_expert_parallel_sum(T):
 
 
 def _worker_varying_t(rank, world, port, q):
-    """One ShardedMoe sized for 96 tokens, fused calls with T = 96, 33, 96, 40, 96, 8 and no barrier or
+    """One ShardedMoe sized for 96 tokens, fused calls with T = 96, 33, 96, 40, 96, 12 and no barrier or
     host synchronisation between them; the ranks are skewed against each other by device-side sleeps, so
     that one rank's push of the next epoch overlaps the other's reduce of the current one."""
     import sys
@@ -161,7 +161,7 @@ def _worker_varying_t(rank, world, port, q):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         Tmax = 96
-        seq = [96, 33, 96, 40, 96, 8]
+        seq = [96, 33, 96, 40, 96, 12]   # all above 8 tokens: both forms then run the same five-kernel chain
         moe = ShardedMoe(Tmax)
         w = gen.make_shard(moe.local_expert_offset, moe.num_local_experts, device="cuda", out_device="cuda")
         cases, want = {}, {}
