@@ -31,6 +31,7 @@ EXPORTS = [
     "moe_fp8_b200_run_unfinalized", "moe_fp8_b200_finalize", "moe_fp8_b200_run_host_async",
     "moe_fp8_b200_host_wait", "moe_fp8_b200_set_expert_map", "moe_fp8_b200_inject_device_status",
     "moe_fp8_b200_exchange_regions", "moe_fp8_b200_copy_rows_h2d",
+    "moe_fp8_b200_invalidate_weights",
 ]
 NOALLOC_MAX_TOKENS = 4096
 
@@ -89,6 +90,8 @@ def load() -> C.CDLL:
         fn.argtypes = [H, C.POINTER(Args), C.c_void_p]
     lib.moe_fp8_b200_exchange_bytes.restype = C.c_size_t
     lib.moe_fp8_b200_exchange_bytes.argtypes = [C.c_int, C.c_int]
+    lib.moe_fp8_b200_invalidate_weights.restype = C.c_int
+    lib.moe_fp8_b200_invalidate_weights.argtypes = [H]
     lib.moe_fp8_b200_copy_rows_h2d.restype = C.c_int
     lib.moe_fp8_b200_copy_rows_h2d.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
                                                C.c_void_p]

@@ -226,7 +226,7 @@ __device__ __forceinline__ float round_bf16(float x) {
 template <int MODE, bool SPLITK>
 __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
     const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-    const __grid_constant__ CUtensorMap tmap_out, Workspace ws, const float* __restrict__ w_scale, int silu_exact)
+    const __grid_constant__ CUtensorMap tmap_out, Workspace ws, const float2* __restrict__ w_scale_packed, int silu_exact)
 {
     constexpr int kKBlocks = (MODE == 1) ? kHiddenBlocks : kInterBlocks;
     constexpr int kTilesN = (MODE == 1) ? (kInter / kBlock) : (kHidden / kTileN);  // 16 / 28
@@ -456,31 +456,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
             unit_range<kKBlocks>(u % plan.split, plan.split, kb0, kb1);
             const int grow = tc.row0 + row;
             const float* sfa = ((MODE == 1) ? ws.sfa1 : ws.sfa2) + grow;
-            const float* sw_lo;
-            const float* sw_hi;
-            if (MODE == 1) {
-                sw_lo = w_scale + ((size_t)tc.e * (kGemm1Out / kBlock) + tc.n) * kHiddenBlocks;
-                sw_hi = sw_lo + (size_t)(kInter / kBlock) * kHiddenBlocks;
-            } else {
-                sw_lo = w_scale + ((size_t)tc.e * kHiddenBlocks + 2 * tc.n + h) * kInterBlocks;
-                sw_hi = sw_lo;
-            }
+            // The tile's weight-block scales for all K blocks, from the pre-laid-out copy (one float2 per
+            // K block, see repack_weight_scales_kernel): lane l keeps the entries of K blocks l and l + 32,
+            // a K block's pair then comes from a shuffle instead of two dependent global loads.
+            const float2* sw_tile = w_scale_packed + ((size_t)tc.e * kTilesN + tc.n) * kKBlocks;
+            const float2 sw_a = (lane < kKBlocks) ? __ldg(sw_tile + lane) : make_float2(0.0f, 0.0f);
+            const float2 sw_b = (kKBlocks > 32 && lane + 32 < kKBlocks) ? __ldg(sw_tile + lane + 32) : make_float2(0.0f, 0.0f);
+            // GEMM1: .x scales the linear-branch block, .y the gated-branch block; GEMM2: .x / .y are the
+            // tile's first / second 128-column block, of which this thread's 128 columns are one
+            const float mine_a = (MODE == 1 || h == 0) ? sw_a.x : sw_a.y, other_a = sw_a.y;
+            const float mine_b = (MODE == 1 || h == 0) ? sw_b.x : sw_b.y, other_b = sw_b.y;
             float acc[128];
 #pragma unroll
             for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
             const bool warp_has_rows = q * 32 < tc.rows;
 
             float sa_n = ld_scale_early(sfa + (size_t)kb0 * ws.m_cap);
-            float lo_n = ld_scale_early(sw_lo + kb0);
-            float hi_n = (MODE == 1) ? ld_scale_early(sw_hi + kb0) : 0.0f;
             for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                const float s_lo = sa_n * lo_n;
-                const float s_hi = (MODE == 1) ? sa_n * hi_n : s_lo;   // GEMM2: one weight block per thread
-                if (kb + 1 < kb1) {
-                    sa_n = ld_scale_early(sfa + (size_t)(kb + 1) * ws.m_cap);
-                    lo_n = ld_scale_early(sw_lo + kb + 1);
-                    if (MODE == 1) hi_n = ld_scale_early(sw_hi + kb + 1);
-                }
+                const float lo_w = __shfl_sync(0xffffffffu, (kKBlocks > 32 && kb >= 32) ? mine_b : mine_a, kb & 31);
+                const float hi_w = (MODE == 1) ? __shfl_sync(0xffffffffu, (kb >= 32) ? other_b : other_a, kb & 31) : lo_w;
+                const float s_lo = sa_n * lo_w;
+                const float s_hi = sa_n * hi_w;
+                if (kb + 1 < kb1) sa_n = ld_scale_early(sfa + (size_t)(kb + 1) * ws.m_cap);
                 const uint32_t as = it & 1u;
                 const uint32_t aph = (it >> 1) & 1u;
                 ok = mbar_wait(smem_u32(&sh->acc_full[as]), aph, abort_flag);
@@ -677,6 +674,51 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
 }
 
 // ---------------------------------------------------------------------------------------
+// Weight-scale pre-layout, run once per pair of scale tensors (the handle remembers their
+// addresses): the promotion wants, per output tile and K block, the two 128x128-block scales the
+// tile's 256 accumulator columns use.  In the operator's layout those lie kInterBlocks rows apart
+// (GEMM1: [E, 32, 56], linear-branch block n and gated-branch block 16 + n) or in neighbouring
+// rows (GEMM2: [E, 56, 16], blocks 2n and 2n + 1); here they become one float2 per (expert, tile,
+// K block), the order the promotion walks.  This is the counterpart of the reference's cached
+// scale transposes (kernel/moe_fp8.cu:981-994, cached per scale pointer at :3007-3014, 3501-3508).
+// ---------------------------------------------------------------------------------------
+__global__ void repack_weight_scales_kernel(const float* __restrict__ s1, const float* __restrict__ s2,
+                                            float2* __restrict__ p1, float2* __restrict__ p2, int num_experts)
+{
+    constexpr int kN1 = kInter / kBlock;        // 16 GEMM1 tiles per expert
+    constexpr int kN2 = kHidden / kTileN;       // 28 GEMM2 tiles per expert
+    const int per1 = kN1 * kHiddenBlocks, per2 = kN2 * kInterBlocks;
+    const int total = num_experts * (per1 + per2);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int e = i / (per1 + per2);
+        const int r = i - e * (per1 + per2);
+        if (r < per1) {
+            const int n = r / kHiddenBlocks, kb = r - n * kHiddenBlocks;
+            const float* src = s1 + ((size_t)e * (kGemm1Out / kBlock) + n) * kHiddenBlocks + kb;
+            p1[(size_t)e * per1 + r] = make_float2(src[0], src[(size_t)kN1 * kHiddenBlocks]);
+        } else {
+            const int r2 = r - per1;
+            const int n = r2 / kInterBlocks, kb = r2 - n * kInterBlocks;
+            const float* src = s2 + ((size_t)e * kHiddenBlocks + 2 * n) * kInterBlocks + kb;
+            p2[(size_t)e * per2 + r2] = make_float2(src[0], src[kInterBlocks]);
+        }
+    }
+}
+
+size_t packed_scale_floats(int mode, int num_experts)
+{
+    return 2 * (size_t)num_experts * (mode == 1 ? (kInter / kBlock) * kHiddenBlocks : (kHidden / kTileN) * kInterBlocks);
+}
+
+cudaError_t launch_repack_weight_scales(const float* s1, const float* s2, float* p1, float* p2, int num_experts,
+                                        cudaStream_t stream)
+{
+    repack_weight_scales_kernel<<<64, 256, 0, stream>>>(s1, s2, reinterpret_cast<float2*>(p1), reinterpret_cast<float2*>(p2),
+                                                        num_experts);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------
 // Host side: tensor maps and launch.
 // ---------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -777,8 +819,9 @@ cudaError_t configure_gemm_kernels()
 int gemm_tiles_n(int mode) { return mode == 1 ? kInter / kBlock : kHidden / kTileN; }
 
 cudaError_t launch_grouped_gemm(int mode, const void* tmap_a, const void* tmap_b, const void* tmap_out, const Workspace& ws,
-                                const float* w_scale, int silu_exact, int num_ctas, int split_k, cudaStream_t stream)
+                                const float* w_scale_packed, int silu_exact, int num_ctas, int split_k, cudaStream_t stream)
 {
+    const float2* w_scale = reinterpret_cast<const float2*>(w_scale_packed);
     const CUtensorMap* ma = static_cast<const CUtensorMap*>(tmap_a);
     const CUtensorMap* mb = static_cast<const CUtensorMap*>(tmap_b);
     const CUtensorMap* mo = static_cast<const CUtensorMap*>(tmap_out);

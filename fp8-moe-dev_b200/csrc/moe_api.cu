@@ -29,6 +29,8 @@ cudaError_t configure_gemm_kernels();
 cudaError_t launch_grouped_gemm(int, const void*, const void*, const void*, const Workspace&, const float*, int, int, int,
                                 cudaStream_t);
 int gemm_tiles_n(int mode);
+size_t packed_scale_floats(int mode, int num_experts);
+cudaError_t launch_repack_weight_scales(const float*, const float*, float*, float*, int, cudaStream_t);
 }  // namespace moe
 
 using namespace moe;
@@ -61,7 +63,7 @@ struct Carve {
 
 struct Layout {
     size_t ctrl, expert_offset, tile_info, num_tiles, expert_map, topk_idx, topk_weight, pair_count, pair_code,
-        pair_weight, row_token, a1, sfa1, a2, sfa2, y, splitk, total;
+        pair_weight, row_token, a1, sfa1, a2, sfa2, y, splitk, sw1_packed, sw2_packed, total;
     int m_cap, max_tiles;
 };
 
@@ -88,6 +90,8 @@ Layout make_layout(int T, int E)
     L.sfa2 = c.take(sizeof(float) * (size_t)kInterBlocks * L.m_cap);
     L.y = c.take(sizeof(__nv_bfloat16) * (size_t)L.m_cap * kHidden);
     L.splitk = c.take(sizeof(float) * (size_t)kSplitKSlots * 4 * 256);  // kSplitKMaxRows rows of 256 floats per unit
+    L.sw1_packed = c.take(sizeof(float) * packed_scale_floats(1, E));
+    L.sw2_packed = c.take(sizeof(float) * packed_scale_floats(2, E));
     L.total = c.off;
     return L;
 }
@@ -120,6 +124,11 @@ struct moe_fp8_b200_ctx {
     alignas(64) unsigned char tmap_dec_w2[128];
     const void* cached_w1 = nullptr;
     const void* cached_w2 = nullptr;
+    // weight scales in the promotion's order (made once per pair of scale tensors, remembered by address)
+    float* sw1_packed = nullptr;
+    float* sw2_packed = nullptr;
+    const float* cached_s1 = nullptr;
+    const float* cached_s2 = nullptr;
     // optional per-stage timing: events around each stage of the last kTimedRuns runs
     int opt_stage_timing = 0;
     static constexpr int kTimedRuns = 64;
@@ -263,6 +272,11 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
             return MOE_FP8_B200_OK;
         }
     }
+    if (e == cudaSuccess && (a.gemm1_weights_scale != h->cached_s1 || a.gemm2_weights_scale != h->cached_s2)) {
+        // new scale tensors: lay them out for the GEMMs' promotion (stream-ordered in front of the chain)
+        e = launch_repack_weight_scales(a.gemm1_weights_scale, a.gemm2_weights_scale, h->sw1_packed, h->sw2_packed, E, stream);
+        if (e == cudaSuccess) { h->cached_s1 = a.gemm1_weights_scale; h->cached_s2 = a.gemm2_weights_scale; }
+    }
     mark(0);
     if (e == cudaSuccess)
         e = launch_route_dispatch(a.routing_logits, a.routing_bias, h->ws, T, (int)a.local_expert_offset, E,
@@ -278,11 +292,11 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
     if (e == cudaSuccess && stop >= 2) e = launch_permute(a.hidden_states, a.hidden_states_scale, h->ws, T, stream);
     mark(3);
     if (e == cudaSuccess && stop >= 3)
-        e = launch_grouped_gemm(1, h->tmap_a1, h->tmap_w1, h->tmap_y, h->ws, a.gemm1_weights_scale, h->opt_exact_silu,
+        e = launch_grouped_gemm(1, h->tmap_a1, h->tmap_w1, h->tmap_y, h->ws, h->sw1_packed, h->opt_exact_silu,
                                 ctas(1), split_k, stream);
     mark(4);
     if (e == cudaSuccess && stop >= 4)
-        e = launch_grouped_gemm(2, h->tmap_a2, h->tmap_w2, h->tmap_y, h->ws, a.gemm2_weights_scale, 0, ctas(2), split_k, stream);
+        e = launch_grouped_gemm(2, h->tmap_a2, h->tmap_w2, h->tmap_y, h->ws, h->sw2_packed, 0, ctas(2), split_k, stream);
     mark(5);
     if (e == cudaSuccess && stop >= 5 && finalize) {
         if (ex) {
@@ -413,6 +427,8 @@ int moe_fp8_b200_create(moe_fp8_b200_handle* out, int device, int max_tokens, in
     w.y = reinterpret_cast<__nv_bfloat16*>(h->base + L.y);
     w.splitk_partial = reinterpret_cast<float*>(h->base + L.splitk);
     w.expert_map = reinterpret_cast<int*>(h->base + L.expert_map);
+    h->sw1_packed = reinterpret_cast<float*>(h->base + L.sw1_packed);
+    h->sw2_packed = reinterpret_cast<float*>(h->base + L.sw2_packed);
     w.m_cap = L.m_cap;
     w.max_tiles = L.max_tiles;
     // Small control arrays start defined; the large row buffers are written before use.
@@ -608,6 +624,14 @@ int moe_fp8_b200_finalize(moe_fp8_b200_handle h, int num_tokens, void* output, v
         return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "output is NULL or not 16-byte aligned");
     const cudaError_t e = launch_combine(h->ws, output, num_tokens, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "combine launch failed: %s", cudaGetErrorString(e));
+    return MOE_FP8_B200_OK;
+}
+
+int moe_fp8_b200_invalidate_weights(moe_fp8_b200_handle h)
+{
+    if (!h) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
+    h->cached_w1 = h->cached_w2 = nullptr;
+    h->cached_s1 = h->cached_s2 = nullptr;
     return MOE_FP8_B200_OK;
 }
 

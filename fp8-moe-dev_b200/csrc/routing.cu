@@ -80,7 +80,12 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_dispatch_kernel(
     pdl_launch_dependents();
     pdl_wait();  // the previous call's kernels still read the pair tables and offsets
     __syncthreads();
-    int n_pairs = 0;
+    // Dispatch is spread over the warp: lane s applies the policy to the token's experts that fall into
+    // 32-expert shard s (the reference does one shard per call; a handle with 64..256 experts, or one with
+    // a strided / table placement, has up to eight).  A lane's kept pairs follow those of the lanes before
+    // it, so the token's pair list is in shard order, then in the policy's emission order, exactly as a
+    // serial walk over the shards would leave it.
+    int n_pairs = 0, pair_base = 0, total_pairs = 0;
     int p_le[kTopK], p_rank[kTopK];
     float p_w[kTopK];
 #pragma unroll
@@ -102,29 +107,26 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_dispatch_kernel(
         ws.topk_weight[(size_t)t * kTopK + lane] = my_w;
     }
 
-    if (lane == 0) {
-        if (pol.expert_stride == 0 || pol.expert_stride == 1) {
-            const int shards = num_local_experts / kShardExperts;
-            for (int sh = 0; sh < shards; ++sh) {
-                dispatch_one_shard(idx, wn, sh, local_expert_offset, pol, rsf, n_pairs, p_le, p_w);
-            }
+    const bool contiguous = pol.expert_stride == 0 || pol.expert_stride == 1;
+    const int n_shards = contiguous ? num_local_experts / kShardExperts : kNumExperts / kShardExperts;
+    if (lane < n_shards) {
+        if (contiguous) {
+            dispatch_one_shard(idx, wn, lane, local_expert_offset, pol, rsf, n_pairs, p_le, p_w);
         } else {
-            // strided or table placement: the policy runs on every global shard, this rank keeps its experts
-            for (int sh = 0; sh < kNumExperts / kShardExperts; ++sh) {
-                int n_sh = 0;
-                int g_le[kTopK];
-                float g_w[kTopK];
+            // strided or table placement: the policy runs on a global shard, this rank keeps its experts
+            int n_sh = 0;
+            int g_le[kTopK];
+            float g_w[kTopK];
 #pragma unroll
-                for (int i = 0; i < kTopK; ++i) { g_le[i] = 0; g_w[i] = 0.0f; }
-                dispatch_one_shard(idx, wn, sh, 0, pol, rsf, n_sh, g_le, g_w);
+            for (int i = 0; i < kTopK; ++i) { g_le[i] = 0; g_w[i] = 0.0f; }
+            dispatch_one_shard(idx, wn, lane, 0, pol, rsf, n_sh, g_le, g_w);
 #pragma unroll
-                for (int i = 0; i < kTopK; ++i) {
-                    if (i < n_sh) {
-                        const int local = pol.expert_stride > 1
-                                              ? (g_le[i] % pol.expert_stride == pol.expert_phase ? g_le[i] / pol.expert_stride : -1)
-                                              : __ldg(ws.expert_map + g_le[i]);
-                        if (local >= 0) emit_pair(p_le, p_w, n_pairs, local, g_w[i]);
-                    }
+            for (int i = 0; i < kTopK; ++i) {
+                if (i < n_sh) {
+                    const int local = pol.expert_stride > 1
+                                          ? (g_le[i] % pol.expert_stride == pol.expert_phase ? g_le[i] / pol.expert_stride : -1)
+                                          : __ldg(ws.expert_map + g_le[i]);
+                    if (local >= 0) emit_pair(p_le, p_w, n_pairs, local, g_w[i]);
                 }
             }
         }
@@ -133,6 +135,15 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_dispatch_kernel(
             if (i < n_pairs) p_rank[i] = atomicAdd(&s_cnt[p_le[i]], 1);
         }
     }
+    // exclusive prefix of the lanes' pair counts (lanes at or above n_shards hold 0)
+    int incl = n_pairs;
+#pragma unroll
+    for (int off = 1; off < 8; off <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += y;
+    }
+    pair_base = incl - n_pairs;
+    total_pairs = __shfl_sync(0xffffffffu, incl, 7);
     }  // t < T
 
     __syncthreads();
@@ -146,16 +157,16 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_dispatch_kernel(
         s_base[e] = base;
     }
     __syncthreads();
-    if (t < T && lane == 0) {
+    if (t < T) {
 #pragma unroll
         for (int i = 0; i < kTopK; ++i) {
             if (i < n_pairs) {
                 const uint32_t slot = (uint32_t)(s_base[p_le[i]] + p_rank[i]);
-                ws.pair_code[(size_t)t * kTopK + i] = ((uint32_t)p_le[i] << 24) | slot;
-                ws.pair_weight[(size_t)t * kTopK + i] = p_w[i];
+                ws.pair_code[(size_t)t * kTopK + pair_base + i] = ((uint32_t)p_le[i] << 24) | slot;
+                ws.pair_weight[(size_t)t * kTopK + pair_base + i] = p_w[i];
             }
         }
-        ws.pair_count[t] = n_pairs;
+        if (lane == 0) ws.pair_count[t] = total_pairs;
     }
 
     if (!do_scan) return;

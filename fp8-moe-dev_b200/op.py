@@ -122,6 +122,12 @@ class MoeLayer:
         if rc != _lib.OK:
             self._raise(rc)
 
+    def invalidate_weights(self):
+        """Call after the weight-scale tensors' contents changed under the same addresses."""
+        rc = self._lib.moe_fp8_b200_invalidate_weights(self._h)
+        if rc != _lib.OK:
+            self._raise(rc)
+
     def set_expert_stride(self, stride: int):
         """Strided expert placement (multi-GPU wrapper): this handle's experts are the global ids g
         with g % stride == local_expert_offset, stacked in increasing g; stride 1 = contiguous."""

@@ -225,6 +225,16 @@ MOE_FP8_B200_API int moe_fp8_b200_exchange_regions(int capacity_tokens, int worl
 MOE_FP8_B200_API int moe_fp8_b200_run_reduce_scatter(moe_fp8_b200_handle h, const moe_fp8_b200_args* args,
                                                      const moe_fp8_b200_exchange* exchange, void* stream);
 
+/* What the handle derives from the weight tensors is made once and remembered BY ADDRESS: the TMA
+ * descriptors of gemm1_weights / gemm2_weights and a copy of the two weight-scale tensors in the order
+ * the GEMMs' accumulator promotion walks them (one pair of block scales per output tile and K block).
+ * A run whose weight or scale pointers differ from the remembered ones redoes that step in front of
+ * its kernels, stream-ordered.  If the CONTENTS of the scale tensors change under the same addresses
+ * (weights reloaded in place), call this before the next run.  The reference keeps the same kind of
+ * pointer-keyed cache for its transposed weight scales (kernel/moe_fp8.cu:3007-3014, 3501-3508) and has
+ * no way to invalidate it; its activations-side caches have no counterpart here. */
+MOE_FP8_B200_API int moe_fp8_b200_invalidate_weights(moe_fp8_b200_handle h);
+
 /* Table form of the expert placement (see MOE_FP8_B200_OPT_EXPERT_STRIDE): local_slot[g] is the
  * index inside this handle's weight tensors of global expert g, or -1 if another handle holds it;
  * every slot 0 .. num_local_experts-1 must appear exactly once.  Lets the multi-GPU wrapper place

@@ -45,7 +45,10 @@ def gpu_shard(offset: int, E: int, base_seed: int = 1000):
     if key not in _shards:
         entry.load_package()
         from fp8_moe_dev_b200 import gen
-        if len(_shards) >= 2:
+        # shards are kept for the whole session (a 32-expert shard is 1.4 GB, all 256 experts 11.3 GB): a
+        # freed shard's addresses could be handed to the next one, which handles that remember weights by
+        # address would take for the old tensors
+        if len(_shards) >= 12:
             _shards.pop(next(iter(_shards)))
             torch.cuda.empty_cache()
         _shards[key] = gen.make_shard(offset, E, base_seed, device="cuda", out_device="cuda")
@@ -66,6 +69,9 @@ def run_layer(layer, inputs, weights, offset, rsf=RSF, out=None):
     T = logits.shape[0]
     if out is None:
         out = torch.full((T, H), float("nan"), dtype=torch.bfloat16, device="cuda")
+    # The handle remembers what it derived from the weight tensors BY ADDRESS.  Test fixtures free shards
+    # and generate others, which the allocator may place at the same addresses: tell the handle.
+    layer.invalidate_weights()
     layer.run(logits, bias, hidden, hscale, w1, s1, w2, s2, offset, rsf, out)
     layer.check()
     return out
@@ -87,10 +93,19 @@ def reference_module():
     return _ref_mod
 
 
+_ref_scales_alive = []
+
+
 def reference_run(inputs, weights, offset, rsf=RSF):
-    """The unmodified reference operator on fresh device buffers (its caches key on pointers)."""
+    """The unmodified reference operator on fresh device buffers.  Its caches key on pointers: the routing
+    result on the input pointers (kernel/moe_fp8.cu:2696-2702) and a transposed copy of the weight scales
+    on the scale pointers (:3007-3014, 3501-3508), with no way to invalidate either.  The inputs are
+    therefore cloned per call, and the scales are cloned into tensors that stay allocated for the whole
+    session, so that no later call can present other scales at an address the reference has seen."""
     logits, bias, hidden, hscale = [x.cuda().clone() for x in inputs]
     w1, s1, w2, s2 = weights
+    s1, s2 = s1.clone(), s2.clone()
+    _ref_scales_alive.append((s1, s2))
     T = logits.shape[0]
     out = torch.zeros(T, H, dtype=torch.bfloat16, device="cuda")
     reference_module().run(logits, bias, hidden, hscale, w1, s1, w2, s2, int(offset), float(rsf), out)

@@ -722,3 +722,29 @@ def test_exchange_wait_runs_out_and_is_reported(pkg):
         assert torch.equal(hp.run_layer(lay, inputs, weights, 0), want)
     finally:
         lay.close()
+
+
+def test_weight_scale_prelayout_follows_pointers_and_invalidation(pkg, layer32):
+    """The handle keeps a copy of the weight scales in the GEMMs' order, keyed by the scale tensors'
+    addresses: other tensors are picked up by themselves, new contents under the same addresses after
+    invalidate_weights()."""
+    T = 40
+    dev = [x.cuda() for x in hp.cpu_inputs(T, seed=6000)]
+    w1, s1, w2, s2 = hp.gpu_shard(0, 32)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+
+    def run(sa, sb):
+        layer32.run(*dev, w1, sa, w2, sb, 0, RSF, out)
+        layer32.check()
+        return out.clone()
+
+    layer32.invalidate_weights()
+    base = run(s1, s2)
+    s1b, s2b = (s1 * 2.0).contiguous(), s2.clone()
+    doubled = run(s1b, s2b)                       # other addresses: seen at once
+    assert not torch.equal(doubled, base)
+    s1b.copy_(s1)                                 # same addresses, old contents back
+    assert torch.equal(run(s1b, s2b), doubled), "the pre-laid-out copy is keyed by address"
+    layer32.invalidate_weights()
+    assert torch.equal(run(s1b, s2b), base)
+    layer32.invalidate_weights()
