@@ -428,7 +428,7 @@ def run_ours(args, rank, world, local):
         cands = {}
         # calibration of the load-aware placement: routed rows per expert of ANOTHER batch (same
         # distribution and routing bias, different seed), never of the batch that is timed
-        cal_logits, _ = gen.make_routing(4096, seed=12345, skew=WORKLOADS[args.workload][1])
+        cal_logits, _ = gen.make_routing(4096, seed=12345, skew=WORKLOADS[args.workload][1], skew_seed=0)
         loads = pkg.expert_loads(cal_logits.cuda(), dev[1], RSF)
         for place in (("contiguous", "balanced") if args.placement == "auto" else (args.placement,)):
             m = ShardedMoe(T, rank, world, local, placement=place, loads=loads)
@@ -483,6 +483,26 @@ def run_ours(args, rank, world, local):
     layer.check()
     if moe is not None and moe.placement == "contiguous":
         contiguous_ms = ms
+    # the fused exchange's own clock (last timed step): how long this rank pushed, waited for its peers, reduced
+    exchange = None
+    if moe is not None and args.collective == "fused":
+        import numpy as np
+        tl = layer.read("exchange_timeline", 8).astype(np.int64)
+        pc = layer.read("pair_count", T)
+        lo_t, hi_t = min(rank * per, T), min(rank * per + per, T)
+        remote_rows = int((pc > 0).sum() - (pc[lo_t:hi_t] > 0).sum())
+        push_us, wait_us, reduce_us = (tl[1] - tl[0]) / 1e3, (tl[3] - tl[2]) / 1e3, (tl[4] - tl[3]) / 1e3
+        gbs = remote_rows * H * 2 / max(push_us, 1e-3) / 1e3
+        exchange = {"push_us_max": round(max_over_ranks(push_us, world), 1),
+                    "wait_for_peers_us_max": round(max_over_ranks(wait_us, world), 1),
+                    "wait_for_peers_us_min": round(-max_over_ranks(-wait_us, world), 1),
+                    "reduce_us_max": round(max_over_ranks(reduce_us, world), 1),
+                    "remote_rows_pushed_max": int(max_over_ranks(remote_rows, world)),
+                    "nvlink_gbs_while_pushing_min": round(-max_over_ranks(-gbs, world), 1),
+                    "note": "per rank from %globaltimer stamps inside combine_push_kernel / reduce_owned_kernel; the "
+                            "wait is the time the owner step spent before every peer's rows had arrived (load imbalance "
+                            "between the ranks shows up here, on the fast ranks)"}
+
 
     # end to end: per-step inputs start in pinned host memory, the result ends in host memory
     pin = [x.pin_memory() for x in (inputs[0], inputs[2], inputs[3])]
@@ -591,7 +611,7 @@ def run_ours(args, rank, world, local):
                     "calibration batch drawn with another seed; auto keeps the faster of the two in a short trial",
                 "placement_trial_ms": placement_ms, "contiguous_ms_per_step": contiguous_ms,
                 "contiguous_tokens_per_s": round(T / contiguous_ms * 1e3, 1) if contiguous_ms else None,
-                "other_collective_ms_per_step": other_ms},
+                "other_collective_ms_per_step": other_ms, "exchange": exchange},
         "parity": parity,
         "clocks": clk.summary(),
         "e2e": None if args.skip_e2e else {"value": round(T / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),

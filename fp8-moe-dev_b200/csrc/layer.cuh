@@ -67,6 +67,11 @@ struct Control {
     unsigned dec_phase;                  // (cleared by CTA 0 of each launch, see decode.cu)
     int pad2;
     unsigned long long dec_time[16];     // phase timestamps (ns) of CTA 0 in the last decode-kernel run
+    // Timestamps (ns, %globaltimer) of the last fused combine + reduce-scatter on this rank:
+    // [0] first CTA of the push starts, [1] last CTA of the push done (flags published), [2] first CTA of the
+    // owner step starts waiting, [3] last CTA has seen all peers' flags, [4] last CTA of the owner step done.
+    // [0] and [2] are minima (reset to all-ones by the routing kernel's scan), the others maxima (reset to 0).
+    unsigned long long xch_time[8];
 };
 
 enum KernelStatus : int {

@@ -49,6 +49,7 @@ __device__ __forceinline__ void scan_tiles_block(const Workspace& ws, int num_lo
         ws.ctrl->expert_rows[e] = m;
         if (!local_counts) ws.ctrl->expert_count[e] = 0;
     }
+    if (e < 8) ws.ctrl->xch_time[e] = (e == 0 || e == 2) ? ~0ull : 0ull;
     if (e == 0) {
         ws.expert_offset[num_local_experts] = total * kTileM;
         ws.num_tiles[0] = total;
@@ -359,6 +360,7 @@ __global__ void __launch_bounds__(kCombineThreads, 2) combine_push_kernel(Worksp
     pdl_wait();
     const int parity = (int)(ex.epoch & 1u);
     const bool any_tiles = ws.num_tiles[0] != 0;
+    if (threadIdx.x == 0) atomicMin(&ws.ctrl->xch_time[0], global_timer_ns());
     // Persistent CTAs walk the tokens starting with the next rank's slice and ending with their
     // own, so the remote stores go out first and every rank starts on a different destination.
     // One system-scope fence per CTA, after its last store, instead of one per token.
@@ -425,6 +427,7 @@ __global__ void __launch_bounds__(kCombineThreads, 2) combine_push_kernel(Worksp
                 uint32_t* flag = reinterpret_cast<uint32_t*>(peer_ptr(ex, o)) + ex.rank;
                 st_release_sys_u32(flag, ex.epoch);
             }
+            ws.ctrl->xch_time[1] = global_timer_ns();
         }
     }
 }
@@ -444,6 +447,7 @@ __global__ void __launch_bounds__(kCombineThreads) reduce_owned_kernel(Workspace
         const uint32_t* flags = reinterpret_cast<const uint32_t*>(mine_base);
         int ok = 1;
         const uint64_t t0 = global_timer_ns();
+        atomicMin(&ws.ctrl->xch_time[2], (unsigned long long)t0);
         const uint64_t limit_ns = (uint64_t)ex.wait_limit_us * 1000ull;
         for (int src = 0; src < ex.world; ++src) {
             uint32_t it = 0;
@@ -454,6 +458,7 @@ __global__ void __launch_bounds__(kCombineThreads) reduce_owned_kernel(Workspace
             if (!ok) break;
         }
         if (!ok) atomicCAS(&ws.ctrl->status, kStatusOk, kStatusExchangeTimeout);
+        atomicMax(&ws.ctrl->xch_time[3], (unsigned long long)global_timer_ns());
         s_ok = ok;
     }
     __syncthreads();
@@ -492,6 +497,7 @@ __global__ void __launch_bounds__(kCombineThreads) reduce_owned_kernel(Workspace
         for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(acc[c][2 * j], acc[c][2 * j + 1]);
         dst[threadIdx.x + c * kCombineThreads] = packed;
     }
+    if (threadIdx.x == 0) atomicMax(&ws.ctrl->xch_time[4], (unsigned long long)global_timer_ns());
 }
 
 cudaError_t launch_combine_push(const Workspace& ws, const ExchangeView& ex, int T, cudaStream_t stream)

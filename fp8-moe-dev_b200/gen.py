@@ -65,12 +65,15 @@ def quantize_blocks_128x128(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor
     return q, scale.contiguous()
 
 
-def make_routing(T: int, seed: int = 0, skew: bool = False, device="cpu"):
+def make_routing(T: int, seed: int = 0, skew: bool = False, device="cpu", skew_seed=None):
+    """`skew_seed` fixes WHICH experts are the popular ones (a property of the router, not of a batch);
+    it defaults to `seed`.  A second batch for the same router: other `seed`, same `skew_seed`, and the
+    first batch's bias."""
     g = _gen(device, seed)
     logits = g.randn(T, NE)
     bias = (0.1 * g.randn(NE)).to(torch.bfloat16)
     if skew:
-        perm = np.random.Generator(np.random.PCG64(int(seed) + 7919)).permutation(NE)
+        perm = np.random.Generator(np.random.PCG64(int(seed if skew_seed is None else skew_seed) + 7919)).permutation(NE)
         rank = torch.from_numpy((perm + 1).astype(np.float32)).to(device)
         logits = logits + 1.5 * torch.log(1.0 / rank)[None, :]
     return logits.contiguous(), bias.contiguous()

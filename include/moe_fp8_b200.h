@@ -118,9 +118,12 @@ enum {
     MOE_FP8_B200_BUF_SFA2 = 12,         /* fp32 [16, M_cap] */
     MOE_FP8_B200_BUF_Y = 13,            /* bf16 [M_cap, 7168] */
     MOE_FP8_B200_BUF_STATUS = 14,       /* int32 [2] device status word + detail */
-    MOE_FP8_B200_BUF_DECODE_TIMELINE = 15 /* uint64 [16] ns clock of CTA 0 in the last decode-kernel run: [0..6] start, tables
+    MOE_FP8_B200_BUF_DECODE_TIMELINE = 15, /* uint64 [16] ns clock of CTA 0 in the last decode-kernel run: [0..6] start, tables
                                            * built, phase 1 done, barrier 1 passed, phase 2 done, barrier 2 passed, end;
                                            * [8..11] inside the table build: token routed, pairs listed, tables merged, published */
+    MOE_FP8_B200_BUF_EXCHANGE_TIMELINE = 16 /* uint64 [8] ns clock of the last moe_fp8_b200_run_reduce_scatter on this rank:
+                                            * [0] push starts, [1] push done and flags published, [2] owner step starts
+                                            * waiting for its peers, [3] all peers' flags seen, [4] owner step done */
 };
 
 /* Library version, (major << 16) | minor.  No counterpart in the reference. */

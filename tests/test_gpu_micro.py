@@ -1,0 +1,31 @@
+"""Micro-benchmark of the grouped GEMM's MMA <-> promotion pipeline (tests/micro/gemm_pipeline_probe.cu),
+compiled with nvcc and run on one SM: it is where the per-K-block cycle figures of the design notes come
+from, and it guards the handshake of ptx.cuh (bounded waits, TMEM allocation and release) in isolation."""
+import re
+import shutil
+import subprocess
+from pathlib import Path
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_gemm_pipeline_probe(tmp_path):
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(nvcc).exists():
+        pytest.skip("nvcc not available on this machine")
+    exe = tmp_path / "probe"
+    src = ROOT / "tests" / "micro" / "gemm_pipeline_probe.cu"
+    subprocess.run([nvcc, "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-I",
+                    str(ROOT / "fp8-moe-dev_b200" / "csrc"), "-o", str(exe), str(src)], check=True, capture_output=True)
+    r = subprocess.run([str(exe), "1", "4000"], capture_output=True, text=True, timeout=120)
+    print(r.stdout)
+    assert r.returncode == 0, r.stdout + r.stderr
+    cyc = {m.group(1): float(m.group(2)) for m in re.finditer(r"^(\w+)\s+([\d.]+) cycles", r.stdout, re.M)}
+    # a K block is 4 MMAs of 128 cycles: the tensor pipe's floor
+    assert 500 <= cyc["mma_only"] <= 560, cyc
+    assert cyc["drain"] < 700 and cyc["promote_packed"] <= cyc["promote_scalar"] + 1, cyc
+    # 128-column instructions are shared-memory bound (A is re-read per half): no faster per column
+    assert cyc["mma_only_n128"] >= cyc["mma_only"], cyc
