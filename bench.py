@@ -56,10 +56,10 @@ WORKLOADS = {
 }
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch of the dominant kernel
-# (GEMM1) from the ncu capture summarised in profiles/gemm_t12288_e32_ncu_full.md: 926 MB for
+# (GEMM1) from the ncu capture summarised in profiles/gemm_t12288_e32_ncu_full.md: 928 MB for
 # T = 12288 on one 32-expert shard.  Weights are 97 % of that traffic and are read exactly once,
 # so for the other workloads the figure is scaled by (experts on the GPU) / 32.
-NCU_GEMM1_DRAM_BYTES_32_EXPERTS_T12288 = 912.0e6
+NCU_GEMM1_DRAM_BYTES_32_EXPERTS_T12288 = 928.0e6
 
 
 def peaks():
@@ -636,7 +636,7 @@ def run_ours(args, rank, world, local):
                      "flops_per_launch": g1_flops, "avg_launch_ms": round(g1_ms, 4), "timed_launches": timed_runs,
                      "traffic": (NCU_GEMM1_DRAM_BYTES_32_EXPERTS_T12288 * E / 32) if T >= 8192 else None,
                      "traffic_note": "SCALED, not measured at this size: ncu dram bytes of GEMM1 at T=12288 on one "
-                                     "32-expert shard (912 MB, weights 97 % of it and read once) x experts/32"},
+                                     "32-expert shard (928 MB, weights 96 % of it and read once) x experts/32"},
     }
     if rank == 0 and world == 1:
         if not args.skip_small:
