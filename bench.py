@@ -529,16 +529,17 @@ def run_ours(args, rank, world, local):
             for t in pipe["tickets"][-2:]:
                 layer.host_wait(t)
     else:
-        host_out2 = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+        host_outs = [host_out] + [torch.empty(T, H, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
 
         def e2e_step():
-            # every rank copies only its token slice over PCIe, NVLink all-gathers the rest; two calls in
-            # flight: step i waits for the output of step i-2 (whose host buffer it reuses), then issues
+            # every rank copies only its token slice over PCIe, the slices are replicated over NVLink; three
+            # calls outstanding over three host output buffers: step i is issued, then the output of step
+            # i-2 is awaited (read) -- one call copies in, one computes, one copies out
             i = pipe["i"]
+            pipe["tickets"].append(moe.run_host_async(pin[0], dev[1], pin[1], pin[2], w1, s1, w2, s2, RSF,
+                                                      host_outs[i % 3], mode=args.collective))
             if i >= 2:
                 moe.host_wait(pipe["tickets"][i - 2])
-            pipe["tickets"].append(moe.run_host_async(pin[0], dev[1], pin[1], pin[2], w1, s1, w2, s2, RSF,
-                                                      host_out if i % 2 == 0 else host_out2, mode=args.collective))
             pipe["i"] = i + 1
 
         def e2e_drain():

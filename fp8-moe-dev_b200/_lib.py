@@ -31,7 +31,8 @@ EXPORTS = [
     "moe_fp8_b200_run_unfinalized", "moe_fp8_b200_finalize", "moe_fp8_b200_run_host_async",
     "moe_fp8_b200_host_wait", "moe_fp8_b200_set_expert_map", "moe_fp8_b200_inject_device_status",
     "moe_fp8_b200_exchange_regions", "moe_fp8_b200_copy_rows_h2d",
-    "moe_fp8_b200_invalidate_weights",
+    "moe_fp8_b200_invalidate_weights", "moe_fp8_b200_copy_device", "moe_fp8_b200_signal_peers",
+    "moe_fp8_b200_wait_peers",
 ]
 NOALLOC_MAX_TOKENS = 4096
 
@@ -90,6 +91,13 @@ def load() -> C.CDLL:
         fn.argtypes = [H, C.POINTER(Args), C.c_void_p]
     lib.moe_fp8_b200_exchange_bytes.restype = C.c_size_t
     lib.moe_fp8_b200_exchange_bytes.argtypes = [C.c_int, C.c_int]
+    lib.moe_fp8_b200_copy_device.restype = C.c_int
+    lib.moe_fp8_b200_copy_device.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
+                                             C.c_void_p]
+    for name in ("moe_fp8_b200_signal_peers", "moe_fp8_b200_wait_peers"):
+        fn = getattr(lib, name)
+        fn.restype = C.c_int
+        fn.argtypes = [H, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_size_t, C.c_uint32, C.c_void_p]
     lib.moe_fp8_b200_invalidate_weights.restype = C.c_int
     lib.moe_fp8_b200_invalidate_weights.argtypes = [H]
     lib.moe_fp8_b200_copy_rows_h2d.restype = C.c_int

@@ -21,6 +21,8 @@ cudaError_t launch_combine(const Workspace&, void*, int, cudaStream_t);
 cudaError_t launch_quantize_rows(const void*, void*, float*, int, cudaStream_t);
 cudaError_t launch_combine_push(const Workspace&, const ExchangeView&, int, cudaStream_t);
 cudaError_t launch_reduce_owned(const Workspace&, const ExchangeView&, int, void*, cudaStream_t);
+cudaError_t launch_signal_peers(const ExchangeView&, size_t, uint32_t, cudaStream_t);
+cudaError_t launch_wait_peers(const ExchangeView&, size_t, uint32_t, Control*, cudaStream_t);
 int encode_kmajor_u8_map(void*, const void*, uint64_t, uint64_t, uint64_t, uint32_t);
 int encode_rows_1k_map(void*, const void*, uint64_t, uint64_t, uint32_t);
 int encode_out_bf16_map(void*, void*, uint64_t, uint64_t);
@@ -794,6 +796,57 @@ int moe_fp8_b200_copy_rows_h2d(void* dst_device, size_t dst_pitch, const void* s
     const cudaError_t e = cudaMemcpy2DAsync(dst_device, dst_pitch, src_host, src_pitch, row_bytes, rows,
                                             cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? MOE_FP8_B200_OK : MOE_FP8_B200_ERR_CUDA;
+}
+
+int moe_fp8_b200_copy_device(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t row_bytes,
+                             size_t rows, void* stream)
+{
+    if (!dst || !src || row_bytes > dst_pitch || row_bytes > src_pitch) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
+    if (rows == 0 || row_bytes == 0) return MOE_FP8_B200_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const cudaError_t e = (rows == 1 || (dst_pitch == row_bytes && src_pitch == row_bytes))
+                              ? cudaMemcpyAsync(dst, src, row_bytes * rows, cudaMemcpyDeviceToDevice, s)
+                              : cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, row_bytes, rows, cudaMemcpyDeviceToDevice, s);
+    return e == cudaSuccess ? MOE_FP8_B200_OK : MOE_FP8_B200_ERR_CUDA;
+}
+
+namespace {
+int peer_view(moe_fp8_b200_handle h, void* const* peer_bases, int world, int rank, ExchangeView& v)
+{
+    if (!h) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
+    if (!peer_bases || (world != 1 && world != 2 && world != 4 && world != 8) || rank < 0 || rank >= world)
+        return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "peer hand-shake: world %d / rank %d invalid", world, rank);
+    std::memset(&v, 0, sizeof v);
+    for (int i = 0; i < world; ++i) {
+        if (!peer_bases[i] || ((uintptr_t)peer_bases[i] & 3u))
+            return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "peer hand-shake: buffer %d is NULL or misaligned", i);
+        v.peer[i] = static_cast<uint8_t*>(peer_bases[i]);
+    }
+    v.world = world;
+    v.rank = rank;
+    v.wait_limit_us = (uint32_t)h->opt_wait_limit_us;
+    return MOE_FP8_B200_OK;
+}
+}  // namespace
+
+int moe_fp8_b200_signal_peers(moe_fp8_b200_handle h, void* const* peer_bases, int world, int rank, size_t flag_offset,
+                              uint32_t value, void* stream)
+{
+    ExchangeView v;
+    const int rc = peer_view(h, peer_bases, world, rank, v);
+    if (rc != MOE_FP8_B200_OK) return rc;
+    const cudaError_t e = launch_signal_peers(v, flag_offset, value, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? MOE_FP8_B200_OK : fail(h, MOE_FP8_B200_ERR_CUDA, "signal launch: %s", cudaGetErrorString(e));
+}
+
+int moe_fp8_b200_wait_peers(moe_fp8_b200_handle h, void* const* peer_bases, int world, int rank, size_t flag_offset,
+                            uint32_t value, void* stream)
+{
+    ExchangeView v;
+    const int rc = peer_view(h, peer_bases, world, rank, v);
+    if (rc != MOE_FP8_B200_OK) return rc;
+    const cudaError_t e = launch_wait_peers(v, flag_offset, value, h->ws.ctrl, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? MOE_FP8_B200_OK : fail(h, MOE_FP8_B200_ERR_CUDA, "wait launch: %s", cudaGetErrorString(e));
 }
 
 int moe_fp8_b200_host_wait(moe_fp8_b200_handle h, int64_t ticket)

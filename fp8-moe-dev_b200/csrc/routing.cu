@@ -500,6 +500,50 @@ __global__ void __launch_bounds__(kCombineThreads) reduce_owned_kernel(Workspace
     if (threadIdx.x == 0) atomicMax(&ws.ctrl->xch_time[4], (unsigned long long)global_timer_ns());
 }
 
+// ---------------------------------------------------------------------------------------
+// Hand-shake for staging buffers that the ranks fill in each other's memory with copy engines (the
+// host-resident form of the layer: every rank brings its token slice over PCIe and stores it into every
+// peer's input staging over NVLink, no SM involved).  signal: this rank's word of every peer's flag
+// array takes `value` (release, system scope; the copies before it in the stream have completed).  wait:
+// bounded spin until every rank's word in the LOCAL array has reached `value`; a peer that does not
+// arrive leaves kStatusExchangeTimeout in the status word, not a hung GPU.
+// ---------------------------------------------------------------------------------------
+__global__ void signal_peers_kernel(ExchangeView ex, size_t flag_offset, uint32_t value)
+{
+    if (threadIdx.x < (unsigned)ex.world) {
+        __threadfence_system();
+        uint32_t* flag = reinterpret_cast<uint32_t*>(peer_ptr(ex, threadIdx.x) + flag_offset) + ex.rank;
+        st_release_sys_u32(flag, value);
+    }
+}
+
+__global__ void wait_peers_kernel(ExchangeView ex, size_t flag_offset, uint32_t value, Control* ctrl)
+{
+    if (threadIdx.x < (unsigned)ex.world) {
+        const uint32_t* flag = reinterpret_cast<const uint32_t*>(peer_ptr(ex, ex.rank) + flag_offset) + threadIdx.x;
+        const uint64_t t0 = global_timer_ns();
+        const uint64_t limit_ns = (uint64_t)ex.wait_limit_us * 1000ull;
+        uint32_t it = 0;
+        while ((int32_t)(ld_acquire_sys_u32(flag) - value) < 0) {
+            if ((++it & 0x3fu) == 0u && global_timer_ns() - t0 > limit_ns) {
+                atomicCAS(&ctrl->status, kStatusOk, kStatusExchangeTimeout);
+                break;
+            }
+        }
+    }
+}
+
+cudaError_t launch_signal_peers(const ExchangeView& ex, size_t flag_offset, uint32_t value, cudaStream_t stream)
+{
+    signal_peers_kernel<<<1, 32, 0, stream>>>(ex, flag_offset, value);
+    return cudaGetLastError();
+}
+cudaError_t launch_wait_peers(const ExchangeView& ex, size_t flag_offset, uint32_t value, Control* ctrl, cudaStream_t stream)
+{
+    wait_peers_kernel<<<1, 32, 0, stream>>>(ex, flag_offset, value, ctrl);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_combine_push(const Workspace& ws, const ExchangeView& ex, int T, cudaStream_t stream)
 {
     int dev = 0, sms = 0;

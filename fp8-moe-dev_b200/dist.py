@@ -139,6 +139,9 @@ class ShardedMoe:
         self._epoch = 0
         self._host_stage = None   # device staging of the host entry points (two sets)
         self._host_seq = 0
+        self.trace = None         # diagnostics: a list makes run_host_async append its per-phase CUDA events
+        self.copy_engine_gather = True   # host entry points: replicate the inputs with peer copies (False: NCCL)
+        self._symm_stage = None
 
     def _ensure_exchange(self):
         """Allocate and exchange the receive buffers (torch symmetric memory: plumbing only;
@@ -176,6 +179,32 @@ class ShardedMoe:
             gemm2_weights, gemm2_weights_scale, self.local_expert_offset, routed_scaling_factor, scatter_out,
             ptrs, nbytes, self.rank, self.world, self._epoch, capacity_tokens=self.max_tokens)
 
+    def _symmetric_input_staging(self, T: int, dev):
+        """Both sets' gathered inputs (logits [T,256], hidden [T,7168], scales [56,T]) in ONE peer-mapped buffer
+        behind a 256-byte flag array, so that every rank can store its token slice straight into every peer's
+        staging with copy engines.  Returns (views of set 0, views of set 1, byte offsets of the three tensors
+        inside a set, set stride, peer base pointers, keep-alive objects)."""
+        import torch.distributed._symmetric_memory as symm_mem
+        W, per = self.world, T // self.world
+        al = lambda n: (n + 255) // 256 * 256
+        b_logits, b_hidden, b_parts = T * NE * 4, T * 7168, 56 * T * 4
+        offs = (0, al(b_logits), al(b_logits) + al(b_hidden))
+        set_bytes = offs[2] + al(b_parts)
+        group = self.group if self.group is not None else dist.group.WORLD
+        buf = symm_mem.empty(256 + 2 * set_bytes, dtype=torch.uint8, device=dev)
+        hdl = symm_mem.rendezvous(buf, group=group)
+        buf.zero_()
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=group)          # nobody signals before every flag array has been zeroed
+        sets = []
+        for s in range(2):
+            base = 256 + s * set_bytes
+            sets.append(dict(
+                logits=buf[base + offs[0]: base + offs[0] + b_logits].view(torch.float32).view(T, NE),
+                hidden=buf[base + offs[1]: base + offs[1] + b_hidden].view(torch.float8_e4m3fn).view(T, 7168),
+                scale=buf[base + offs[2]: base + offs[2] + b_parts].view(torch.float32).view(56, T)))
+        return sets, offs, set_bytes, [int(p) for p in hdl.buffer_ptrs], (buf, hdl)
+
     def _host_stage_set(self, T: int, which: int):
         """Device staging of the host entry points: two sets, so that a call's copies can overlap
         the neighbouring calls' compute."""
@@ -183,21 +212,79 @@ class ShardedMoe:
         per = T // W
         dev = torch.device("cuda", self.layer.device)
         if self._host_stage is None or self._host_stage[0]["T"] != T:
-            def one():
-                return dict(T=T,
-                            logits=torch.empty((T, NE), dtype=torch.float32, device=dev),
-                            hidden=torch.empty((T, 7168), dtype=torch.float8_e4m3fn, device=dev),
-                            scale_parts=torch.empty((W, 56, per), dtype=torch.float32, device=dev),
-                            scale=torch.empty((56, T), dtype=torch.float32, device=dev),
-                            out=torch.empty((per, 7168), dtype=torch.bfloat16, device=dev),
-                            full=torch.empty((T, 7168), dtype=torch.bfloat16, device=dev),
-                            ev_in=torch.cuda.Event(), ev_compute=torch.cuda.Event(), ev_out=torch.cuda.Event())
             torch.cuda.synchronize(dev)
-            self._host_stage = [one(), one()]
+            self._symm_stage = None
+            shared = [dict(), dict()]
+            if W > 1 and self.copy_engine_gather:
+                sets, offs, set_bytes, ptrs, keep = self._symmetric_input_staging(T, dev)
+                shared = sets
+                self._symm_stage = dict(offs=offs, set_bytes=set_bytes, ptrs=ptrs, keep=keep)
+
+            def one(sh):
+                st = dict(T=T, out=torch.empty((per, 7168), dtype=torch.bfloat16, device=dev),
+                          full=torch.empty((T, 7168), dtype=torch.bfloat16, device=dev),
+                          ev_in=torch.cuda.Event(), ev_compute=torch.cuda.Event(), ev_out=torch.cuda.Event())
+                if sh:       # peer-mapped: the slices arrive in place, scales included
+                    st.update(sh)
+                else:        # NCCL: contiguous per-rank scale pieces are gathered, then re-laid as [56, T]
+                    st.update(logits=torch.empty((T, NE), dtype=torch.float32, device=dev),
+                              hidden=torch.empty((T, 7168), dtype=torch.float8_e4m3fn, device=dev),
+                              scale_parts=torch.empty((W, 56, per), dtype=torch.float32, device=dev),
+                              scale=torch.empty((56, T), dtype=torch.float32, device=dev))
+                return st
+            self._host_stage = [one(shared[0]), one(shared[1])]
+            # one "output is in host memory" event per call in flight (three may be: one copying in, one
+            # computing, one copying out), so that waiting for a call never waits for a later one
+            self._done_events = [torch.cuda.Event() for _ in range(4)]
+            self._waited_upto = -1
+            # flag values for the peers, one pinned word per call (a 4-byte copy delivers it: no SM needed)
+            self._flag_ring = torch.zeros(1024, dtype=torch.int32).pin_memory()
             self._host_seq = 0
             self._s_in = torch.cuda.Stream(dev)
             self._s_out = torch.cuda.Stream(dev)
         return self._host_stage[which]
+
+    def _push_slices_to_peers(self, T: int, seq: int):
+        """Copy-engine form of the all-gather that replicates the inputs: this rank's rows of logits and hidden
+        and its columns of the scale matrix go from its own staging into the same place of every peer's staging
+        (peer copies on the copy-in stream), followed by this call's number into this rank's word of every
+        peer's flag array (a 4-byte copy from pinned host memory).  Nothing here needs an SM: the persistent
+        GEMM CTAs of the call that is computing meanwhile leave none free, and an NCCL all-gather (or any
+        kernel) on this stream would wait for them.  The consumer side is `_wait_for_peer_slices`.  Safe to
+        overwrite a peer's set: this rank's compute of two calls ago has finished, and the cross-rank sum inside
+        it completed only after every peer had finished the kernels that read that set."""
+        sg, lib = self._symm_stage, self.layer._lib
+        W, per, s = self.world, T // self.world, seq & 1
+        lo = self.rank * per
+        base = 256 + s * sg["set_bytes"]
+        # (offset of the piece, dst/src pitch, bytes per row, rows)
+        pieces = ((sg["offs"][0] + lo * NE * 4, per * NE * 4, per * NE * 4, 1),
+                  (sg["offs"][1] + lo * 7168, per * 7168, per * 7168, 1),
+                  (sg["offs"][2] + lo * 4, T * 4, per * 4, 56))
+        stream = self._s_in.cuda_stream
+        mine = sg["ptrs"][self.rank]
+        slot = seq % self._flag_ring.numel()
+        self._flag_ring[slot] = (seq + 1) & 0x7FFFFFFF
+        flag_src = self._flag_ring.data_ptr() + 4 * slot
+        for d in range(W):
+            p = (self.rank + 1 + d) % W        # every rank starts on another destination; itself last (flag only)
+            if p != self.rank:
+                for off, pitch, row_bytes, rows in pieces:
+                    if lib.moe_fp8_b200_copy_device(sg["ptrs"][p] + base + off, pitch, mine + base + off, pitch,
+                                                    row_bytes, rows, stream) != 0:
+                        raise RuntimeError("moe_fp8_b200_copy_device failed")
+            if lib.moe_fp8_b200_copy_rows_h2d(sg["ptrs"][p] + 4 * self.rank, 4, flag_src, 4, 4, 1, stream) != 0:
+                raise RuntimeError("flag copy failed")
+
+    def _wait_for_peer_slices(self, seq: int, stream: int):
+        """On the compute stream, in front of the layer: bounded wait until every rank's word of the local
+        flag array has reached this call's number (a peer that never delivers shows up in layer.check())."""
+        import ctypes as C
+        sg, W = self._symm_stage, self.world
+        arr = (C.c_void_p * W)(*sg["ptrs"])
+        h = self.layer._h
+        if self.layer._lib.moe_fp8_b200_wait_peers(h, arr, W, self.rank, 0, (seq + 1) & 0x7FFFFFFF, C.c_void_p(stream)) != 0:
+            raise RuntimeError("peer wait launch failed: " + self.layer._lib.moe_fp8_b200_last_error(h).decode())
 
     def run_host_async(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
                        gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, routed_scaling_factor, output,
@@ -208,8 +295,11 @@ class ShardedMoe:
         routes all tokens), the layer runs with the reduce-scatter fused in, and the rank writes its
         slice of the summed output back to `output[lo:hi]` (`all_reduce`: all of `output`).  T must be
         a multiple of the group size.  Returns a ticket at once; the host tensors must stay untouched
-        until `host_wait(ticket)`, and at most two calls may be in flight.  Copy-in, compute and
-        copy-out run on three streams, so consecutive calls overlap them."""
+        until `host_wait(ticket)`.  Up to three calls may be outstanding (one copying in, one computing,
+        one copying out, on three streams): issue call i, then wait for call i-2 -- with three rotating host
+        output buffers -- and neither PCIe direction stands in front of the compute.  (Two device staging
+        sets suffice: a set's inputs are free once its call has computed, its output once it is copied out,
+        and those two conditions are waited for on the device.)"""
         T = int(routing_logits.shape[0])
         W = self.world
         if T % W:
@@ -219,31 +309,54 @@ class ShardedMoe:
         dev = torch.device("cuda", self.layer.device)
         self._host_stage_set(T, 0)
         seq = self._host_seq
+        if seq - 3 > self._waited_upto:
+            raise RuntimeError(f"call {seq}: at most three calls may be outstanding; host_wait({seq - 3}) first")
         self._host_seq += 1
         st = self._host_stage[seq & 1]
         cur = torch.cuda.current_stream(dev)
+        tr = None
+        if self.trace is not None:   # (seq, copy-in start, copied, gathered, compute start, compute end, copy-out end)
+            tr = [seq] + [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+            self.trace.append(tr)
         with torch.cuda.stream(self._s_in):
             if seq >= 2:
                 self._s_in.wait_event(st["ev_compute"])   # the set's inputs were read two calls ago
+            if tr:
+                tr[1].record(self._s_in)
             # this rank's slice, straight into its place in the gathered tensors: two contiguous runs of
             # rows, and the rank's columns of the [56, T] scale matrix as ONE strided copy (a plain
             # tensor copy of that view would pack it through pageable memory and block the host)
             st["logits"][lo:lo + per].copy_(routing_logits[lo:lo + per], non_blocking=True)
             st["hidden"][lo:lo + per].view(torch.uint8).copy_(hidden_states[lo:lo + per].view(torch.uint8), non_blocking=True)
-            part = st["scale_parts"][self.rank]
+            if self._symm_stage is not None:    # straight into the rank's columns of the [56, T] staging
+                dst, dpitch = st["scale"].data_ptr() + lo * 4, T * 4
+            else:                               # contiguous piece for the NCCL gather
+                dst, dpitch = st["scale_parts"][self.rank].data_ptr(), per * 4
             rc = self.layer._lib.moe_fp8_b200_copy_rows_h2d(
-                part.data_ptr(), per * 4, hidden_states_scale.data_ptr() + lo * 4, T * 4, per * 4, 56,
-                self._s_in.cuda_stream)
+                dst, dpitch, hidden_states_scale.data_ptr() + lo * 4, T * 4, per * 4, 56, self._s_in.cuda_stream)
             if rc != 0:
                 raise RuntimeError(f"moe_fp8_b200_copy_rows_h2d failed: {rc}")
+            if tr:
+                tr[2].record(self._s_in)
             # the all-gather that replicates the inputs runs behind the copies on the copy-in stream, so
-            # that it overlaps the previous call's compute instead of standing in front of this call's
-            gather_token_slices(st["logits"], st["hidden"].view(torch.uint8), st["scale_parts"], st["scale"],
-                                self.rank, W, self.group)
+            # that it overlaps the previous call's compute instead of standing in front of this call's:
+            # with copy engines into peer-mapped staging (no SM: an NCCL kernel would have to wait for the
+            # persistent GEMM CTAs of the previous call to leave), or through NCCL
+            if self._symm_stage is not None:
+                self._push_slices_to_peers(T, seq)
+            else:
+                gather_token_slices(st["logits"], st["hidden"].view(torch.uint8), st["scale_parts"], st["scale"],
+                                    self.rank, W, self.group)
             st["ev_in"].record(self._s_in)
+            if tr:
+                tr[3].record(self._s_in)
         cur.wait_event(st["ev_in"])
         if seq >= 2:
             cur.wait_event(st["ev_out"])                  # the set's output was copied out two calls ago
+        if self._symm_stage is not None:
+            self._wait_for_peer_slices(seq, cur.cuda_stream)
+        if tr:
+            tr[4].record(cur)
         if mode == "fused" and W > 1:
             res = self.run_fused(st["logits"], routing_bias, st["hidden"], st["scale"], gemm1_weights, gemm1_weights_scale,
                                  gemm2_weights, gemm2_weights_scale, routed_scaling_factor, scatter_out=st["out"])
@@ -252,6 +365,8 @@ class ShardedMoe:
                            gemm2_weights, gemm2_weights_scale, routed_scaling_factor, st["full"],
                            mode="reduce_scatter" if mode == "fused" else mode, scatter_out=st["out"])
         st["ev_compute"].record(cur)
+        if tr:
+            tr[5].record(cur)
         with torch.cuda.stream(self._s_out):
             self._s_out.wait_event(st["ev_compute"])
             if mode == "all_reduce":
@@ -259,15 +374,19 @@ class ShardedMoe:
             else:
                 output[lo:lo + per].copy_(res[:per], non_blocking=True)
             st["ev_out"].record(self._s_out)
+            self._done_events[seq % 4].record(self._s_out)
+            if tr:
+                tr[6].record(self._s_out)
         return seq
 
     def host_wait(self, ticket: int) -> None:
         """Blocks until the output of call `ticket` is in host memory."""
         if self._host_stage is None or not 0 <= ticket < self._host_seq:
             raise ValueError(f"ticket {ticket} was never issued")
-        # the set's event is re-recorded by every later call on the set, in the stream of the ticket's own
-        # copy-out: its latest record also covers the older ticket
-        self._host_stage[ticket & 1]["ev_out"].synchronize()
+        if ticket + 4 <= self._host_seq:
+            return   # run_host_async only let call ticket + 3 start after this one had been waited for
+        self._done_events[ticket % 4].synchronize()
+        self._waited_upto = max(self._waited_upto, ticket)
 
     def run_host(self, *args, **kwargs):
         """Blocking form of run_host_async."""

@@ -184,6 +184,25 @@ MOE_FP8_B200_API int moe_fp8_b200_host_wait(moe_fp8_b200_handle h, int64_t ticke
 MOE_FP8_B200_API int moe_fp8_b200_copy_rows_h2d(void* dst_device, size_t dst_pitch, const void* src_host,
                                                 size_t src_pitch, size_t row_bytes, size_t rows, void* stream);
 
+/* Plumbing of the multi-GPU wrapper's host-resident form, in which the ranks fill each other's input staging
+ * with copy engines instead of an SM-based all-gather (no counterpart in the reference):
+ *   copy_device    `rows` pieces of `row_bytes` bytes device-to-device on `stream` (one cudaMemcpyAsync or
+ *                  cudaMemcpy2DAsync: copy engines, no SM; dst may be a peer's mapped memory);
+ *   signal_peers   after the copies: this rank's 32-bit word (index `rank`) of the flag array at `flag_offset`
+ *                  inside EVERY rank's buffer takes `value` (release at system scope).  A tiny kernel: where
+ *                  no SM may be free (behind persistent kernels) the wrapper stores the word with a 4-byte
+ *                  copy from pinned host memory instead (moe_fp8_b200_copy_rows_h2d), which needs none;
+ *   wait_peers     before the consumer: spins, bounded by MOE_FP8_B200_OPT_WAIT_LIMIT_US, until all `world`
+ *                  words of the LOCAL flag array have reached `value` (wrap-safe); on expiry the device
+ *                  status word records it and moe_fp8_b200_check returns MOE_FP8_B200_ERR_DEVICE.
+ * peer_bases[i] is rank i's buffer as mapped into this process (peer_bases[rank] the local one). */
+MOE_FP8_B200_API int moe_fp8_b200_copy_device(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                                              size_t row_bytes, size_t rows, void* stream);
+MOE_FP8_B200_API int moe_fp8_b200_signal_peers(moe_fp8_b200_handle h, void* const* peer_bases, int world, int rank,
+                                               size_t flag_offset, uint32_t value, void* stream);
+MOE_FP8_B200_API int moe_fp8_b200_wait_peers(moe_fp8_b200_handle h, void* const* peer_bases, int world, int rank,
+                                             size_t flag_offset, uint32_t value, void* stream);
+
 /* ---- expert-parallel run with the reduce-scatter fused into the combine step -----------
  * No counterpart in the reference (it has no multi-GPU code; its local_expert_offset
  * argument, kernel/moe_fp8.cu:2671, only says which 32 experts a rank holds).  `world` ranks

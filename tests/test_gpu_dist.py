@@ -92,6 +92,14 @@ def _worker(rank, world, port, T, q):
                 moe.host_wait(tickets[i])
                 ok_fused = ok_fused and torch.equal(outs[i % 2][lo:hi], want[lo:hi].cpu())
             moe.layer.check()
+            # the same with the inputs replicated by NCCL all-gathers instead of peer copies
+            moe_n = ShardedMoe(T)
+            moe_n.copy_engine_gather = False
+            host_out.zero_()
+            dist.barrier()
+            moe_n.run_host(pin[0], dev[1], pin[1], pin[2], *w, 2.5, host_out, mode="fused")
+            moe_n.layer.check()
+            ok_fused = ok_fused and torch.equal(host_out[lo:hi], want[lo:hi].cpu())
         # strided expert placement: other owners, same pairs; the summed output agrees up to the
         # rounding of the partial outputs, and the ranks' row counts add up to the same total
         rows_c = torch.tensor([int(moe.layer.read("pair_count", T).sum())], device="cuda")
