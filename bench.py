@@ -613,6 +613,10 @@ def run_ours(args, rank, world, local):
                 "placement_trial_ms": placement_ms, "contiguous_ms_per_step": contiguous_ms,
                 "contiguous_tokens_per_s": round(T / contiguous_ms * 1e3, 1) if contiguous_ms else None,
                 "other_collective_ms_per_step": other_ms, "exchange": exchange},
+        # the same metric with the partition the layer's interface names (local_expert_offset = 256/N * rank),
+        # whatever placement `value` was measured with
+        "value_contiguous_placement": (round(T / contiguous_ms * 1e3, 1) if contiguous_ms else None) if world > 1
+                                       else round(T / ms * 1e3, 1),
         "parity": parity,
         "clocks": clk.summary(),
         "e2e": None if args.skip_e2e else {"value": round(T / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
