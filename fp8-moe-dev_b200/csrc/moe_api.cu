@@ -333,6 +333,7 @@ int validate(moe_fp8_b200_handle h, const moe_fp8_b200_args* a, bool need_output
     // (kernel/moe_fp8.cu:462-463 filters [offset, offset + 32)), so the offset is a multiple of 32 and the
     // block ends inside the 256 experts.  Strided placement: the offset is the phase.  Table: ignored.
     if (h->expert_map_set) {
+        // table placement: the offset plays no part
     } else if (h->opt_expert_stride > 1) {
         if (a->local_expert_offset < 0 || a->local_expert_offset >= h->opt_expert_stride)
             return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT,
