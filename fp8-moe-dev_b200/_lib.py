@@ -32,7 +32,8 @@ EXPORTS = [
     "moe_fp8_b200_host_wait", "moe_fp8_b200_set_expert_map", "moe_fp8_b200_inject_device_status",
     "moe_fp8_b200_exchange_regions", "moe_fp8_b200_copy_rows_h2d",
     "moe_fp8_b200_invalidate_weights", "moe_fp8_b200_copy_device", "moe_fp8_b200_signal_peers",
-    "moe_fp8_b200_wait_peers",
+    "moe_fp8_b200_wait_peers", "moe_fp8_b200_create_shaped", "moe_fp8_b200_workspace_bytes_shaped",
+    "moe_fp8_b200_get_shape",
 ]
 NOALLOC_MAX_TOKENS = 4096
 
@@ -45,6 +46,12 @@ class Args(C.Structure):
         ("gemm2_weights", C.c_void_p), ("gemm2_weights_scale", C.c_void_p), ("local_expert_offset", C.c_int64),
         ("routed_scaling_factor", C.c_double), ("output", C.c_void_p), ("num_tokens", C.c_int32),
     ]
+
+
+class Shape(C.Structure):
+    """moe_fp8_b200_shape"""
+    _fields_ = [("hidden", C.c_int32), ("intermediate", C.c_int32), ("top_k", C.c_int32), ("n_group", C.c_int32),
+                ("topk_group", C.c_int32)]
 
 
 class Exchange(C.Structure):
@@ -79,6 +86,12 @@ def load() -> C.CDLL:
     lib.moe_fp8_b200_row_capacity.argtypes = [C.c_int, C.c_int]
     lib.moe_fp8_b200_create.restype = C.c_int
     lib.moe_fp8_b200_create.argtypes = [C.POINTER(H), C.c_int, C.c_int, C.c_int]
+    lib.moe_fp8_b200_create_shaped.restype = C.c_int
+    lib.moe_fp8_b200_create_shaped.argtypes = [C.POINTER(H), C.c_int, C.c_int, C.c_int, C.POINTER(Shape)]
+    lib.moe_fp8_b200_workspace_bytes_shaped.restype = C.c_size_t
+    lib.moe_fp8_b200_workspace_bytes_shaped.argtypes = [C.c_int, C.c_int, C.POINTER(Shape)]
+    lib.moe_fp8_b200_get_shape.restype = C.c_int
+    lib.moe_fp8_b200_get_shape.argtypes = [H, C.POINTER(Shape)]
     lib.moe_fp8_b200_destroy.restype = C.c_int
     lib.moe_fp8_b200_destroy.argtypes = [H]
     lib.moe_fp8_b200_last_error.restype = C.c_char_p

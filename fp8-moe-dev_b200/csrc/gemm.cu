@@ -122,15 +122,15 @@ __device__ __forceinline__ TileCoord decode_tile(const Workspace& ws, int id, in
 struct UnitPlan {
     int units, split;
 };
-template <int KBLOCKS, bool SPLITK>
-__device__ __forceinline__ UnitPlan plan_units(int total_tiles, int num_ctas) {
+template <bool SPLITK>
+__device__ __forceinline__ UnitPlan plan_units(int KBLOCKS, int total_tiles, int num_ctas) {
     UnitPlan p;
     p.split = 1;
     if (SPLITK && total_tiles > 0 && total_tiles < num_ctas) {
         // rounds x (K blocks per unit + reduction overhead, about six K blocks' worth), units capped
         // by the scratch slots; ties keep the smaller split
         int best = KBLOCKS;
-        for (int s = 2; s <= KBLOCKS / 4 && total_tiles * s <= kSplitKSlots; ++s) {
+        for (int s = 2; s <= KBLOCKS / 4 && s <= kSplitKMaxSplit && total_tiles * s <= kSplitKSlots; ++s) {
             const int rounds = (total_tiles * s + num_ctas - 1) / num_ctas;
             const int cost = rounds * ((KBLOCKS + s - 1) / s + 6);
             if (cost < best) { best = cost; p.split = s; }
@@ -140,8 +140,7 @@ __device__ __forceinline__ UnitPlan plan_units(int total_tiles, int num_ctas) {
     return p;
 }
 // K-block range [kb0, kb1) of split `s` out of `split`
-template <int KBLOCKS>
-__device__ __forceinline__ void unit_range(int s, int split, int& kb0, int& kb1) {
+__device__ __forceinline__ void unit_range(int KBLOCKS, int s, int split, int& kb0, int& kb1) {
     kb0 = (KBLOCKS * s) / split;
     kb1 = (KBLOCKS * (s + 1)) / split;
 }
@@ -223,13 +222,19 @@ __device__ __forceinline__ float round_bf16(float x) {
 // MODE 1: GEMM1 + SwiGLU + requant (K = 7168).  MODE 2: GEMM2 -> bf16 Y (K = 2048).
 // SPLITK compiles the split-K path in; the plain instantiation carries none of its code
 // (having it in the main kernel cost 5-7 % on mid-size batches through register pressure).
-template <int MODE, bool SPLITK>
+// GENERIC takes hidden / intermediate from Workspace::geo instead of the reference's 7168 / 2048
+// (hidden a multiple of 256, intermediate of 128, at most 64 K blocks each); the reference's
+// geometry keeps its compile-time instantiation.
+template <int MODE, bool SPLITK, bool GENERIC = false>
 __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
     const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
     const __grid_constant__ CUtensorMap tmap_out, Workspace ws, const float2* __restrict__ w_scale_packed, int silu_exact)
 {
-    constexpr int kKBlocks = (MODE == 1) ? kHiddenBlocks : kInterBlocks;
-    constexpr int kTilesN = (MODE == 1) ? (kInter / kBlock) : (kHidden / kTileN);  // 16 / 28
+    static_assert(!(GENERIC && SPLITK), "the split-K kernel exists for the reference's geometry only");
+    const int hidden = GENERIC ? ws.geo.hidden : kHidden;
+    const int inter = GENERIC ? ws.geo.inter : kInter;
+    const int kKBlocks = ((MODE == 1) ? hidden : inter) / kBlock;                   // 56 / 16
+    const int kTilesN = (MODE == 1) ? (inter / kBlock) : (hidden / kTileN);         // 16 / 28
     constexpr int kStages = gemm_stages<SPLITK>();
 
     extern __shared__ uint8_t smem_raw[];
@@ -270,7 +275,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
     // Everything above is independent of earlier kernels; from here on their results are read.
     pdl_wait();
     const int total_tiles = ws.num_tiles[0] * kTilesN;
-    const UnitPlan plan = plan_units<kKBlocks, SPLITK>(total_tiles, (int)gridDim.x);
+    const UnitPlan plan = plan_units<SPLITK>(kKBlocks, total_tiles, (int)gridDim.x);
     if ((int)blockIdx.x >= plan.units) return;  // nothing for this CTA: leave before touching TMEM
     if (warp == 2) {
         tmem_alloc(smem_u32(&sh->tmem_base), kTmemCols);
@@ -293,7 +298,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
             for (int u = blockIdx.x; ok && u < plan.units; u += gridDim.x) {
                 const TileCoord tc = decode_tile(ws, u / plan.split, kTilesN);
                 int kb0, kb1;
-                unit_range<kKBlocks>(u % plan.split, plan.split, kb0, kb1);
+                unit_range(kKBlocks, u % plan.split, plan.split, kb0, kb1);
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
@@ -305,7 +310,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                     tma_load_2d(a_dst, &tmap_a, full, kb * kBlock, tc.row0);
                     if (MODE == 1) {
                         tma_load_3d(b_dst, &tmap_b, full, kb * kBlock, tc.n * kBlock, tc.e);
-                        tma_load_3d(b_dst + kBTileBytes / 2, &tmap_b, full, kb * kBlock, kInter + tc.n * kBlock, tc.e);
+                        tma_load_3d(b_dst + kBTileBytes / 2, &tmap_b, full, kb * kBlock, inter + tc.n * kBlock, tc.e);
                     } else {
                         tma_load_3d(b_dst, &tmap_b, full, kb * kBlock, tc.n * kTileN, tc.e);
                     }
@@ -332,7 +337,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
             bool next_full_ready = false;
             for (int u = blockIdx.x; ok && u < plan.units; u += gridDim.x) {
                 int kb0, kb1;
-                unit_range<kKBlocks>(u % plan.split, plan.split, kb0, kb1);
+                unit_range(kKBlocks, u % plan.split, plan.split, kb0, kb1);
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t as = it & 1u;
                     const uint32_t aph = (it >> 1) & 1u;
@@ -420,7 +425,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                         const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2] * inv_scale, v[3] * inv_scale),
                                                                      __NV_SATFINITE, __NV_E4M3);
                         const int grow = tc.row0 + r;
-                        reinterpret_cast<uint32_t*>(ws.a2 + (size_t)grow * kInter + tc.n * kBlock)[lane] = lo | (hi << 16);
+                        reinterpret_cast<uint32_t*>(ws.a2 + (size_t)grow * inter + tc.n * kBlock)[lane] = lo | (hi << 16);
                         if (lane == 0) ws.sfa2[(size_t)tc.n * ws.m_cap + grow] = scale;
                     }
                     __syncwarp();
@@ -453,7 +458,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
             const int tile_id = u / plan.split;
             const TileCoord tc = decode_tile(ws, tile_id, kTilesN);
             int kb0, kb1;
-            unit_range<kKBlocks>(u % plan.split, plan.split, kb0, kb1);
+            unit_range(kKBlocks, u % plan.split, plan.split, kb0, kb1);
             const int grow = tc.row0 + row;
             const float* sfa = ((MODE == 1) ? ws.sfa1 : ws.sfa2) + grow;
             // The tile's weight-block scales for all K blocks, from the pre-laid-out copy (one float2 per
@@ -620,7 +625,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                 const float scale = (maxv > 0.0f) ? (maxv / 448.0f) : 1.0f;
                 const float inv_scale = 1.0f / scale;
                 if (valid) {
-                    uint4* dst = reinterpret_cast<uint4*>(ws.a2 + (size_t)grow * kInter + tc.n * kBlock + 64 * h);
+                    uint4* dst = reinterpret_cast<uint4*>(ws.a2 + (size_t)grow * inter + tc.n * kBlock + 64 * h);
 #pragma unroll
                     for (int v8 = 0; v8 < 2; ++v8) {
                         uint4 pk[2];
@@ -644,7 +649,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                 }
             } else {
                 if (valid) {
-                    uint4* dst = reinterpret_cast<uint4*>(ws.y + (size_t)grow * kHidden + tc.n * kTileN + 128 * h);
+                    uint4* dst = reinterpret_cast<uint4*>(ws.y + (size_t)grow * hidden + tc.n * kTileN + 128 * h);
 #pragma unroll
                     for (int v8 = 0; v8 < 8; ++v8) {
                         uint4 pk[2];
@@ -683,38 +688,41 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
 // scale transposes (kernel/moe_fp8.cu:981-994, cached per scale pointer at :3007-3014, 3501-3508).
 // ---------------------------------------------------------------------------------------
 __global__ void repack_weight_scales_kernel(const float* __restrict__ s1, const float* __restrict__ s2,
-                                            float2* __restrict__ p1, float2* __restrict__ p2, int num_experts)
+                                            float2* __restrict__ p1, float2* __restrict__ p2, int num_experts,
+                                            Geometry geo)
 {
-    constexpr int kN1 = kInter / kBlock;        // 16 GEMM1 tiles per expert
-    constexpr int kN2 = kHidden / kTileN;       // 28 GEMM2 tiles per expert
-    const int per1 = kN1 * kHiddenBlocks, per2 = kN2 * kInterBlocks;
+    const int hb = geo.hidden / kBlock, ib = geo.inter / kBlock;   // 56 / 16 K blocks
+    const int kN1 = ib;                    // 16 GEMM1 tiles per expert
+    const int kN2 = geo.hidden / kTileN;   // 28 GEMM2 tiles per expert
+    const int per1 = kN1 * hb, per2 = kN2 * ib;
     const int total = num_experts * (per1 + per2);
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         const int e = i / (per1 + per2);
         const int r = i - e * (per1 + per2);
         if (r < per1) {
-            const int n = r / kHiddenBlocks, kb = r - n * kHiddenBlocks;
-            const float* src = s1 + ((size_t)e * (kGemm1Out / kBlock) + n) * kHiddenBlocks + kb;
-            p1[(size_t)e * per1 + r] = make_float2(src[0], src[(size_t)kN1 * kHiddenBlocks]);
+            const int n = r / hb, kb = r - n * hb;
+            const float* src = s1 + ((size_t)e * (2 * kN1) + n) * hb + kb;
+            p1[(size_t)e * per1 + r] = make_float2(src[0], src[(size_t)kN1 * hb]);
         } else {
             const int r2 = r - per1;
-            const int n = r2 / kInterBlocks, kb = r2 - n * kInterBlocks;
-            const float* src = s2 + ((size_t)e * kHiddenBlocks + 2 * n) * kInterBlocks + kb;
-            p2[(size_t)e * per2 + r2] = make_float2(src[0], src[kInterBlocks]);
+            const int n = r2 / ib, kb = r2 - n * ib;
+            const float* src = s2 + ((size_t)e * hb + 2 * n) * ib + kb;
+            p2[(size_t)e * per2 + r2] = make_float2(src[0], src[ib]);
         }
     }
 }
 
-size_t packed_scale_floats(int mode, int num_experts)
+size_t packed_scale_floats(int mode, int num_experts, const Geometry& geo)
 {
-    return 2 * (size_t)num_experts * (mode == 1 ? (kInter / kBlock) * kHiddenBlocks : (kHidden / kTileN) * kInterBlocks);
+    const size_t hb = geo.hidden / kBlock, ib = geo.inter / kBlock;
+    return 2 * (size_t)num_experts * (mode == 1 ? ib * hb : (size_t)(geo.hidden / kTileN) * ib);
 }
 
 cudaError_t launch_repack_weight_scales(const float* s1, const float* s2, float* p1, float* p2, int num_experts,
-                                        cudaStream_t stream)
+                                        const Geometry& geo, cudaStream_t stream)
 {
     repack_weight_scales_kernel<<<64, 256, 0, stream>>>(s1, s2, reinterpret_cast<float2*>(p1), reinterpret_cast<float2*>(p2),
-                                                        num_experts);
+                                                        num_experts, geo);
     return cudaGetLastError();
 }
 
@@ -813,10 +821,16 @@ cudaError_t configure_gemm_kernels()
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(grouped_gemm_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)gemm_smem_bytes<2, true>());
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(grouped_gemm_kernel<1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)gemm_smem_bytes<1, false>());
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(grouped_gemm_kernel<2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)gemm_smem_bytes<2, false>());
     return e;
 }
 
-int gemm_tiles_n(int mode) { return mode == 1 ? kInter / kBlock : kHidden / kTileN; }
+int gemm_tiles_n(int mode, const Geometry& geo) { return mode == 1 ? geo.inter / kBlock : geo.hidden / kTileN; }
 
 cudaError_t launch_grouped_gemm(int mode, const void* tmap_a, const void* tmap_b, const void* tmap_out, const Workspace& ws,
                                 const float* w_scale_packed, int silu_exact, int num_ctas, int split_k, cudaStream_t stream)
@@ -834,6 +848,13 @@ cudaError_t launch_grouped_gemm(int mode, const void* tmap_a, const void* tmap_b
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (!ws.geo.is_reference()) {
+        // other geometries: the generic instantiations (no split-K form; the caller does not ask for one)
+        cfg.dynamicSmemBytes = gemm_smem_bytes<1, false>();
+        if (split_k) return cudaErrorInvalidValue;
+        if (mode == 1) return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<1, false, true>, *ma, *mb, *mo, ws, w_scale, silu_exact);
+        return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<2, false, true>, *ma, *mb, *mo, ws, w_scale, silu_exact);
+    }
     if (mode == 1) {
         cfg.dynamicSmemBytes = split_k ? gemm_smem_bytes<1, true>() : gemm_smem_bytes<1, false>();
         if (split_k) return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<1, true>, *ma, *mb, *mo, ws, w_scale, silu_exact);

@@ -49,6 +49,19 @@ struct DispatchPolicy {
     // are exactly those of the reference's shard calls.
     int expert_stride;
     int expert_phase;
+    // Routing constants (the reference compiles 8 / 8 / 4 in, kernel/moe_fp8.cu:301-304; FlashInfer's
+    // definition of the layer carries them as axes).  0 in all three = the reference's values.
+    int top_k;        // experts selected per token, <= 8
+    int n_group;      // routing groups: 1, 2, 4 or 8 (256 / n_group experts each)
+    int topk_group;   // groups kept per token, <= n_group
+};
+
+// Run-time geometry of a handle.  The reference's layer is hidden 7168 / intermediate 2048; other
+// multiples of the 128 block (hidden a multiple of 256, both at most 8192) run through the generic
+// instantiations of the kernels, the reference's own geometry through the compile-time ones.
+struct Geometry {
+    int hidden, inter;
+    __host__ __device__ bool is_reference() const { return hidden == kHidden && inter == kInter; }
 };
 
 // Integer control block.  Zeroed when the handle is created; after that the last CTA of the
@@ -131,6 +144,7 @@ struct Workspace {
     float* splitk_partial;  // [kSplitKSlots, 4, 256] fp32 partial rows of split-K work units
     int m_cap;              // packed-row capacity (multiple of 128)
     int max_tiles;
+    Geometry geo;
 };
 
 }  // namespace moe

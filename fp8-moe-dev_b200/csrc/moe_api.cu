@@ -18,7 +18,7 @@ cudaError_t launch_route_dispatch(const float*, const void*, const Workspace&, i
                                   const DispatchPolicy&, int, cudaStream_t);
 cudaError_t launch_permute(const void*, const float*, const Workspace&, int, cudaStream_t);
 cudaError_t launch_combine(const Workspace&, void*, int, cudaStream_t);
-cudaError_t launch_quantize_rows(const void*, void*, float*, int, cudaStream_t);
+cudaError_t launch_quantize_rows(const void*, void*, float*, int, int, cudaStream_t);
 cudaError_t launch_combine_push(const Workspace&, const ExchangeView&, int, cudaStream_t);
 cudaError_t launch_reduce_owned(const Workspace&, const ExchangeView&, int, void*, cudaStream_t);
 cudaError_t launch_signal_peers(const ExchangeView&, size_t, uint32_t, cudaStream_t);
@@ -30,9 +30,9 @@ size_t tensor_map_bytes();
 cudaError_t configure_gemm_kernels();
 cudaError_t launch_grouped_gemm(int, const void*, const void*, const void*, const Workspace&, const float*, int, int, int,
                                 cudaStream_t);
-int gemm_tiles_n(int mode);
-size_t packed_scale_floats(int mode, int num_experts);
-cudaError_t launch_repack_weight_scales(const float*, const float*, float*, float*, int, cudaStream_t);
+int gemm_tiles_n(int mode, const Geometry& geo);
+size_t packed_scale_floats(int mode, int num_experts, const Geometry& geo);
+cudaError_t launch_repack_weight_scales(const float*, const float*, float*, float*, int, const Geometry&, cudaStream_t);
 }  // namespace moe
 
 using namespace moe;
@@ -69,8 +69,11 @@ struct Layout {
     int m_cap, max_tiles;
 };
 
-Layout make_layout(int T, int E)
+constexpr Geometry kReferenceGeometry = {kHidden, kInter};
+
+Layout make_layout(int T, int E, const Geometry& geo = kReferenceGeometry)
 {
+    const size_t hidden = (size_t)geo.hidden, inter = (size_t)geo.inter;
     Layout L;
     L.m_cap = row_capacity(T, E);
     L.max_tiles = L.m_cap / kTileM;
@@ -86,14 +89,14 @@ Layout make_layout(int T, int E)
     L.pair_code = c.take(sizeof(uint32_t) * (size_t)T * kTopK);
     L.pair_weight = c.take(sizeof(float) * (size_t)T * kTopK);
     L.row_token = c.take(sizeof(int) * (size_t)L.m_cap);
-    L.a1 = c.take((size_t)L.m_cap * kHidden);
-    L.sfa1 = c.take(sizeof(float) * (size_t)kHiddenBlocks * L.m_cap);
-    L.a2 = c.take((size_t)L.m_cap * kInter);
-    L.sfa2 = c.take(sizeof(float) * (size_t)kInterBlocks * L.m_cap);
-    L.y = c.take(sizeof(__nv_bfloat16) * (size_t)L.m_cap * kHidden);
+    L.a1 = c.take((size_t)L.m_cap * hidden);
+    L.sfa1 = c.take(sizeof(float) * (hidden / kBlock) * L.m_cap);
+    L.a2 = c.take((size_t)L.m_cap * inter);
+    L.sfa2 = c.take(sizeof(float) * (inter / kBlock) * L.m_cap);
+    L.y = c.take(sizeof(__nv_bfloat16) * (size_t)L.m_cap * hidden);
     L.splitk = c.take(sizeof(float) * (size_t)kSplitKSlots * 4 * 256);  // kSplitKMaxRows rows of 256 floats per unit
-    L.sw1_packed = c.take(sizeof(float) * packed_scale_floats(1, E));
-    L.sw2_packed = c.take(sizeof(float) * packed_scale_floats(2, E));
+    L.sw1_packed = c.take(sizeof(float) * packed_scale_floats(1, E, geo));
+    L.sw2_packed = c.take(sizeof(float) * packed_scale_floats(2, E, geo));
     L.total = c.off;
     return L;
 }
@@ -105,6 +108,9 @@ struct moe_fp8_b200_ctx {
     int max_tokens = 0;
     int num_local_experts = 0;
     int num_sms = 0;
+    Geometry geo = {kHidden, kInter};
+    int top_k = kTopK, n_group = kNumGroups, topk_group = kTopKGroup;
+    bool reference_routing() const { return top_k == kTopK && n_group == kNumGroups && topk_group == kTopKGroup; }
     int opt_reference_pruning = 1;
     int opt_exact_silu = 0;
     bool counters_dirty = false;
@@ -205,18 +211,28 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
     const int placement = h->expert_map_set ? -1 : h->opt_expert_stride;   // -1 table, 1 contiguous, S strided
     pol.expert_stride = placement;
     pol.expert_phase = placement < 0 ? 0 : (int)a.local_expert_offset;
+    if (!h->reference_routing()) { pol.top_k = h->top_k; pol.n_group = h->n_group; pol.topk_group = h->topk_group; }
+    const bool ref_geo = h->geo.is_reference();
+    const uint64_t hidden = (uint64_t)h->geo.hidden, inter = (uint64_t)h->geo.inter;
+    if (ex && !ref_geo)
+        return fail(h, MOE_FP8_B200_ERR_UNSUPPORTED, "the fused combine + reduce-scatter exists for hidden 7168 only (handle has %d)",
+                    h->geo.hidden);
     if (a.gemm1_weights != h->cached_w1) {
-        const int r = encode_kmajor_u8_map(h->tmap_w1, a.gemm1_weights, kHidden, kGemm1Out, E, 128);
+        const int r = encode_kmajor_u8_map(h->tmap_w1, a.gemm1_weights, hidden, 2 * inter, E, 128);
         if (r != 0) return fail(h, MOE_FP8_B200_ERR_CUDA, "cuTensorMapEncodeTiled(W1) failed: %d", r);
-        const int r2 = encode_rows_1k_map(h->tmap_dec_w1, a.gemm1_weights, kHidden, (uint64_t)E * kGemm1Out, 8);
-        if (r2 != 0) return fail(h, MOE_FP8_B200_ERR_CUDA, "cuTensorMapEncodeTiled(W1, decode view) failed: %d", r2);
+        if (ref_geo) {
+            const int r2 = encode_rows_1k_map(h->tmap_dec_w1, a.gemm1_weights, kHidden, (uint64_t)E * kGemm1Out, 8);
+            if (r2 != 0) return fail(h, MOE_FP8_B200_ERR_CUDA, "cuTensorMapEncodeTiled(W1, decode view) failed: %d", r2);
+        }
         h->cached_w1 = a.gemm1_weights;
     }
     if (a.gemm2_weights != h->cached_w2) {
-        const int r = encode_kmajor_u8_map(h->tmap_w2, a.gemm2_weights, kInter, kHidden, E, 256);
+        const int r = encode_kmajor_u8_map(h->tmap_w2, a.gemm2_weights, inter, hidden, E, 256);
         if (r != 0) return fail(h, MOE_FP8_B200_ERR_CUDA, "cuTensorMapEncodeTiled(W2) failed: %d", r);
-        const int r2 = encode_rows_1k_map(h->tmap_dec_w2, a.gemm2_weights, kInter, (uint64_t)E * kHidden, 16);
-        if (r2 != 0) return fail(h, MOE_FP8_B200_ERR_CUDA, "cuTensorMapEncodeTiled(W2, decode view) failed: %d", r2);
+        if (ref_geo) {
+            const int r2 = encode_rows_1k_map(h->tmap_dec_w2, a.gemm2_weights, kInter, (uint64_t)E * kHidden, 16);
+            if (r2 != 0) return fail(h, MOE_FP8_B200_ERR_CUDA, "cuTensorMapEncodeTiled(W2, decode view) failed: %d", r2);
+        }
         h->cached_w2 = a.gemm2_weights;
     }
     cudaEvent_t* ev = nullptr;
@@ -239,7 +255,7 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
         h->counters_dirty = false;
     }
     if (h->opt_decode && h->decode_ctas_per_sm > 0 && T <= kDecodeMaxTokens && finalize && !ex && placement == 1 &&
-        h->opt_stop_after == 0) {
+        h->opt_stop_after == 0 && ref_geo && h->reference_routing()) {
         // the whole layer as one cooperative kernel, one CTA per SM
         DecodeArgs d;
         d.logits = a.routing_logits;
@@ -276,7 +292,8 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
     }
     if (e == cudaSuccess && (a.gemm1_weights_scale != h->cached_s1 || a.gemm2_weights_scale != h->cached_s2)) {
         // new scale tensors: lay them out for the GEMMs' promotion (stream-ordered in front of the chain)
-        e = launch_repack_weight_scales(a.gemm1_weights_scale, a.gemm2_weights_scale, h->sw1_packed, h->sw2_packed, E, stream);
+        e = launch_repack_weight_scales(a.gemm1_weights_scale, a.gemm2_weights_scale, h->sw1_packed, h->sw2_packed, E, h->geo,
+                                        stream);
         if (e == cudaSuccess) { h->cached_s1 = a.gemm1_weights_scale; h->cached_s2 = a.gemm2_weights_scale; }
     }
     mark(0);
@@ -288,7 +305,7 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
     const int stop = h->opt_stop_after > 0 ? h->opt_stop_after : 99;
     // decode-sized batches may leave most SMs without a tile: there the split-K instantiation
     // (chosen here from T alone, it decides on the device whether to split) spreads the K range
-    const int split_k = T <= 4 ? 1 : 0;   // 4 = kSplitKMaxRows of the GEMM kernel
+    const int split_k = (T <= 4 && ref_geo) ? 1 : 0;   // 4 = kSplitKMaxRows of the GEMM kernel
     // one persistent CTA per SM; CTAs without work leave at once, spare ones take split-K units
     auto ctas = [&](int) { return h->num_sms; };
     if (e == cudaSuccess && stop >= 2) e = launch_permute(a.hidden_states, a.hidden_states_scale, h->ws, T, stream);
@@ -380,13 +397,53 @@ int moe_fp8_b200_reference_policy(int num_tokens, int32_t out_flags[5], float ou
     return MOE_FP8_B200_OK;
 }
 
+namespace {
+// NULL = the reference's shape.  Returns NULL when the shape is usable, else what is wrong with it.
+const char* check_shape(const moe_fp8_b200_shape* sh, moe_fp8_b200_shape& out)
+{
+    out = {kHidden, kInter, kTopK, kNumGroups, kTopKGroup};
+    if (!sh) return nullptr;
+    out = *sh;
+    if (out.hidden < 256 || out.hidden > 8192 || out.hidden % 256 != 0) return "hidden must be a multiple of 256 in [256, 8192]";
+    if (out.intermediate < 128 || out.intermediate > 8192 || out.intermediate % 128 != 0)
+        return "intermediate must be a multiple of 128 in [128, 8192]";
+    if (out.top_k < 1 || out.top_k > kTopK) return "top_k must be in [1, 8]";
+    if (out.n_group != 1 && out.n_group != 2 && out.n_group != 4 && out.n_group != 8) return "n_group must be 1, 2, 4 or 8";
+    if (out.topk_group < 1 || out.topk_group > out.n_group) return "topk_group must be in [1, n_group]";
+    if (out.topk_group * (kNumExperts / out.n_group) < out.top_k) return "the kept groups hold fewer than top_k experts";
+    return nullptr;
+}
+}  // namespace
+
+size_t moe_fp8_b200_workspace_bytes_shaped(int max_tokens, int num_local_experts, const moe_fp8_b200_shape* shape)
+{
+    moe_fp8_b200_shape sh;
+    if (max_tokens <= 0 || num_local_experts <= 0 || num_local_experts > kMaxLocalExperts || check_shape(shape, sh)) return 0;
+    return make_layout(max_tokens, num_local_experts, Geometry{sh.hidden, sh.intermediate}).total;
+}
+
+int moe_fp8_b200_get_shape(moe_fp8_b200_handle h, moe_fp8_b200_shape* out)
+{
+    if (!h || !out) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
+    *out = {h->geo.hidden, h->geo.inter, h->top_k, h->n_group, h->topk_group};
+    return MOE_FP8_B200_OK;
+}
+
 int moe_fp8_b200_create(moe_fp8_b200_handle* out, int device, int max_tokens, int num_local_experts)
+{
+    return moe_fp8_b200_create_shaped(out, device, max_tokens, num_local_experts, nullptr);
+}
+
+int moe_fp8_b200_create_shaped(moe_fp8_b200_handle* out, int device, int max_tokens, int num_local_experts,
+                               const moe_fp8_b200_shape* shape)
 {
     if (!out) return fail(nullptr, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "out is NULL");
     *out = nullptr;
     if (max_tokens <= 0) return fail(nullptr, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "max_tokens must be positive");
     if (num_local_experts != 32 && num_local_experts != 64 && num_local_experts != 128 && num_local_experts != 256)
         return fail(nullptr, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "num_local_experts must be 32, 64, 128 or 256");
+    moe_fp8_b200_shape sh;
+    if (const char* why = check_shape(shape, sh)) return fail(nullptr, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "shape: %s", why);
     cudaError_t e = cudaSetDevice(device);
     if (e != cudaSuccess)
         return fail(nullptr, MOE_FP8_B200_ERR_CUDA, "cudaSetDevice(%d): %s", device, cudaGetErrorString(e));
@@ -404,7 +461,11 @@ int moe_fp8_b200_create(moe_fp8_b200_handle* out, int device, int max_tokens, in
     h->num_local_experts = num_local_experts;
     h->num_sms = prop.multiProcessorCount;
     h->decode_ctas_per_sm = decode_max_ctas_per_sm();
-    h->layout = make_layout(max_tokens, num_local_experts);
+    h->geo = Geometry{sh.hidden, sh.intermediate};
+    h->top_k = sh.top_k;
+    h->n_group = sh.n_group;
+    h->topk_group = sh.topk_group;
+    h->layout = make_layout(max_tokens, num_local_experts, h->geo);
     e = cudaMalloc(&h->base, h->layout.total);
     if (e != cudaSuccess) {
         const int rc = fail(nullptr, MOE_FP8_B200_ERR_CUDA, "cudaMalloc(%zu): %s", h->layout.total, cudaGetErrorString(e));
@@ -434,6 +495,7 @@ int moe_fp8_b200_create(moe_fp8_b200_handle* out, int device, int max_tokens, in
     h->sw2_packed = reinterpret_cast<float*>(h->base + L.sw2_packed);
     w.m_cap = L.m_cap;
     w.max_tiles = L.max_tiles;
+    w.geo = h->geo;
     // Small control arrays start defined; the large row buffers are written before use.
     e = cudaMemset(h->base, 0, L.topk_idx);
     if (e == cudaSuccess) e = cudaMemset(w.row_token, 0xff, sizeof(int) * (size_t)L.m_cap);
@@ -441,9 +503,9 @@ int moe_fp8_b200_create(moe_fp8_b200_handle* out, int device, int max_tokens, in
     int mr = 0;
     if (e == cudaSuccess) {
         if (tensor_map_bytes() > sizeof(h->tmap_a1)) mr = -100;
-        if (mr == 0) mr = encode_kmajor_u8_map(h->tmap_a1, w.a1, kHidden, L.m_cap, 0, kTileM);
-        if (mr == 0) mr = encode_kmajor_u8_map(h->tmap_a2, w.a2, kInter, L.m_cap, 0, kTileM);
-        if (mr == 0) mr = encode_out_bf16_map(h->tmap_y, w.y, kHidden, L.m_cap);
+        if (mr == 0) mr = encode_kmajor_u8_map(h->tmap_a1, w.a1, h->geo.hidden, L.m_cap, 0, kTileM);
+        if (mr == 0) mr = encode_kmajor_u8_map(h->tmap_a2, w.a2, h->geo.inter, L.m_cap, 0, kTileM);
+        if (mr == 0) mr = encode_out_bf16_map(h->tmap_y, w.y, h->geo.hidden, L.m_cap);
     }
     if (e != cudaSuccess || mr != 0) {
         const int rc = (e != cudaSuccess)
@@ -596,7 +658,7 @@ int moe_fp8_b200_quantize_hidden(moe_fp8_b200_handle h, const void* x, int num_t
     if (!x || !q || !scale) return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "a tensor pointer is NULL");
     if (((uintptr_t)x & 15u) || ((uintptr_t)q & 15u) || ((uintptr_t)scale & 3u))
         return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "x and q must be 16-byte aligned");
-    const cudaError_t e = launch_quantize_rows(x, q, scale, num_tokens, static_cast<cudaStream_t>(stream));
+    const cudaError_t e = launch_quantize_rows(x, q, scale, num_tokens, h->geo.hidden, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "quantize launch failed: %s", cudaGetErrorString(e));
     return MOE_FP8_B200_OK;
 }
@@ -671,9 +733,10 @@ int moe_fp8_b200_run_host(moe_fp8_b200_handle h, const moe_fp8_b200_args* args, 
     // staging sized once, on the first call, for the handle's max_tokens: no later call allocates or frees
     const size_t Tm = (size_t)h->max_tokens;
     const size_t b_logits = align_up(sizeof(float) * Tm * kNumExperts, 256);
-    const size_t b_hidden = align_up(Tm * kHidden, 256);
-    const size_t b_scale = align_up(sizeof(float) * (size_t)kHiddenBlocks * Tm, 256);
-    const size_t b_out = align_up(sizeof(__nv_bfloat16) * Tm * kHidden, 256);
+    const size_t hidden = (size_t)h->geo.hidden, hidden_blocks = hidden / kBlock;
+    const size_t b_hidden = align_up(Tm * hidden, 256);
+    const size_t b_scale = align_up(sizeof(float) * hidden_blocks * Tm, 256);
+    const size_t b_out = align_up(sizeof(__nv_bfloat16) * Tm * hidden, 256);
     if (!h->stage) {
         const size_t need = b_logits + b_hidden + b_scale + b_out;
         const cudaError_t e = cudaMalloc(&h->stage, need);
@@ -690,9 +753,9 @@ int moe_fp8_b200_run_host(moe_fp8_b200_handle h, const moe_fp8_b200_args* args, 
     cudaError_t e = cudaMemcpyAsync(d_logits, args->routing_logits, sizeof(float) * (size_t)T * kNumExperts,
                                     cudaMemcpyHostToDevice, stream);
     if (e == cudaSuccess)
-        e = cudaMemcpyAsync(d_hidden, args->hidden_states, (size_t)T * kHidden, cudaMemcpyHostToDevice, stream);
+        e = cudaMemcpyAsync(d_hidden, args->hidden_states, (size_t)T * hidden, cudaMemcpyHostToDevice, stream);
     if (e == cudaSuccess)
-        e = cudaMemcpyAsync(d_scale, args->hidden_states_scale, sizeof(float) * (size_t)kHiddenBlocks * T,
+        e = cudaMemcpyAsync(d_scale, args->hidden_states_scale, sizeof(float) * hidden_blocks * T,
                             cudaMemcpyHostToDevice, stream);
     if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "host-to-device copy: %s", cudaGetErrorString(e));
     moe_fp8_b200_args dev = *args;
@@ -702,7 +765,7 @@ int moe_fp8_b200_run_host(moe_fp8_b200_handle h, const moe_fp8_b200_args* args, 
     dev.output = d_out;
     const int rc = enqueue_layer(h, dev, stream);
     if (rc != MOE_FP8_B200_OK) return rc;
-    e = cudaMemcpyAsync(args->output, d_out, sizeof(__nv_bfloat16) * (size_t)T * kHidden, cudaMemcpyDeviceToHost, stream);
+    e = cudaMemcpyAsync(args->output, d_out, sizeof(__nv_bfloat16) * (size_t)T * hidden, cudaMemcpyDeviceToHost, stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "device-to-host copy: %s", cudaGetErrorString(e));
     return MOE_FP8_B200_OK;
@@ -728,9 +791,10 @@ int moe_fp8_b200_run_host_async(moe_fp8_b200_handle h, const moe_fp8_b200_args* 
     }
     const size_t Tm = (size_t)h->max_tokens;
     const size_t b_logits = align_up(sizeof(float) * Tm * kNumExperts, 256);
-    const size_t b_hidden = align_up(Tm * kHidden, 256);
-    const size_t b_scale = align_up(sizeof(float) * (size_t)kHiddenBlocks * Tm, 256);
-    const size_t b_out = align_up(sizeof(__nv_bfloat16) * Tm * kHidden, 256);
+    const size_t hidden = (size_t)h->geo.hidden, hidden_blocks = hidden / kBlock;
+    const size_t b_hidden = align_up(Tm * hidden, 256);
+    const size_t b_scale = align_up(sizeof(float) * hidden_blocks * Tm, 256);
+    const size_t b_out = align_up(sizeof(__nv_bfloat16) * Tm * hidden, 256);
     if (!h->pipe_stage[0]) {   // sized once for max_tokens: no allocation between pipelined calls
         const size_t need = b_logits + b_hidden + b_scale + b_out;
         for (int i = 0; i < 2 && e == cudaSuccess; ++i) e = cudaMalloc(&h->pipe_stage[i], need);
@@ -762,9 +826,9 @@ int moe_fp8_b200_run_host_async(moe_fp8_b200_handle h, const moe_fp8_b200_args* 
     if (seq >= 2) e = cudaStreamWaitEvent(h->pipe_in, h->pipe_compute_done[set], 0);
     if (e == cudaSuccess)
         e = cudaMemcpyAsync(d_logits, args->routing_logits, sizeof(float) * (size_t)T * kNumExperts, cudaMemcpyHostToDevice, h->pipe_in);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(d_hidden, args->hidden_states, (size_t)T * kHidden, cudaMemcpyHostToDevice, h->pipe_in);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_hidden, args->hidden_states, (size_t)T * hidden, cudaMemcpyHostToDevice, h->pipe_in);
     if (e == cudaSuccess)
-        e = cudaMemcpyAsync(d_scale, args->hidden_states_scale, sizeof(float) * (size_t)kHiddenBlocks * T, cudaMemcpyHostToDevice, h->pipe_in);
+        e = cudaMemcpyAsync(d_scale, args->hidden_states_scale, sizeof(float) * hidden_blocks * T, cudaMemcpyHostToDevice, h->pipe_in);
     if (e == cudaSuccess) e = cudaEventRecord(h->pipe_in_done[set], h->pipe_in);
     // compute: needs the inputs, and the set's output buffer must have been copied out (two calls ago)
     if (e == cudaSuccess) e = cudaStreamWaitEvent(stream, h->pipe_in_done[set], 0);
@@ -781,7 +845,7 @@ int moe_fp8_b200_run_host_async(moe_fp8_b200_handle h, const moe_fp8_b200_args* 
     // copy-out
     if (e == cudaSuccess) e = cudaStreamWaitEvent(h->pipe_out, h->pipe_compute_done[set], 0);
     if (e == cudaSuccess)
-        e = cudaMemcpyAsync(args->output, d_out, sizeof(__nv_bfloat16) * (size_t)T * kHidden, cudaMemcpyDeviceToHost, h->pipe_out);
+        e = cudaMemcpyAsync(args->output, d_out, sizeof(__nv_bfloat16) * (size_t)T * hidden, cudaMemcpyDeviceToHost, h->pipe_out);
     if (e == cudaSuccess) e = cudaEventRecord(h->pipe_out_done[set], h->pipe_out);
     if (e != cudaSuccess) return fail(h, MOE_FP8_B200_ERR_CUDA, "pipeline copy-out: %s", cudaGetErrorString(e));
     *ticket = seq;
@@ -938,11 +1002,11 @@ int moe_fp8_b200_read_intermediate(moe_fp8_b200_handle h, int buffer, void* dst,
         case MOE_FP8_B200_BUF_PAIR_WEIGHT: src = w.pair_weight; size = sizeof(float) * T * kTopK; break;
         case MOE_FP8_B200_BUF_NUM_TILES: src = w.num_tiles; size = sizeof(int); break;
         case MOE_FP8_B200_BUF_ROW_TOKEN: src = w.row_token; size = sizeof(int) * M; break;
-        case MOE_FP8_B200_BUF_A1: src = w.a1; size = M * kHidden; break;
-        case MOE_FP8_B200_BUF_SFA1: src = w.sfa1; size = sizeof(float) * kHiddenBlocks * M; break;
-        case MOE_FP8_B200_BUF_A2: src = w.a2; size = M * kInter; break;
-        case MOE_FP8_B200_BUF_SFA2: src = w.sfa2; size = sizeof(float) * kInterBlocks * M; break;
-        case MOE_FP8_B200_BUF_Y: src = w.y; size = sizeof(__nv_bfloat16) * M * kHidden; break;
+        case MOE_FP8_B200_BUF_A1: src = w.a1; size = M * w.geo.hidden; break;
+        case MOE_FP8_B200_BUF_SFA1: src = w.sfa1; size = sizeof(float) * (w.geo.hidden / kBlock) * M; break;
+        case MOE_FP8_B200_BUF_A2: src = w.a2; size = M * w.geo.inter; break;
+        case MOE_FP8_B200_BUF_SFA2: src = w.sfa2; size = sizeof(float) * (w.geo.inter / kBlock) * M; break;
+        case MOE_FP8_B200_BUF_Y: src = w.y; size = sizeof(__nv_bfloat16) * M * w.geo.hidden; break;
         case MOE_FP8_B200_BUF_STATUS: src = &w.ctrl->status; size = sizeof(int) * 2; break;
         case MOE_FP8_B200_BUF_DECODE_TIMELINE: src = w.ctrl->dec_time; size = sizeof(w.ctrl->dec_time); break;
         case MOE_FP8_B200_BUF_EXCHANGE_TIMELINE: src = w.ctrl->xch_time; size = sizeof(w.ctrl->xch_time); break;

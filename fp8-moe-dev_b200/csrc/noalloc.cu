@@ -130,6 +130,7 @@ extern "C" int moe_fp8_b200_route_noalloc(const float* routing_logits, const voi
 
     Workspace ws;
     std::memset(&ws, 0, sizeof ws);
+    ws.geo = Geometry{kHidden, kInter};
     ws.ctrl = reinterpret_cast<Control*>(scratch);
     ws.pair_count = reinterpret_cast<int*>(scratch + kCtrlBytes);
     ws.pair_code = reinterpret_cast<uint32_t*>(scratch + kCtrlBytes + kPairCountBytes);

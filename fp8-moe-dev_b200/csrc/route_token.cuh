@@ -207,4 +207,99 @@ __device__ __forceinline__ void route_token_warp(const float* __restrict__ logit
 
 }
 
+// The same selection for other routing constants (FlashInfer's definition of the layer carries top_k,
+// n_group and topk_group as axes; the reference compiles 8 / 8 / 4 in): n_group in {1, 2, 4, 8} groups of
+// 256 / n_group experts -- a group is 8 / n_group of the warp's 32-expert slices -- scored by the sum of
+// their two largest biased scores, topk_group groups kept, top_k <= 8 argmax rounds with the tie order of
+// the routine above, weights normalised over the top_k picks.  Entries past top_k come back as expert -1
+// with weight 0, which no dispatch takes for a local expert.
+__device__ __forceinline__ void route_token_warp_generic(const float* __restrict__ logits_row,
+                                                         const __nv_bfloat16* __restrict__ bias, int lane,
+                                                         int (&idx)[kTopK], float (&wn)[kTopK], int n_group,
+                                                         int topk_group, int top_k)
+{
+    constexpr uint32_t kFull = 0xffffffffu;
+    float s[kNumGroups], sb[kNumGroups];
+    uint32_t k1[kNumGroups], k2[kNumGroups];   // the two largest keys of each 32-expert slice (duplicates count)
+#pragma unroll
+    for (int w = 0; w < kNumGroups; ++w) {
+        const float l = logits_row[w * 32 + lane];
+        const float sig = 1.0f / (1.0f + __expf(-l));
+        s[w] = sig;
+        sb[w] = sig + __bfloat162float(bias[w * 32 + lane]);
+        const uint32_t key = float_to_ordered(sb[w]);
+        k1[w] = __reduce_max_sync(kFull, key);
+        const uint32_t holders = __ballot_sync(kFull, key == k1[w]);
+        k2[w] = (__popc(holders) >= 2) ? k1[w] : __reduce_max_sync(kFull, (key == k1[w]) ? 0u : key);
+    }
+    const int per = kNumGroups / n_group;   // slices per group
+    float gscore[kNumGroups];
+#pragma unroll
+    for (int g = 0; g < kNumGroups; ++g) {
+        uint32_t a = 0u, b = 0u;
+#pragma unroll
+        for (int w = 0; w < kNumGroups; ++w) {
+            if (g < n_group && w / per == g) {
+                const uint32_t t1 = a >= k1[w] ? a : k1[w];
+                const uint32_t t2 = a >= k1[w] ? (b >= k1[w] ? b : k1[w]) : (a >= k2[w] ? a : k2[w]);
+                a = t1;
+                b = t2;
+            }
+        }
+        gscore[g] = (g < n_group) ? ordered_to_float(a) + ordered_to_float(b) : kNegSentinel;
+    }
+    uint32_t kept_mask = 0;
+    for (int k = 0; k < topk_group; ++k) {
+        float best = kNegSentinel;
+        int best_i = -1;
+#pragma unroll
+        for (int i = 0; i < kNumGroups; ++i) {
+            if (i < n_group && !((kept_mask >> i) & 1u) && gscore[i] > best) { best = gscore[i]; best_i = i; }
+        }
+        if (best_i >= 0) kept_mask |= 1u << best_i;
+    }
+#pragma unroll
+    for (int w = 0; w < kNumGroups; ++w) {
+        if (!((kept_mask >> (w / per)) & 1u)) sb[w] = kNegSentinel;
+    }
+    const uint32_t lane_rev = __brev((uint32_t)lane) >> 27;
+    float sel[kTopK];
+#pragma unroll
+    for (int k = 0; k < kTopK; ++k) {
+        if (k < top_k) {
+            float bv = sb[0];
+            int bw = 0;
+#pragma unroll
+            for (int w = 1; w < kNumGroups; ++w) {
+                if (sb[w] > bv) { bv = sb[w]; bw = w; }
+            }
+            const uint32_t key = float_to_ordered(bv);
+            const uint32_t kmax = __reduce_max_sync(kFull, key);
+            const uint32_t my_rank = (key == kmax) ? ((uint32_t)bw * 32u + lane_rev) : 0xffffffffu;
+            const uint32_t win_rank = __reduce_min_sync(kFull, my_rank);
+            const int win_w = (int)(win_rank >> 5);
+            const int win_lane = (int)(__brev(win_rank & 31u) >> 27);
+            float s_mine = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kNumGroups; ++w) {
+                if (w == win_w) {
+                    s_mine = s[w];
+                    if (lane == win_lane) sb[w] = kNegSentinel;
+                }
+            }
+            sel[k] = __shfl_sync(kFull, s_mine, win_lane);
+            idx[k] = win_w * 32 + win_lane;
+        } else {
+            sel[k] = 0.0f;
+            idx[k] = -1;
+        }
+    }
+    float sumw = 1e-20f;
+#pragma unroll
+    for (int k = 0; k < kTopK; ++k) sumw += sel[k];
+    const float inv = 1.0f / sumw;
+#pragma unroll
+    for (int k = 0; k < kTopK; ++k) wn[k] = sel[k] * inv;
+}
+
 }  // namespace moe

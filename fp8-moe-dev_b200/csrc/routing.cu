@@ -66,6 +66,9 @@ __device__ __forceinline__ void scan_tiles_block(const Workspace& ws, int num_lo
 
 constexpr int kRouteWarps = 8;
 
+// GENERIC_ROUTE: the routing constants come from the policy record (top_k, n_group, topk_group) instead of
+// the reference's 8 / 8 / 4.
+template <bool GENERIC_ROUTE>
 __global__ void __launch_bounds__(kRouteWarps * 32) route_dispatch_kernel(
     const float* __restrict__ logits, const __nv_bfloat16* __restrict__ bias, Workspace ws, int T,
     int local_expert_offset, int num_local_experts, float rsf, DispatchPolicy pol, int do_scan)
@@ -95,7 +98,10 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_dispatch_kernel(
 
     int idx[kTopK];
     float wn[kTopK];
-    route_token_warp(logits + (size_t)t * kNumExperts, bias, lane, idx, wn);
+    if (GENERIC_ROUTE)
+        route_token_warp_generic(logits + (size_t)t * kNumExperts, bias, lane, idx, wn, pol.n_group, pol.topk_group, pol.top_k);
+    else
+        route_token_warp(logits + (size_t)t * kNumExperts, bias, lane, idx, wn);
 
     if (lane < kTopK) {
         int my_idx = 0;
@@ -231,6 +237,35 @@ __global__ void __launch_bounds__(kPermuteWarps * 32) permute_rows_kernel(
     }
 }
 
+// The same movement for a run-time row length (Workspace::geo.hidden, a multiple of 256 bytes): the row
+// is re-read per packed row it goes to (it sits in L1 after the first pass).
+__global__ void __launch_bounds__(kPermuteWarps * 32) permute_rows_generic_kernel(
+    const uint8_t* __restrict__ hidden, const float* __restrict__ hidden_scale, Workspace ws, int T)
+{
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * kPermuteWarps + (threadIdx.x >> 5);
+    pdl_launch_dependents();
+    pdl_wait();
+    if (t >= T) return;
+    if (ws.num_tiles[0] == 0) return;
+    const int n_pairs = ws.pair_count[t];
+    if (n_pairs == 0) return;
+    const int H = ws.geo.hidden;
+    const int vecs = H / 16, blocks = H / kBlock;   // <= 512 uint4, <= 64 scales
+    const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)t * H);
+    const float sc0 = (lane < blocks) ? __ldg(hidden_scale + (size_t)lane * T + t) : 0.0f;
+    const float sc1 = (lane + 32 < blocks) ? __ldg(hidden_scale + (size_t)(lane + 32) * T + t) : 0.0f;
+    for (int p = 0; p < n_pairs; ++p) {
+        const uint32_t code = ws.pair_code[(size_t)t * kTopK + p];
+        const int row = ws.expert_offset[code >> 24] + (int)(code & 0x00ffffffu);
+        uint4* dst = reinterpret_cast<uint4*>(ws.a1 + (size_t)row * H);
+        for (int i = lane; i < vecs; i += 32) dst[i] = __ldg(src + i);
+        if (lane < blocks) ws.sfa1[(size_t)lane * ws.m_cap + row] = sc0;
+        if (lane + 32 < blocks) ws.sfa1[(size_t)(lane + 32) * ws.m_cap + row] = sc1;
+        if (lane == 0) ws.row_token[row] = t;
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // Combine.  out[t, :] = bf16( sum_p float(Y[row_p, :]) * w_p ) with the pairs taken in
 // dispatch order and fp32 accumulation; tokens without a local expert get zeros.  Same
@@ -280,6 +315,42 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(Workspace ws, 
     }
 }
 
+// Run-time row length: a thread walks 8-column chunks, each summed over the pairs in the same order.
+__global__ void __launch_bounds__(256) combine_generic_kernel(Workspace ws, __nv_bfloat16* __restrict__ out, int T)
+{
+    const int t = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (t >= T) return;
+    int n_pairs = ws.pair_count[t];
+    if (ws.num_tiles[0] == 0) n_pairs = 0;
+    const int H = ws.geo.hidden;
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)t * H);
+    for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+        for (int p = 0; p < n_pairs; ++p) {
+            const uint32_t code = ws.pair_code[(size_t)t * kTopK + p];
+            const float w = ws.pair_weight[(size_t)t * kTopK + p];
+            const int row = ws.expert_offset[code >> 24] + (int)(code & 0x00ffffffu);
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(ws.y + (size_t)row * H) + v);
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(h2[j]);
+                acc[2 * j] += f.x * w;
+                acc[2 * j + 1] += f.y * w;
+            }
+        }
+        uint4 packed;
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        dst[v] = packed;
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // Launchers (called by the C-ABI layer).  All launches carry the programmatic stream
 // serialization attribute (see ptx.cuh).
@@ -306,7 +377,11 @@ cudaError_t launch_route_dispatch(const float* logits, const void* bias, const W
                                   const DispatchPolicy& pol, int do_scan, cudaStream_t stream)
 {
     const int grid = (T + kRouteWarps - 1) / kRouteWarps;
-    return launch_pdl(route_dispatch_kernel, dim3(grid), dim3(kRouteWarps * 32), 0, stream, logits,
+    if (pol.top_k != 0)
+        return launch_pdl(route_dispatch_kernel<true>, dim3(grid), dim3(kRouteWarps * 32), 0, stream, logits,
+                          static_cast<const __nv_bfloat16*>(bias), ws, T, local_expert_offset, num_local_experts, rsf, pol,
+                          do_scan);
+    return launch_pdl(route_dispatch_kernel<false>, dim3(grid), dim3(kRouteWarps * 32), 0, stream, logits,
                       static_cast<const __nv_bfloat16*>(bias), ws, T, local_expert_offset, num_local_experts, rsf, pol,
                       do_scan);
 }
@@ -315,12 +390,17 @@ cudaError_t launch_permute(const void* hidden, const float* hidden_scale, const 
                            cudaStream_t stream)
 {
     const int grid = (T + kPermuteWarps - 1) / kPermuteWarps;
+    if (!ws.geo.is_reference())
+        return launch_pdl(permute_rows_generic_kernel, dim3(grid), dim3(kPermuteWarps * 32), 0, stream,
+                          static_cast<const uint8_t*>(hidden), hidden_scale, ws, T);
     return launch_pdl(permute_rows_kernel, dim3(grid), dim3(kPermuteWarps * 32), 0, stream,
                       static_cast<const uint8_t*>(hidden), hidden_scale, ws, T);
 }
 
 cudaError_t launch_combine(const Workspace& ws, void* out, int T, cudaStream_t stream)
 {
+    if (!ws.geo.is_reference())
+        return launch_pdl(combine_generic_kernel, dim3(T), dim3(256), 0, stream, ws, static_cast<__nv_bfloat16*>(out), T);
     return launch_pdl(combine_kernel, dim3(T), dim3(kCombineThreads), 0, stream, ws, static_cast<__nv_bfloat16*>(out),
                       T);
 }

@@ -79,34 +79,35 @@ def make_routing(T: int, seed: int = 0, skew: bool = False, device="cpu", skew_s
     return logits.contiguous(), bias.contiguous()
 
 
-def make_hidden(T: int, seed: int = 1, device="cpu"):
+def make_hidden(T: int, seed: int = 1, device="cpu", hidden: int = H):
     g = _gen(device, seed)
-    x = g.randn(T, H).to(torch.bfloat16)
+    x = g.randn(T, hidden).to(torch.bfloat16)
     return quantize_rows_1x128(x)
 
 
-def make_expert(e_global: int, base_seed: int = 1000, device="cpu"):
-    """(w1 e4m3 [4096,7168], s1 [32,56], w2 e4m3 [7168,2048], s2 [56,16]) of one global expert."""
+def make_expert(e_global: int, base_seed: int = 1000, device="cpu", hidden: int = H, inter: int = I):
+    """(w1 e4m3 [4096,7168], s1 [32,56], w2 e4m3 [7168,2048], s2 [56,16]) of one global expert; with other
+    `hidden` / `inter`: [2*inter, hidden], [2*inter/128, hidden/128], [hidden, inter], [hidden/128, inter/128]."""
     g = _gen(device, base_seed + int(e_global))
-    w1 = 0.02 * g.randn(N1, H)
+    w1 = 0.02 * g.randn(2 * inter, hidden)
     q1, s1 = quantize_blocks_128x128(w1)
     del w1
-    w2 = 0.02 * g.randn(H, I)
+    w2 = 0.02 * g.randn(hidden, inter)
     q2, s2 = quantize_blocks_128x128(w2)
     return q1, s1, q2, s2
 
 
 def make_shard(local_expert_offset: int, num_local_experts: int, base_seed: int = 1000, device="cpu",
-               out_device=None):
+               out_device=None, hidden: int = H, inter: int = I):
     """Stacked weights of experts [offset, offset + E)."""
     out_device = out_device or device
     E = num_local_experts
-    w1 = torch.empty(E, N1, H, dtype=torch.float8_e4m3fn, device=out_device)
-    s1 = torch.empty(E, N1 // BLK, H // BLK, dtype=torch.float32, device=out_device)
-    w2 = torch.empty(E, H, I, dtype=torch.float8_e4m3fn, device=out_device)
-    s2 = torch.empty(E, H // BLK, I // BLK, dtype=torch.float32, device=out_device)
+    w1 = torch.empty(E, 2 * inter, hidden, dtype=torch.float8_e4m3fn, device=out_device)
+    s1 = torch.empty(E, 2 * inter // BLK, hidden // BLK, dtype=torch.float32, device=out_device)
+    w2 = torch.empty(E, hidden, inter, dtype=torch.float8_e4m3fn, device=out_device)
+    s2 = torch.empty(E, hidden // BLK, inter // BLK, dtype=torch.float32, device=out_device)
     for i in range(E):
-        q1, a1, q2, a2 = make_expert(local_expert_offset + i, base_seed, device)
+        q1, a1, q2, a2 = make_expert(local_expert_offset + i, base_seed, device, hidden, inter)
         w1[i].copy_(q1)
         s1[i].copy_(a1)
         w2[i].copy_(q2)

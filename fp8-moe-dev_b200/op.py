@@ -55,15 +55,22 @@ class MoeLayer:
     """One handle = one GPU's workspace for up to `max_tokens` tokens and `num_local_experts`
     experts (32 per reference shard; 64/128/256 hold several shards on one GPU)."""
 
-    def __init__(self, max_tokens: int, num_local_experts: int = 32, device: Optional[int] = None):
+    def __init__(self, max_tokens: int, num_local_experts: int = 32, device: Optional[int] = None, *,
+                 hidden: int = H, intermediate: int = I, top_k: int = 8, n_group: int = 8, topk_group: int = 4):
+        """The keyword arguments select another shape of the layer (hidden a multiple of 256, intermediate of
+        128, both at most 8192; top_k <= 8; n_group 1, 2, 4 or 8); the defaults are the reference's."""
         self._lib = _lib.load()
         if device is None:
             device = torch.cuda.current_device()
         self.device = int(device)
         self.max_tokens = int(max_tokens)
         self.num_local_experts = int(num_local_experts)
+        self.hidden, self.intermediate = int(hidden), int(intermediate)
+        self.top_k, self.n_group, self.topk_group = int(top_k), int(n_group), int(topk_group)
+        shape = _lib.Shape(self.hidden, self.intermediate, self.top_k, self.n_group, self.topk_group)
         h = C.c_void_p()
-        rc = self._lib.moe_fp8_b200_create(C.byref(h), self.device, self.max_tokens, self.num_local_experts)
+        rc = self._lib.moe_fp8_b200_create_shaped(C.byref(h), self.device, self.max_tokens, self.num_local_experts,
+                                                  C.byref(shape))
         if rc != _lib.OK:
             raise MoeError(rc, self._lib.moe_fp8_b200_last_error(None).decode())
         self._h = h
@@ -174,6 +181,8 @@ class MoeLayer:
         io_dev = torch.device("cpu") if host else dev
         _check_tensor("routing_logits", routing_logits, torch.float32, (T, NE), io_dev)
         _check_tensor("routing_bias", routing_bias, torch.bfloat16, (NE,), dev)
+        H, I = self.hidden, self.intermediate
+        N1 = 2 * I
         _check_tensor("hidden_states", hidden_states, torch.float8_e4m3fn, (T, H), io_dev)
         _check_tensor("hidden_states_scale", hidden_states_scale, torch.float32, (H // 128, T), io_dev)
         _check_tensor("gemm1_weights", gemm1_weights, torch.float8_e4m3fn, (E, N1, H), dev)
@@ -239,6 +248,7 @@ class MoeLayer:
     def quantize_hidden(self, x, q_out=None, scale_out=None, stream: Optional[int] = None):
         """bf16 x [T, 7168] (device) -> (e4m3 [T, 7168], fp32 scales [56, T]): the pair `run` takes."""
         T = int(x.shape[0])
+        H = self.hidden
         dev = torch.device("cuda", self.device)
         _check_tensor("x", x, torch.bfloat16, (T, H), dev)
         if q_out is None:
@@ -274,7 +284,7 @@ class MoeLayer:
             self._raise(rc)
         E, cap = self.num_local_experts, int(v.row_capacity)
         return dict(
-            y=_device_view(v.y, (cap, H), "<i2", self.device).view(torch.bfloat16),
+            y=_device_view(v.y, (cap, self.hidden), "<i2", self.device).view(torch.bfloat16),
             expert_offset=_device_view(v.expert_offset, (E + 1,), "<i4", self.device),
             pair_count=_device_view(v.pair_count, (T,), "<i4", self.device),
             pair_code=_device_view(v.pair_code, (T, 8), "<i4", self.device),
@@ -282,7 +292,7 @@ class MoeLayer:
 
     def finalize(self, num_tokens: int, output, stream: Optional[int] = None):
         """The weighted combine of the latest unfinalized run into bf16 `output` [T, 7168]."""
-        _check_tensor("output", output, torch.bfloat16, (int(num_tokens), H), torch.device("cuda", self.device))
+        _check_tensor("output", output, torch.bfloat16, (int(num_tokens), self.hidden), torch.device("cuda", self.device))
         if stream is None:
             stream = torch.cuda.current_stream(self.device).cuda_stream
         rc = self._lib.moe_fp8_b200_finalize(self._h, int(num_tokens), output.data_ptr(), C.c_void_p(stream))

@@ -142,6 +142,31 @@ MOE_FP8_B200_API int moe_fp8_b200_row_capacity(int max_tokens, int num_local_exp
  * Workspace of kernel/moe_fp8.cu:2349-2461, 2677-2689. */
 MOE_FP8_B200_API int moe_fp8_b200_create(moe_fp8_b200_handle* out, int device, int max_tokens, int num_local_experts);
 
+/* Other shapes of the same layer.  The reference compiles hidden 7168 / intermediate 2048 and the routing
+ * constants 8 / 8 / 4 in (kernel/moe_fp8.cu:301-304); FlashInfer's definition of the operator carries them
+ * as axes.  A handle made here runs the five-kernel chain with those values at run time:
+ *   hidden        multiple of 256, 256 .. 8192     tensors [T, hidden], scales [hidden/128, T]
+ *   intermediate  multiple of 128, 128 .. 8192     W1 [E, 2*intermediate, hidden], W2 [E, hidden, intermediate]
+ *   top_k         1 .. 8                            experts per token; table rows keep 8 entries, the unused ones
+ *                                                   hold expert -1 and weight 0
+ *   n_group       1, 2, 4 or 8                      routing groups of 256 / n_group experts
+ *   topk_group    1 .. n_group, with topk_group * (256 / n_group) >= top_k
+ * The number of global experts stays 256.  shape == NULL, or the reference's values, gives exactly the
+ * handle of moe_fp8_b200_create.  With another hidden or intermediate size the single-kernel decode path,
+ * the split-K GEMMs, moe_fp8_b200_run_reduce_scatter and moe_fp8_b200_route_noalloc are not available
+ * (MOE_FP8_B200_ERR_UNSUPPORTED where they are asked for explicitly, the chain otherwise). */
+typedef struct moe_fp8_b200_shape {
+    int32_t hidden, intermediate;
+    int32_t top_k, n_group, topk_group;
+} moe_fp8_b200_shape;
+MOE_FP8_B200_API int moe_fp8_b200_create_shaped(moe_fp8_b200_handle* out, int device, int max_tokens, int num_local_experts,
+                                                const moe_fp8_b200_shape* shape);
+/* Workspace bytes of such a handle (0 for a shape that create_shaped refuses). */
+MOE_FP8_B200_API size_t moe_fp8_b200_workspace_bytes_shaped(int max_tokens, int num_local_experts,
+                                                            const moe_fp8_b200_shape* shape);
+/* The shape a handle was made with. */
+MOE_FP8_B200_API int moe_fp8_b200_get_shape(moe_fp8_b200_handle h, moe_fp8_b200_shape* out);
+
 MOE_FP8_B200_API int moe_fp8_b200_destroy(moe_fp8_b200_handle h);
 
 /* Text of the last error on this handle (or of the last failed create when h is NULL).

@@ -35,19 +35,30 @@
 #include <omp.h>
 #endif
 
-#define H 7168
-#define I 2048
-#define N1 4096
 #define NE 256
 #define SHARD 32
 #define BLK 128
-#define HB 56
-#define IB 16
-#define TOPK 8
-#define NGROUP 8
-#define KGROUP 4
+#define TOPK 8        /* row length of the routing and pair tables */
+#define MAXGROUP 8
+
+/* Shape of the layer.  The reference compiles these in (kernel/moe_fp8.cu:301-304 and its tensor checks);
+ * oracle_set_shape changes them for the tests of other shapes.  Process-wide, not thread-safe. */
+static int H = 7168, I = 2048, N1 = 4096, HB = 56, IB = 16;
+static int KSEL = 8;      /* top_k: experts selected per token */
+static int NGROUP = 8;    /* routing groups of NE / NGROUP experts */
+static int KGROUP = 4;    /* groups kept */
 
 #define API __attribute__((visibility("default")))
+
+API int oracle_set_shape(int hidden, int inter, int top_k, int n_group, int topk_group) {
+    if (hidden % BLK || inter % BLK || hidden <= 0 || inter <= 0) return -1;
+    if (top_k < 1 || top_k > TOPK) return -1;
+    if (n_group != 1 && n_group != 2 && n_group != 4 && n_group != 8) return -1;
+    if (topk_group < 1 || topk_group > n_group || topk_group * (NE / n_group) < top_k) return -1;
+    H = hidden; I = inter; N1 = 2 * inter; HB = hidden / BLK; IB = inter / BLK;
+    KSEL = top_k; NGROUP = n_group; KGROUP = topk_group;
+    return 0;
+}
 
 /* ------------------------------------------------------------------ number formats */
 static float bf16_to_f32(uint16_t b) {
@@ -140,17 +151,18 @@ static void route_token(const float* logit, const uint16_t* bias, int exact_sigm
         s[e] = sg;
         sb[e] = sg + bf16_to_f32(bias[e]);
     }
-    float gscore[NGROUP];
+    const int gsize = NE / NGROUP;   /* 32 in the reference */
+    float gscore[MAXGROUP];
     for (int g = 0; g < NGROUP; ++g) {
         float top1 = -1e30f, top2 = -1e30f;
-        for (int i = 0; i < SHARD; ++i) {
-            float v = sb[g * SHARD + i];
+        for (int i = 0; i < gsize; ++i) {
+            float v = sb[g * gsize + i];
             if (v > top1) { top2 = top1; top1 = v; }
             else if (v > top2) { top2 = v; }
         }
         gscore[g] = top1 + top2;
     }
-    int kept[NGROUP] = {0};
+    int kept[MAXGROUP] = {0};
     for (int k = 0; k < KGROUP; ++k) {
         float best = -1e30f;
         int bi = -1;
@@ -159,8 +171,9 @@ static void route_token(const float* logit, const uint16_t* bias, int exact_sigm
         if (bi >= 0) kept[bi] = 1;
     }
     for (int e = 0; e < NE; ++e)
-        if (!kept[e / SHARD]) sb[e] = -1e30f;
-    for (int k = 0; k < TOPK; ++k) {
+        if (!kept[e / gsize]) sb[e] = -1e30f;
+    for (int k = KSEL; k < TOPK; ++k) { idx[k] = -1; w[k] = 0.0f; }
+    for (int k = 0; k < KSEL; ++k) {
         float wmax[NE / 32];
         int widx[NE / 32];
         for (int wp = 0; wp < NE / 32; ++wp) {
@@ -189,9 +202,9 @@ static void route_token(const float* logit, const uint16_t* bias, int exact_sigm
         sb[bi] = -1e30f;
     }
     float sumw = 1e-20f;
-    for (int k = 0; k < TOPK; ++k) sumw += s[idx[k]];
+    for (int k = 0; k < KSEL; ++k) sumw += s[idx[k]];
     float inv = 1.0f / sumw;
-    for (int k = 0; k < TOPK; ++k) w[k] = s[idx[k]] * inv;
+    for (int k = 0; k < KSEL; ++k) w[k] = s[idx[k]] * inv;
 }
 
 API void oracle_route(const float* logits, const uint16_t* bias, int T, int* idx, float* w) {
@@ -208,30 +221,32 @@ API void oracle_route_margin(const float* logits, const uint16_t* bias, int T, f
         const float* logit = logits + (size_t)t * NE;
         float sb[NE];
         for (int e = 0; e < NE; ++e) sb[e] = 1.0f / (1.0f + expf(-logit[e])) + bf16_to_f32(bias[e]);
-        float gs[NGROUP];
+        const int gsize = NE / NGROUP;
+        float gs[MAXGROUP];
+        for (int g = 0; g < MAXGROUP; ++g) gs[g] = -1e30f;
         for (int g = 0; g < NGROUP; ++g) {
             float t1 = -1e30f, t2 = -1e30f;
-            for (int i = 0; i < SHARD; ++i) {
-                float v = sb[g * SHARD + i];
+            for (int i = 0; i < gsize; ++i) {
+                float v = sb[g * gsize + i];
                 if (v > t1) { t2 = t1; t1 = v; } else if (v > t2) t2 = v;
             }
             gs[g] = t1 + t2;
         }
-        float sorted[NGROUP];
+        float sorted[MAXGROUP];
         memcpy(sorted, gs, sizeof gs);
         for (int a = 0; a < NGROUP; ++a)
             for (int b = a + 1; b < NGROUP; ++b)
                 if (sorted[b] > sorted[a]) { float x = sorted[a]; sorted[a] = sorted[b]; sorted[b] = x; }
-        float mg = sorted[KGROUP - 1] - sorted[KGROUP];
+        float mg = KGROUP < NGROUP ? sorted[KGROUP - 1] - sorted[KGROUP] : 1e30f;
         float cand[NE];
         int n = 0;
         for (int g = 0; g < NGROUP; ++g)
             if (gs[g] >= sorted[KGROUP - 1])
-                for (int i = 0; i < SHARD; ++i) cand[n++] = sb[g * SHARD + i];
+                for (int i = 0; i < gsize; ++i) cand[n++] = sb[g * gsize + i];
         for (int a = 0; a < n; ++a)
             for (int b = a + 1; b < n; ++b)
                 if (cand[b] > cand[a]) { float x = cand[a]; cand[a] = cand[b]; cand[b] = x; }
-        if (n > TOPK) { float d = cand[TOPK - 1] - cand[TOPK]; if (d < mg) mg = d; }
+        if (n > KSEL) { float d = cand[KSEL - 1] - cand[KSEL]; if (d < mg) mg = d; }
         margin[t] = mg;
     }
 }

@@ -55,6 +55,27 @@ def _c(a, dt):
     return a
 
 
+class shape:
+    """Context manager: the oracle computes another shape of the layer inside the block (the library's
+    setting is process-wide), the reference's 7168 / 2048 / 8 / 8 / 4 outside."""
+
+    def __init__(self, hidden=7168, inter=2048, top_k=8, n_group=8, topk_group=4):
+        self.args = (hidden, inter, top_k, n_group, topk_group)
+
+    def __enter__(self):
+        global H, I, N1
+        if lib().oracle_set_shape(*map(C.c_int, self.args)) != 0:
+            raise ValueError(f"oracle: unusable shape {self.args}")
+        H, I, N1 = self.args[0], self.args[1], 2 * self.args[1]
+        return self
+
+    def __exit__(self, *exc):
+        global H, I, N1
+        lib().oracle_set_shape(*map(C.c_int, (7168, 2048, 8, 8, 4)))
+        H, I, N1 = 7168, 2048, 4096
+        return False
+
+
 def num_threads() -> int:
     return lib().oracle_num_threads()
 

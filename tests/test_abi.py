@@ -94,6 +94,29 @@ def test_create_rejects_bad_arguments(pkg):
     assert b"num_local_experts" in lib.moe_fp8_b200_last_error(None) or lib.moe_fp8_b200_last_error(None)
 
 
+def test_shaped_create_checks_the_shape_before_touching_a_device(pkg):
+    lib = pkg._lib.load()
+    Shape = pkg._lib.Shape
+    h = C.c_void_p()
+    bad = [(7168 + 128, 2048, 8, 8, 4), (0, 2048, 8, 8, 4), (8192 + 256, 2048, 8, 8, 4), (7168, 2048 + 64, 8, 8, 4),
+           (7168, 0, 8, 8, 4), (7168, 2048, 0, 8, 4), (7168, 2048, 9, 8, 4), (7168, 2048, 8, 3, 1),
+           (7168, 2048, 8, 8, 0), (7168, 2048, 8, 8, 9), (7168, 2048, 8, 4, 5)]
+    for sh in bad:
+        rc = lib.moe_fp8_b200_create_shaped(C.byref(h), 0, 16, 32, C.byref(Shape(*sh)))
+        assert rc == pkg._lib.ERR_INVALID_ARGUMENT and not h.value, sh
+        assert b"shape" in lib.moe_fp8_b200_last_error(None)
+        assert lib.moe_fp8_b200_workspace_bytes_shaped(16, 32, C.byref(Shape(*sh))) == 0
+    # one kept group of 32 experts still supplies 8 picks
+    assert lib.moe_fp8_b200_workspace_bytes_shaped(16, 32, C.byref(Shape(7168, 2048, 8, 8, 1))) > 0
+    # NULL and the reference's values size exactly like the plain entry point
+    ref = lib.moe_fp8_b200_workspace_bytes(1024, 32)
+    assert lib.moe_fp8_b200_workspace_bytes_shaped(1024, 32, None) == ref
+    assert lib.moe_fp8_b200_workspace_bytes_shaped(1024, 32, C.byref(Shape(7168, 2048, 8, 8, 4))) == ref
+    small = lib.moe_fp8_b200_workspace_bytes_shaped(1024, 32, C.byref(Shape(1024, 512, 4, 4, 2)))
+    cap = lib.moe_fp8_b200_row_capacity(1024, 32)
+    assert cap * (1024 + 512 + 2048) <= small < ref
+
+
 def test_tvm_ffi_shim_exports_run(pkg):
     shim = ROOT / "fp8-moe-dev_b200" / "libmoe_fp8_b200_tvm.so"
     if not shim.exists():
