@@ -143,7 +143,7 @@ MOE_FP8_B200_API int moe_fp8_b200_row_capacity(int max_tokens, int num_local_exp
 MOE_FP8_B200_API int moe_fp8_b200_create(moe_fp8_b200_handle* out, int device, int max_tokens, int num_local_experts);
 
 /* Other shapes of the same layer.  The reference compiles hidden 7168 / intermediate 2048 and the routing
- * constants 8 / 8 / 4 in (kernel/moe_fp8.cu:301-304); FlashInfer's definition of the operator carries them
+ * constants 8 / 8 / 4 in (kernel/moe_fp8.cu:292-304); FlashInfer's definition of the operator carries them
  * as axes.  A handle made here runs the five-kernel chain with those values at run time:
  *   hidden        multiple of 256, 256 .. 8192     tensors [T, hidden], scales [hidden/128, T]
  *   intermediate  multiple of 128, 128 .. 8192     W1 [E, 2*intermediate, hidden], W2 [E, hidden, intermediate]

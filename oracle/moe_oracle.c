@@ -41,7 +41,7 @@
 #define TOPK 8        /* row length of the routing and pair tables */
 #define MAXGROUP 8
 
-/* Shape of the layer.  The reference compiles these in (kernel/moe_fp8.cu:301-304 and its tensor checks);
+/* Shape of the layer.  The reference compiles these in (kernel/moe_fp8.cu:292-304);
  * oracle_set_shape changes them for the tests of other shapes.  Process-wide, not thread-safe. */
 static int H = 7168, I = 2048, N1 = 4096, HB = 56, IB = 16;
 static int KSEL = 8;      /* top_k: experts selected per token */
