@@ -347,12 +347,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                     // probed while the previous block's MMAs ran (next_full_ready), which keeps
                     // that probe's latency off the release -> issue chain below.
                     if (!next_full_ready && !mbar_wait(smem_u32(&sh->full[s]), ph, abort_flag)) { ok = false; break; }
-                    if (!mbar_wait(smem_u32(&sh->acc_empty[as]), aph ^ 1u, abort_flag)) { ok = false; break; }
-                    tc_fence_after();
                     const uint32_t a_addr = base + s * kStageBytes;
                     const uint64_t adesc = make_kmajor_sw128_desc(a_addr);
                     const uint64_t bdesc = make_kmajor_sw128_desc(a_addr + kATileBytes);
                     const uint32_t d = tmem_base + as * kTileN;
+                    if (!mbar_wait(smem_u32(&sh->acc_empty[as]), aph ^ 1u, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
 #pragma unroll
                     for (int k = 0; k < kBlock / 32; ++k) {
                         // 32 e4m3 = 32 B along K inside the 128 B swizzled row: +2 in 16 B units.
@@ -442,12 +442,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
         const int q = warp & 3;      // TMEM lane quarter this warp may read
         const int row = q * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-        // accumulator column of the four 32-column chunks this thread promotes
-        //   GEMM1: linear-branch columns 64h..64h+63 and gated-branch columns 128+64h..128+64h+63
-        //   GEMM2: columns 128h..128h+127
-        const uint32_t c0 = (MODE == 1) ? (uint32_t)(64 * h) : (uint32_t)(128 * h);
+        // accumulator column of the four 32-column chunks this thread promotes: columns 64h..64h+63 of the
+        // tile's first 128-column half and 128+64h..128+64h+63 of its second (GEMM1: linear and gated branch)
+        const uint32_t c0 = (uint32_t)(64 * h);
         const uint32_t c1 = c0 + 32;
-        const uint32_t c2 = (MODE == 1) ? (uint32_t)(128 + 64 * h) : c0 + 64;
+        const uint32_t c2 = (uint32_t)(128 + 64 * h);
         const uint32_t c3 = c2 + 32;
 
         uint32_t it = 0;
@@ -467,10 +466,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
             const float2* sw_tile = w_scale_packed + ((size_t)tc.e * kTilesN + tc.n) * kKBlocks;
             const float2 sw_a = (lane < kKBlocks) ? __ldg(sw_tile + lane) : make_float2(0.0f, 0.0f);
             const float2 sw_b = (kKBlocks > 32 && lane + 32 < kKBlocks) ? __ldg(sw_tile + lane + 32) : make_float2(0.0f, 0.0f);
-            // GEMM1: .x scales the linear-branch block, .y the gated-branch block; GEMM2: .x / .y are the
-            // tile's first / second 128-column block, of which this thread's 128 columns are one
-            const float mine_a = (MODE == 1 || h == 0) ? sw_a.x : sw_a.y, other_a = sw_a.y;
-            const float mine_b = (MODE == 1 || h == 0) ? sw_b.x : sw_b.y, other_b = sw_b.y;
+            // .x scales the tile's first 128-column block (GEMM1: linear branch), .y its second (gated branch)
+            const float mine_a = sw_a.x, other_a = sw_a.y;
+            const float mine_b = sw_b.x, other_b = sw_b.y;
             float acc[128];
 #pragma unroll
             for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
@@ -479,7 +477,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
             float sa_n = ld_scale_early(sfa + (size_t)kb0 * ws.m_cap);
             for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const float lo_w = __shfl_sync(0xffffffffu, (kKBlocks > 32 && kb >= 32) ? mine_b : mine_a, kb & 31);
-                const float hi_w = (MODE == 1) ? __shfl_sync(0xffffffffu, (kb >= 32) ? other_b : other_a, kb & 31) : lo_w;
+                const float hi_w = __shfl_sync(0xffffffffu, (kb >= 32) ? other_b : other_a, kb & 31);
                 const float s_lo = sa_n * lo_w;
                 const float s_hi = sa_n * hi_w;
                 if (kb + 1 < kb1) sa_n = ld_scale_early(sfa + (size_t)(kb + 1) * ws.m_cap);
@@ -526,8 +524,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                     if (!ok) break;
                 }
                 if (warp_has_rows) {
-                    const int pa = (MODE == 1) ? h : 2 * h;
-                    const int pb = (MODE == 1) ? 2 + h : 2 * h + 1;
+                    const int pa = h, pb = 2 + h;
                     uint8_t* ra = tile_stage + pa * kPanelBytes + row * 128;
                     uint8_t* rb = tile_stage + pb * kPanelBytes + row * 128;
                     const uint32_t sw = (uint32_t)(row & 7);
@@ -649,7 +646,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                 }
             } else {
                 if (valid) {
-                    uint4* dst = reinterpret_cast<uint4*>(ws.y + (size_t)grow * hidden + tc.n * kTileN + 128 * h);
+                    // acc[0..63] are columns 64h.., acc[64..127] columns 128 + 64h.. of the tile
+                    uint4* dst = reinterpret_cast<uint4*>(ws.y + (size_t)grow * hidden + tc.n * kTileN + 64 * h);
 #pragma unroll
                     for (int v8 = 0; v8 < 8; ++v8) {
                         uint4 pk[2];
@@ -660,7 +658,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                             for (int i = 0; i < 4; ++i)
                                 h2[i] = __floats2bfloat162_rn(acc[v8 * 16 + q2 * 8 + 2 * i], acc[v8 * 16 + q2 * 8 + 2 * i + 1]);
                         }
-                        st_global_32B(dst + 2 * v8, pk[0], pk[1]);
+                        st_global_32B(dst + (v8 < 4 ? 0 : 8) + 2 * v8, pk[0], pk[1]);
                     }
                 }
             }
