@@ -638,7 +638,8 @@ def run_ours(args, rank, world, local):
                 "path": "moe_fp8_b200_run_host_async + host_wait (C ABI, pinned host buffers, two calls in flight: copy-in of step "
                         "i+1 and copy-out of step i-1 overlap the compute of step i); sync_call_ms_per_step = one blocking "
                         "moe_fp8_b200_run_host per step" if world == 1
-                        else ("ShardedMoe.run_host_async + host_wait (two calls in flight): pinned H2D of the rank's token slice + NCCL all-gather of the inputs + "
+                        else ("ShardedMoe.run_host_async + host_wait (three calls in flight): pinned H2D of the rank's token slice, copy-engine "
+                              "replication of the slice into every peer's input staging over NVLink (bounded flag hand-shake) + "
                               + ("moe_fp8_b200_run_reduce_scatter (peer stores)" if args.collective == "fused"
                                  else f"moe_fp8_b200_run + NCCL {args.collective}") + " + D2H of the rank's output slice; "
                               "bytes are per rank")},
