@@ -3,11 +3,18 @@
 // eight promotion warps with the kernel's own handshake (ptx.cuh of the package).  It reports SM cycles
 // per 128-wide K block for a few forms of the loop, which is where the figures quoted in the design notes
 // about the promotion pipeline come from:
-//   mma_only        4 x tcgen05.mma M128 N256 K32 per K block, promotion warps release the stage at once
-//   mma_only_n128   the same block issued as 8 x M128 N128 K32 (what a finer accumulator split would need)
-//   drain           promotion warps read the whole stage from TMEM (4 x 32 columns each), no arithmetic
-//   promote_scalar  + fp32 scale-and-add with scalar FMAs
-//   promote_packed  + the packed two-wide FMA the kernel uses
+//   mma_only            4 x tcgen05.mma M128 N256 K32 per K block, promotion warps release the stage at once
+//   mma_only_n128       the same block issued as 8 x M128 N128 K32 (what a finer accumulator split would need)
+//   drain               promotion warps read the whole stage from TMEM (4 x 32 columns each), no arithmetic
+//   promote_scalar      + fp32 scale-and-add with scalar FMAs
+//   promote_packed      + the packed two-wide FMA the kernel uses
+//   ring                + the operand ring's barrier traffic on the issuing thread, with no data behind it: a
+//                       stand-in producer, the wait for a full stage (probed one block ahead, as in the kernel)
+//                       and the second tcgen05.commit that frees the stage
+//   ring_scales         + the kernel's per-block scale handling in the promotion warps (two shuffles, a global
+//                       load issued one block ahead, two multiplies): the kernel's loop minus TMA and tiles
+//   ring_scales_relayed the stage is freed by a promotion warp's plain arrive instead of a second commit
+//   ring_scales_two     two MMA-issuing threads, one per accumulator stage
 // Build: nvcc -std=c++17 -O3 -gencode arch=compute_100a,code=sm_100a -I <package>/csrc gemm_pipeline_probe.cu
 // Run:   ./a.out [ctas=1] [k_blocks=4000]     (every wait is bounded; a failed wait ends the kernel)
 #include <cstdio>
@@ -17,7 +24,16 @@
 #include "ptx.cuh"
 using namespace moe;
 
-enum Form { kMmaOnly = 0, kMmaOnlyN128 = 1, kDrain = 2, kPromoteScalar = 3, kPromotePacked = 4 };
+enum : int {
+    F_N128 = 1,         // 128-column MMA instructions
+    F_LOADS = 2,        // promotion warps read the stage
+    F_FMA_SCALAR = 4,   // ... and promote with scalar FMAs
+    F_FMA_PACKED = 8,   // ... or with packed FMAs
+    F_RING = 16,        // operand-ring barriers on the issuing thread
+    F_SCALES = 32,      // per-block scale handling in the promotion warps
+    F_RELAY = 64,       // a promotion warp frees the operand stage
+    F_TWO = 128,        // two issuing threads (warps 1 and 3)
+};
 
 __device__ __forceinline__ void wait_loads(uint32_t (&a)[32], uint32_t (&b)[32]) {
     // tcgen05.wait::ld with the destination registers as in/out operands (no use may move above it)
@@ -46,15 +62,26 @@ __device__ __forceinline__ void promote32(float (&acc)[128], const uint32_t (&r)
     }
 }
 
+// The operand ring has three stages; its barriers come as one full / empty pair per K block of a window of
+// six, so that with two issuing threads (even / odd K blocks) every pair is always used by the same thread
+// and its phases are seen in order (a parity wait cannot tell a phase from the one two before it).
+constexpr int kRingStages = 3;
+constexpr int kRingBars = 6;
+
 template <int FORM>
 __global__ void __launch_bounds__(384, 1) probe(float* out, long long* cycles, int iters) {
+    constexpr bool kN128 = FORM & F_N128, kLoads = FORM & F_LOADS, kFma = FORM & (F_FMA_SCALAR | F_FMA_PACKED);
+    constexpr bool kPacked = FORM & F_FMA_PACKED, kRing = FORM & F_RING, kScales = FORM & F_SCALES;
+    constexpr bool kRelay = FORM & F_RELAY, kTwo = FORM & F_TWO;
     __shared__ uint32_t slot;
     __shared__ uint64_t acc_full[2], acc_empty[2];
+    __shared__ uint64_t st_full[kRingBars], st_empty[kRingBars];
     __shared__ int abort_word;
     extern __shared__ __align__(1024) uint8_t tiles[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&acc_full[s]), 1); mbar_init(smem_u32(&acc_empty[s]), 8); }
+        for (int s = 0; s < kRingBars; ++s) { mbar_init(smem_u32(&st_full[s]), 1); mbar_init(smem_u32(&st_empty[s]), 1); }
         abort_word = 0;
         fence_mbar_init();
     }
@@ -66,25 +93,42 @@ __global__ void __launch_bounds__(384, 1) probe(float* out, long long* cycles, i
     volatile int* abort_flag = &abort_word;
     if (warp < 4) {
         setmaxnreg_dec<56>();
-        if (warp == 1 && lane == 0) {
+        if (kRing && warp == 0 && lane == 0) {
+            // stand-in for the TMA producer: same barrier traffic, no data
+            for (int it = 0; it < iters; ++it) {
+                if (it >= kRingStages) {
+                    const int pit = it - kRingStages;   // the K block that last used this stage
+                    if (!mbar_wait(smem_u32(&st_empty[pit % kRingBars]), (pit / kRingBars) & 1, abort_flag)) break;
+                }
+                mbar_arrive(smem_u32(&st_full[it % kRingBars]));
+            }
+        }
+        if ((warp == 1 || (kTwo && warp == 3)) && lane == 0) {
+            const uint32_t mine = warp == 3 ? 1u : 0u;
+            const int step = kTwo ? 2 : 1;
             const uint32_t tb = (smem_u32(tiles) + 1023u) & ~1023u;   // operand bytes are whatever the SM holds
             const uint64_t ad = make_kmajor_sw128_desc(tb), bd = make_kmajor_sw128_desc(tb + 16384);
             const uint32_t idesc = make_idesc_e4m3(128, 256), idesc128 = make_idesc_e4m3(128, 128);
             const long long t0 = clock64();
+            bool next_ready = false;
             for (int it = 0; it < iters; ++it) {
                 const uint32_t as = it & 1, aph = (it >> 1) & 1;
+                if (kTwo && as != mine) continue;
+                if (kRing && !next_ready && !mbar_wait(smem_u32(&st_full[it % kRingBars]), (it / kRingBars) & 1, abort_flag)) break;
                 if (!mbar_wait(smem_u32(&acc_empty[as]), aph ^ 1, abort_flag)) break;
                 tc_fence_after();
-                if (FORM == kMmaOnlyN128) {
+                if (kN128) {
                     for (int hh = 0; hh < 2; ++hh)
                         for (int kk = 0; kk < 4; ++kk)
                             umma_f8(base + as * 256 + 128 * hh, ad + 2 * kk, bd + 1024 * hh + 2 * kk, idesc128, kk > 0);
                 } else {
                     for (int kk = 0; kk < 4; ++kk) umma_f8(base + as * 256, ad + 2 * kk, bd + 2 * kk, idesc, kk > 0);
                 }
+                if (kRing && !kRelay) tc_commit(smem_u32(&st_empty[it % kRingBars]));
                 tc_commit(smem_u32(&acc_full[as]));
+                if (kRing) next_ready = mbar_try_wait(smem_u32(&st_full[(it + step) % kRingBars]), ((it + step) / kRingBars) & 1);
             }
-            if (blockIdx.x == 0) cycles[0] = clock64() - t0;
+            if (blockIdx.x == 0 && warp == 1) cycles[0] = clock64() - t0;
         }
     } else {
         setmaxnreg_inc<224>();
@@ -94,21 +138,28 @@ __global__ void __launch_bounds__(384, 1) probe(float* out, long long* cycles, i
 #pragma unroll
         for (int j = 0; j < 128; ++j) acc[j] = 0.f;
         uint32_t r0[32], r1[32];
+        float sa_n = 1.0f;
         for (int it = 0; it < iters; ++it) {
             const uint32_t as = it & 1, aph = (it >> 1) & 1;
-            const float s_lo = 1.0f + it * 1e-9f, s_hi = 1.0f - it * 1e-9f;
+            float s_lo = 1.0f + it * 1e-9f, s_hi = 1.0f - it * 1e-9f;
+            if (kScales) {
+                const float lo_w = __shfl_sync(0xffffffffu, s_lo, it & 31), hi_w = __shfl_sync(0xffffffffu, s_hi, it & 31);
+                s_lo = sa_n * lo_w;
+                s_hi = sa_n * hi_w;
+                asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(sa_n) : "l"(out + 1024 + ((it * 128 + threadIdx.x) & 1023)));
+            }
             bool ok = mbar_wait(smem_u32(&acc_full[as]), aph, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            if (FORM == kMmaOnly || FORM == kMmaOnlyN128) {
+            if (kRing && kRelay && warp == 4 && lane == 0) mbar_arrive(smem_u32(&st_empty[it % kRingBars]));
+            if (!kLoads) {
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&acc_empty[as]));
                 continue;
             }
             const uint32_t t = la + as * 256 + 128 * h;
-            constexpr bool kFma = FORM >= kPromoteScalar, kPacked = FORM == kPromotePacked;
             tmem_ld_32x32(t, r0);
             tmem_ld_32x32(t + 32, r1);
             wait_loads(r0, r1);
@@ -142,7 +193,7 @@ static int run(const char* name, int ctas, int iters, float* out, long long* d) 
     const cudaError_t e = cudaDeviceSynchronize();
     long long h[2] = {0, 0};
     cudaMemcpy(h, d, sizeof h, cudaMemcpyDeviceToHost);
-    printf("%-15s %8.1f cycles per K block   (%s%s)\n", name, (double)h[0] / iters, cudaGetErrorString(e),
+    printf("%-20s %8.1f cycles per K block   (%s%s)\n", name, (double)h[0] / iters, cudaGetErrorString(e),
            h[1] ? ", a wait ran out" : "");
     return (e == cudaSuccess && h[1] == 0) ? 0 : 1;
 }
@@ -152,14 +203,20 @@ int main(int argc, char** argv) {
     const int iters = argc > 2 ? atoi(argv[2]) : 4000;
     float* out;
     long long* d;
-    cudaMalloc(&out, 4096);
+    cudaMalloc(&out, 16384);
+    cudaMemset(out, 0, 16384);
     cudaMalloc(&d, 64);
     printf("ctas %d, K blocks %d\n", ctas, iters);
+    constexpr int kPromote = F_LOADS | F_FMA_PACKED;
     int bad = 0;
-    bad |= run<kMmaOnly>("mma_only", ctas, iters, out, d);
-    bad |= run<kMmaOnlyN128>("mma_only_n128", ctas, iters, out, d);
-    bad |= run<kDrain>("drain", ctas, iters, out, d);
-    bad |= run<kPromoteScalar>("promote_scalar", ctas, iters, out, d);
-    bad |= run<kPromotePacked>("promote_packed", ctas, iters, out, d);
+    bad |= run<0>("mma_only", ctas, iters, out, d);
+    bad |= run<F_N128>("mma_only_n128", ctas, iters, out, d);
+    bad |= run<F_LOADS>("drain", ctas, iters, out, d);
+    bad |= run<F_LOADS | F_FMA_SCALAR>("promote_scalar", ctas, iters, out, d);
+    bad |= run<kPromote>("promote_packed", ctas, iters, out, d);
+    bad |= run<kPromote | F_RING>("ring", ctas, iters, out, d);
+    bad |= run<kPromote | F_RING | F_SCALES>("ring_scales", ctas, iters, out, d);
+    bad |= run<kPromote | F_RING | F_SCALES | F_RELAY>("ring_scales_relayed", ctas, iters, out, d);
+    bad |= run<kPromote | F_RING | F_SCALES | F_TWO>("ring_scales_two", ctas, iters, out, d);
     return bad;
 }

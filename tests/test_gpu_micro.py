@@ -27,5 +27,10 @@ def test_gemm_pipeline_probe(tmp_path):
     # a K block is 4 MMAs of 128 cycles: the tensor pipe's floor
     assert 500 <= cyc["mma_only"] <= 560, cyc
     assert cyc["drain"] < 700 and cyc["promote_packed"] <= cyc["promote_scalar"] + 1, cyc
-    # 128-column instructions are shared-memory bound (A is re-read per half): no faster per column
+    # 128-column instructions re-read A per half: no faster per column
     assert cyc["mma_only_n128"] >= cyc["mma_only"], cyc
+    # the operand ring's barrier work on the issuing thread is not hidden by the tensor pipe ...
+    assert cyc["ring"] > cyc["promote_packed"] + 100, cyc
+    # ... and a second issuing thread takes most of it back (in this probe; see the design notes for the kernel)
+    assert cyc["ring_scales_two"] < cyc["ring_scales"] - 100, cyc
+    assert cyc["ring_scales_relayed"] < cyc["ring_scales"], cyc
