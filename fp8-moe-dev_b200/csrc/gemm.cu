@@ -14,7 +14,7 @@
 //
 // Structure of one CTA (384 threads, one CTA per SM, 128 x 256 output tile):
 //   warp 0      TMA producer: 128x128 B A tile + 256x128 B weight tile per 128-wide K block,
-//               4-stage shared-memory ring, SWIZZLE_128B, one mbarrier pair per stage
+//               3-stage shared-memory ring (4 in the split-K kernel), SWIZZLE_128B, one mbarrier pair per stage
 //   warp 1      MMA issuer: 4 x tcgen05.mma (M128 N256 K32, e4m3 -> fp32) per K block into one
 //               of two 256-column TMEM accumulator stages, overwrite mode on the first
 //   warp 2      TMEM allocation / release
