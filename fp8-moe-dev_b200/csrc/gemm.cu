@@ -392,41 +392,61 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                     __syncwarp();
                 } else {
                     // GEMM1: D was rounded to bf16 on its way here (the reference materialises it in
-                    // bf16).  One row per warp pass, lane l owns SwiGLU columns 4l..4l+3 of the tile's
+                    // bf16).  Of each row, lane l owns SwiGLU columns 4l..4l+3 of the tile's
                     // 128-column block: x1 from panels 0-1 (linear branch), x2 from panels 2-3 (gated
                     // branch); v = silu(x2) * x1 in fp32, row absmax by shuffles, scale = amax / 448
                     // (1 for an all-zero block), e4m3 codes -> 128 coalesced bytes per row.
+                    const int r_begin = ew * (kTileM / 2);
                     const int r_end = tc.rows < (ew + 1) * (kTileM / 2) ? tc.rows : (ew + 1) * (kTileM / 2);
                     const uint32_t pan = (uint32_t)(lane >> 4) * kPanelBytes;
                     const uint32_t chunk = (uint32_t)(lane & 15) >> 1, sub = (uint32_t)(lane & 1) * 8u;
-                    for (int r = ew * (kTileM / 2); r < r_end; ++r) {
-                        const uint8_t* src = tile_stage + pan + r * 128 + ((chunk ^ (uint32_t)(r & 7)) << 4) + sub;
-                        const uint2 l1 = *reinterpret_cast<const uint2*>(src);
-                        const uint2 l2 = *reinterpret_cast<const uint2*>(src + 2 * kPanelBytes);
-                        const float x1[4] = {__uint_as_float(l1.x << 16), __uint_as_float(l1.x & 0xffff0000u),
-                                             __uint_as_float(l1.y << 16), __uint_as_float(l1.y & 0xffff0000u)};
-                        const float x2[4] = {__uint_as_float(l2.x << 16), __uint_as_float(l2.x & 0xffff0000u),
-                                             __uint_as_float(l2.y << 16), __uint_as_float(l2.y & 0xffff0000u)};
-                        float v[4];
-                        float amax = 0.0f;
+                    // The generic instantiation takes four rows per pass, so that their shared-memory loads,
+                    // shuffles and conversions overlap: with few K blocks per tile (a small hidden size) the
+                    // epilogue warps set GEMM1's pace.  With the reference's 56 K blocks they have time to
+                    // spare, and one row per pass leaves more issue slots to the promotion warps they share
+                    // their schedulers with (measured: four rows per pass cost 1.3 % there).
+                    constexpr int kRowsPerPass = GENERIC ? 4 : 1;
+                    for (int r0 = r_begin; r0 < r_end; r0 += kRowsPerPass) {
+                        float v[kRowsPerPass][4], amax[kRowsPerPass];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float silu = silu_exact ? x2[j] / (1.0f + __expf(-x2[j]))
-                                                          : x2[j] * (0.5f * (x2[j] * rsqrtf(fmaf(x2[j], x2[j], 4.0f)) + 1.0f));
-                            v[j] = silu * x1[j];
-                            amax = fmaxf(amax, fabsf(v[j]));
+                        for (int u4 = 0; u4 < kRowsPerPass; ++u4) {
+                            const int r = r0 + u4;   // < 128: rows past r_end hold stale data and are not stored
+                            const uint8_t* src = tile_stage + pan + r * 128 + ((chunk ^ (uint32_t)(r & 7)) << 4) + sub;
+                            const uint2 l1 = *reinterpret_cast<const uint2*>(src);
+                            const uint2 l2 = *reinterpret_cast<const uint2*>(src + 2 * kPanelBytes);
+                            const float x1[4] = {__uint_as_float(l1.x << 16), __uint_as_float(l1.x & 0xffff0000u),
+                                                 __uint_as_float(l1.y << 16), __uint_as_float(l1.y & 0xffff0000u)};
+                            const float x2[4] = {__uint_as_float(l2.x << 16), __uint_as_float(l2.x & 0xffff0000u),
+                                                 __uint_as_float(l2.y << 16), __uint_as_float(l2.y & 0xffff0000u)};
+                            amax[u4] = 0.0f;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float silu = silu_exact ? x2[j] / (1.0f + __expf(-x2[j]))
+                                                              : x2[j] * (0.5f * (x2[j] * rsqrtf(fmaf(x2[j], x2[j], 4.0f)) + 1.0f));
+                                v[u4][j] = silu * x1[j];
+                                amax[u4] = fmaxf(amax[u4], fabsf(v[u4][j]));
+                            }
                         }
 #pragma unroll
-                        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-                        const float scale = (amax > 0.0f) ? (amax / 448.0f) : 1.0f;
-                        const float inv_scale = 1.0f / scale;
-                        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0] * inv_scale, v[1] * inv_scale),
-                                                                     __NV_SATFINITE, __NV_E4M3);
-                        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2] * inv_scale, v[3] * inv_scale),
-                                                                     __NV_SATFINITE, __NV_E4M3);
-                        const int grow = tc.row0 + r;
-                        reinterpret_cast<uint32_t*>(ws.a2 + (size_t)grow * inter + tc.n * kBlock)[lane] = lo | (hi << 16);
-                        if (lane == 0) ws.sfa2[(size_t)tc.n * ws.m_cap + grow] = scale;
+                        for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+                            for (int u4 = 0; u4 < kRowsPerPass; ++u4) amax[u4] = fmaxf(amax[u4], __shfl_xor_sync(0xffffffffu, amax[u4], off));
+                        }
+#pragma unroll
+                        for (int u4 = 0; u4 < kRowsPerPass; ++u4) {
+                            const int r = r0 + u4;
+                            if (r < r_end) {
+                                const float scale = (amax[u4] > 0.0f) ? (amax[u4] / 448.0f) : 1.0f;
+                                const float inv_scale = 1.0f / scale;
+                                const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[u4][0] * inv_scale, v[u4][1] * inv_scale),
+                                                                             __NV_SATFINITE, __NV_E4M3);
+                                const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[u4][2] * inv_scale, v[u4][3] * inv_scale),
+                                                                             __NV_SATFINITE, __NV_E4M3);
+                                const int grow = tc.row0 + r;
+                                reinterpret_cast<uint32_t*>(ws.a2 + (size_t)grow * inter + tc.n * kBlock)[lane] = lo | (hi << 16);
+                                if (lane == 0) ws.sfa2[(size_t)tc.n * ws.m_cap + grow] = scale;
+                            }
+                        }
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&sh->tile_empty));
