@@ -182,9 +182,17 @@ def test_reference_geometry_with_other_routing_constants(pkg, oracle):
 
 
 def test_default_shape_handle_is_the_reference_handle(pkg):
+    import ctypes as C
     a = pkg.MoeLayer(64, 32, 0)
     b = pkg.MoeLayer(64, 32, 0, hidden=7168, intermediate=2048, top_k=8, n_group=8, topk_group=4)
+    c = pkg.MoeLayer(64, 32, 0, hidden=1024, intermediate=512, top_k=4, n_group=4, topk_group=2)
     try:
+        lib = pkg._lib.load()
+        for lay, want in ((a, (7168, 2048, 8, 8, 4)), (b, (7168, 2048, 8, 8, 4)), (c, (1024, 512, 4, 4, 2))):
+            sh = pkg._lib.Shape()
+            assert lib.moe_fp8_b200_get_shape(lay._h, C.byref(sh)) == 0
+            assert (sh.hidden, sh.intermediate, sh.top_k, sh.n_group, sh.topk_group) == want
+        c.close()
         inputs = hp.cpu_inputs(48, seed=9)
         weights = hp.gpu_shard(0, 32)
         x = hp.run_layer(a, inputs, weights, 0)
