@@ -135,6 +135,8 @@ struct Workspace {
     int* pair_count;        // [T]   kept (token, local expert) pairs
     uint32_t* pair_code;    // [T,8] (local expert << 24) | slot inside the expert
     float* pair_weight;     // [T,8] weight * (renorm) * routed_scaling_factor
+    int* pair_row;          // [T,8] packed row of each kept pair, -1 past the token's pair count (written by the
+                            //       permute kernel; lets the fused exchange find a token's rows in one load)
     int* row_token;         // [M_cap] token of each packed row (diagnostics / tests)
     uint8_t* a1;            // [M_cap, H]   e4m3 rows gathered per expert
     float* sfa1;            // [56, M_cap]  their 1x128 scales, k-block major

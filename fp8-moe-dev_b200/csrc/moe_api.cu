@@ -65,7 +65,7 @@ struct Carve {
 
 struct Layout {
     size_t ctrl, expert_offset, tile_info, num_tiles, expert_map, topk_idx, topk_weight, pair_count, pair_code,
-        pair_weight, row_token, a1, sfa1, a2, sfa2, y, splitk, sw1_packed, sw2_packed, total;
+        pair_weight, pair_row, row_token, a1, sfa1, a2, sfa2, y, splitk, sw1_packed, sw2_packed, total;
     int m_cap, max_tiles;
 };
 
@@ -88,6 +88,7 @@ Layout make_layout(int T, int E, const Geometry& geo = kReferenceGeometry)
     L.pair_count = c.take(sizeof(int) * (size_t)T);
     L.pair_code = c.take(sizeof(uint32_t) * (size_t)T * kTopK);
     L.pair_weight = c.take(sizeof(float) * (size_t)T * kTopK);
+    L.pair_row = c.take(sizeof(int) * (size_t)T * kTopK);
     L.row_token = c.take(sizeof(int) * (size_t)L.m_cap);
     L.a1 = c.take((size_t)L.m_cap * hidden);
     L.sfa1 = c.take(sizeof(float) * (hidden / kBlock) * L.m_cap);
@@ -483,6 +484,7 @@ int moe_fp8_b200_create_shaped(moe_fp8_b200_handle* out, int device, int max_tok
     w.pair_count = reinterpret_cast<int*>(h->base + L.pair_count);
     w.pair_code = reinterpret_cast<uint32_t*>(h->base + L.pair_code);
     w.pair_weight = reinterpret_cast<float*>(h->base + L.pair_weight);
+    w.pair_row = reinterpret_cast<int*>(h->base + L.pair_row);
     w.row_token = reinterpret_cast<int*>(h->base + L.row_token);
     w.a1 = h->base + L.a1;
     w.sfa1 = reinterpret_cast<float*>(h->base + L.sfa1);

@@ -211,8 +211,15 @@ __global__ void __launch_bounds__(kPermuteWarps * 32) permute_rows_kernel(
     pdl_launch_dependents();
     pdl_wait();
     if (t >= T) return;
-    if (ws.num_tiles[0] == 0) return;
-    const int n_pairs = ws.pair_count[t];
+    const int n_pairs = (ws.num_tiles[0] == 0) ? 0 : ws.pair_count[t];
+    if (lane < kTopK) {   // the token's packed rows, for the fused exchange
+        int r = -1;
+        if (lane < n_pairs) {
+            const uint32_t code = ws.pair_code[(size_t)t * kTopK + lane];
+            r = ws.expert_offset[code >> 24] + (int)(code & 0x00ffffffu);
+        }
+        ws.pair_row[(size_t)t * kTopK + lane] = r;
+    }
     if (n_pairs == 0) return;
 
     constexpr int kVec = kHidden / 16 / 32;  // 14 uint4 per lane
@@ -247,8 +254,15 @@ __global__ void __launch_bounds__(kPermuteWarps * 32) permute_rows_generic_kerne
     pdl_launch_dependents();
     pdl_wait();
     if (t >= T) return;
-    if (ws.num_tiles[0] == 0) return;
-    const int n_pairs = ws.pair_count[t];
+    const int n_pairs = (ws.num_tiles[0] == 0) ? 0 : ws.pair_count[t];
+    if (lane < kTopK) {
+        int r = -1;
+        if (lane < n_pairs) {
+            const uint32_t code = ws.pair_code[(size_t)t * kTopK + lane];
+            r = ws.expert_offset[code >> 24] + (int)(code & 0x00ffffffu);
+        }
+        ws.pair_row[(size_t)t * kTopK + lane] = r;
+    }
     if (n_pairs == 0) return;
     const int H = ws.geo.hidden;
     const int vecs = H / 16, blocks = H / kBlock;   // <= 512 uint4, <= 64 scales
@@ -434,6 +448,23 @@ __device__ __forceinline__ uint8_t* peer_ptr(const ExchangeView& ex, int i) {
     return p;
 }
 
+// A token's rows here and their weights: two 32-byte loads from the tables the permute kernel left behind
+// (row -1 = no such pair), one round trip instead of the chain pair count -> pair code -> expert offset.
+struct PairTable {
+    int4 row[2];
+    float4 weight[2];
+};
+__device__ __forceinline__ PairTable load_pair_table(const Workspace& ws, int t) {
+    PairTable p;
+    const int4* r = reinterpret_cast<const int4*>(ws.pair_row + (size_t)t * kTopK);
+    const float4* w = reinterpret_cast<const float4*>(ws.pair_weight + (size_t)t * kTopK);
+    p.row[0] = __ldg(r);
+    p.row[1] = __ldg(r + 1);
+    p.weight[0] = __ldg(w);
+    p.weight[1] = __ldg(w + 1);
+    return p;
+}
+
 __global__ void __launch_bounds__(kCombineThreads, 2) combine_push_kernel(Workspace ws, ExchangeView ex, int T)
 {
     pdl_launch_dependents();
@@ -446,34 +477,66 @@ __global__ void __launch_bounds__(kCombineThreads, 2) combine_push_kernel(Worksp
     // One system-scope fence per CTA, after its last store, instead of one per token.
     const int span = ex.tokens_per_rank * ex.world;
     const int start = ((ex.rank + 1) % ex.world) * ex.tokens_per_rank;
-    for (int i = blockIdx.x; i < span; i += gridDim.x) {
+    auto token_of = [&](int i) {
         int t = start + i;
         if (t >= span) t -= span;
+        return t;
+    };
+    // the next token's table travels while this token's rows are summed and stored
+    PairTable next;
+    {
+        const int t0 = token_of(blockIdx.x);
+        if (t0 < T) next = load_pair_table(ws, t0);
+    }
+    for (int i = blockIdx.x; i < span; i += gridDim.x) {
+        const int t = token_of(i);
+        const PairTable cur = next;
+        if (i + (int)gridDim.x < span) {
+            const int tn = token_of(i + gridDim.x);
+            if (tn < T) next = load_pair_table(ws, tn);
+        }
         if (t >= T) continue;
-        const int n_pairs = any_tiles ? ws.pair_count[t] : 0;
+        const int rows[kTopK] = {cur.row[0].x, cur.row[0].y, cur.row[0].z, cur.row[0].w,
+                                 cur.row[1].x, cur.row[1].y, cur.row[1].z, cur.row[1].w};
+        const float wts[kTopK] = {cur.weight[0].x, cur.weight[0].y, cur.weight[0].z, cur.weight[0].w,
+                                  cur.weight[1].x, cur.weight[1].y, cur.weight[1].z, cur.weight[1].w};
+        const bool has_rows = any_tiles && rows[0] >= 0;   // pairs are packed from entry 0
         const int owner = t / ex.tokens_per_rank;
         const int tl = t - owner * ex.tokens_per_rank;
         uint8_t* dst_base = peer_ptr(ex, owner) + ex.data_offset;
-        if (n_pairs > 0) {
+        if (has_rows) {
             float acc[2][8];
 #pragma unroll
             for (int c = 0; c < 2; ++c)
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[c][j] = 0.0f;
-            for (int p = 0; p < n_pairs; ++p) {
-                const uint32_t code = ws.pair_code[(size_t)t * kTopK + p];
-                const float w = ws.pair_weight[(size_t)t * kTopK + p];
-                const int row = ws.expert_offset[code >> 24] + (int)(code & 0x00ffffffu);
-                const uint4* src = reinterpret_cast<const uint4*>(ws.y + (size_t)row * kHidden);
+            // the rows of four pairs are requested together, then added in pair order
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    const uint4 raw = __ldg(src + threadIdx.x + c * kCombineThreads);
-                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            for (int p0 = 0; p0 < kTopK; p0 += 4) {
+                if (rows[p0] < 0) break;
+                uint4 raw[4][2];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float2 f = __bfloat1622float2(h2[j]);
-                        acc[c][2 * j] += f.x * w;
-                        acc[c][2 * j + 1] += f.y * w;
+                for (int u = 0; u < 4; ++u) {
+                    if (rows[p0 + u] >= 0) {
+                        const uint4* src = reinterpret_cast<const uint4*>(ws.y + (size_t)rows[p0 + u] * kHidden);
+                        raw[u][0] = __ldg(src + threadIdx.x);
+                        raw[u][1] = __ldg(src + threadIdx.x + kCombineThreads);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (rows[p0 + u] >= 0) {
+                        const float w = wts[p0 + u];
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u][c]);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float2 f = __bfloat1622float2(h2[j]);
+                                acc[c][2 * j] += f.x * w;
+                                acc[c][2 * j + 1] += f.y * w;
+                            }
+                        }
                     }
                 }
             }
@@ -491,7 +554,7 @@ __global__ void __launch_bounds__(kCombineThreads, 2) combine_push_kernel(Worksp
         if (threadIdx.x == 0) {
             uint8_t* present = dst_base + 2 * ex.rows_bytes_per_parity + (size_t)parity * ex.present_bytes_per_parity +
                                (size_t)ex.rank * ex.present_stride + tl;
-            *present = n_pairs > 0 ? 1 : 0;
+            *present = has_rows ? 1 : 0;
         }
     }
     // All of this CTA's peer stores become visible system-wide before it takes its ticket; the
