@@ -472,15 +472,14 @@ __global__ void __launch_bounds__(kCombineThreads, 2) combine_push_kernel(Worksp
     const int parity = (int)(ex.epoch & 1u);
     const bool any_tiles = ws.num_tiles[0] != 0;
     if (threadIdx.x == 0) atomicMin(&ws.ctrl->xch_time[0], global_timer_ns());
-    // Persistent CTAs walk the tokens starting with the next rank's slice and ending with their
-    // own, so the remote stores go out first and every rank starts on a different destination.
-    // One system-scope fence per CTA, after its last store, instead of one per token.
+    // Persistent CTAs walk the tokens destination by destination in turn -- index i goes to rank
+    // (rank + 1 + i mod world) -- so that stores to every peer and the local rows (which cost HBM, not
+    // NVLink, bandwidth) are under way at the same time.  One system-scope fence per CTA, after its last
+    // store, instead of one per token.
     const int span = ex.tokens_per_rank * ex.world;
-    const int start = ((ex.rank + 1) % ex.world) * ex.tokens_per_rank;
     auto token_of = [&](int i) {
-        int t = start + i;
-        if (t >= span) t -= span;
-        return t;
+        const int dest = (ex.rank + 1 + i % ex.world) % ex.world;
+        return dest * ex.tokens_per_rank + i / ex.world;
     };
     // the next token's table travels while this token's rows are summed and stored
     PairTable next;
