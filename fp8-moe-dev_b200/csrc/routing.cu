@@ -432,6 +432,9 @@ cudaError_t launch_combine(const Workspace& ws, void* out, int T, cudaStream_t s
 __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ void st_relaxed_sys_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -564,10 +567,12 @@ __global__ void __launch_bounds__(kCombineThreads, 2) combine_push_kernel(Worksp
         const int ticket = atomicAdd(&ws.ctrl->push_done, 1);
         if (ticket == (int)gridDim.x - 1) {
             ws.ctrl->push_done = 0;
+            // one system-scope fence, then the flags as relaxed stores (fence + relaxed store is a release
+            // pattern): they leave back to back instead of each waiting for the one before it
             __threadfence_system();
             for (int o = 0; o < ex.world; ++o) {
                 uint32_t* flag = reinterpret_cast<uint32_t*>(peer_ptr(ex, o)) + ex.rank;
-                st_release_sys_u32(flag, ex.epoch);
+                st_relaxed_sys_u32(flag, ex.epoch);
             }
             ws.ctrl->xch_time[1] = global_timer_ns();
         }
