@@ -20,6 +20,7 @@ DECODE_MAX_TOKENS = 8
 BUF = dict(
     expert_count=0, expert_offset=1, topk_idx=2, topk_weight=3, pair_count=4, pair_code=5, pair_weight=6,
     num_tiles=7, row_token=8, a1=9, sfa1=10, a2=11, sfa2=12, y=13, status=14, decode_timeline=15, exchange_timeline=16,
+    pair_row=17,
 )
 
 EXPORTS = [

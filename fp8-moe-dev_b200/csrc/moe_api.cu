@@ -1012,6 +1012,7 @@ int moe_fp8_b200_read_intermediate(moe_fp8_b200_handle h, int buffer, void* dst,
         case MOE_FP8_B200_BUF_STATUS: src = &w.ctrl->status; size = sizeof(int) * 2; break;
         case MOE_FP8_B200_BUF_DECODE_TIMELINE: src = w.ctrl->dec_time; size = sizeof(w.ctrl->dec_time); break;
         case MOE_FP8_B200_BUF_EXCHANGE_TIMELINE: src = w.ctrl->xch_time; size = sizeof(w.ctrl->xch_time); break;
+        case MOE_FP8_B200_BUF_PAIR_ROW: src = w.pair_row; size = sizeof(int) * T * kTopK; break;
         default: return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "unknown buffer id %d", buffer);
     }
     if (offset > size || bytes > size - offset)

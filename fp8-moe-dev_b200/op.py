@@ -348,7 +348,7 @@ class MoeLayer:
     _DTYPES = dict(expert_count=np.int32, expert_offset=np.int32, topk_idx=np.int32, topk_weight=np.float32,
                    pair_count=np.int32, pair_code=np.uint32, pair_weight=np.float32, num_tiles=np.int32,
                    row_token=np.int32, a1=np.uint8, sfa1=np.float32, a2=np.uint8, sfa2=np.float32, y=np.uint16,
-                   status=np.int32, decode_timeline=np.uint64, exchange_timeline=np.uint64)
+                   status=np.int32, decode_timeline=np.uint64, exchange_timeline=np.uint64, pair_row=np.int32)
 
     def read(self, name: str, count: int, offset_elems: int = 0) -> np.ndarray:
         """First `count` elements (after `offset_elems`) of an intermediate buffer of the last run."""

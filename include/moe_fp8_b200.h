@@ -121,9 +121,11 @@ enum {
     MOE_FP8_B200_BUF_DECODE_TIMELINE = 15, /* uint64 [16] ns clock of CTA 0 in the last decode-kernel run: [0..6] start, tables
                                            * built, phase 1 done, barrier 1 passed, phase 2 done, barrier 2 passed, end;
                                            * [8..11] inside the table build: token routed, pairs listed, tables merged, published */
-    MOE_FP8_B200_BUF_EXCHANGE_TIMELINE = 16 /* uint64 [8] ns clock of the last moe_fp8_b200_run_reduce_scatter on this rank:
+    MOE_FP8_B200_BUF_EXCHANGE_TIMELINE = 16, /* uint64 [8] ns clock of the last moe_fp8_b200_run_reduce_scatter on this rank:
                                             * [0] push starts, [1] push done and flags published, [2] owner step starts
                                             * waiting for its peers, [3] all peers' flags seen, [4] owner step done */
+    MOE_FP8_B200_BUF_PAIR_ROW = 17       /* int32 [T, 8] packed row of each kept pair (expert offset + slot), -1 past the
+                                          * token's pair count; written by the permute stage of the chain */
 };
 
 /* Library version, (major << 16) | minor.  No counterpart in the reference. */

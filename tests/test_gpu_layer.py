@@ -96,8 +96,10 @@ def test_dispatch_and_permute(pkg, oracle, layer32, T, offset, pruning):
     sfa1 = np.stack([layer32.read("sfa1", M, kb * layer32.row_capacity) for kb in range(56)]) if M else None
     hidden = hp.np_u8(inputs[2])
     hscale = inputs[3].numpy()
+    pair_row = layer32.read("pair_row", T * TOPK).reshape(T, TOPK)
     slots = [set() for _ in range(32)]
     for t in range(T):
+        assert list(pair_row[t]) == [int(eoff[le]) + slot for le, slot, _ in pairs[t]] + [-1] * (TOPK - len(pairs[t]))
         got = [(le, wt.tobytes()) for le, _, wt in pairs[t]]
         want = [(int(ple[t, p]), np.float32(pw[t, p]).tobytes()) for p in range(pc[t])]
         assert got == want, (t, pairs[t])
