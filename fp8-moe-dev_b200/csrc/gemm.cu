@@ -308,7 +308,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                     const uint32_t a_dst = base + s * kStageBytes;
                     const uint32_t b_dst = a_dst + kATileBytes;
                     tma_load_2d(a_dst, &tmap_a, full, kb * kBlock, tc.row0);
-                    if (MODE == 1) {
+                    if (ws.w_tiled) {
+                        // tile-ordered copy of the weights: the operand of (expert, n tile, K block) is one
+                        // contiguous 32 KB piece
+                        tma_load_2d(b_dst, &tmap_b, full, 0, ((tc.e * kTilesN + tc.n) * kKBlocks + kb) * kTileN);
+                    } else if (MODE == 1) {
                         tma_load_3d(b_dst, &tmap_b, full, kb * kBlock, tc.n * kBlock, tc.e);
                         tma_load_3d(b_dst + kBTileBytes / 2, &tmap_b, full, kb * kBlock, inter + tc.n * kBlock, tc.e);
                     } else {
@@ -741,6 +745,50 @@ cudaError_t launch_repack_weight_scales(const float* s1, const float* s2, float*
 {
     repack_weight_scales_kernel<<<64, 256, 0, stream>>>(s1, s2, reinterpret_cast<float2*>(p1), reinterpret_cast<float2*>(p2),
                                                         num_experts, geo);
+    return cudaGetLastError();
+}
+
+// Tile-ordered copy of one weight tensor: for every (expert, n tile, K block) the 256 x 128-byte
+// operand the K loop loads becomes one contiguous 32 KB piece (GEMM1: 128 linear rows of the n
+// tile, then its 128 gated rows), so that a TMA box reads whole DRAM pages instead of 256 pieces
+// of 128 bytes that lie a weight row apart.  One warp per source row, read once front to back.
+// The reference keeps such a per-pointer pre-layout of W1 (kernel/moe_fp8.cu:981-994, 3007-3014).
+__global__ void __launch_bounds__(256) tile_weights_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                                           int mode, int num_experts, Geometry geo)
+{
+    const int k_bytes = mode == 1 ? geo.hidden : geo.inter;
+    const int rows = mode == 1 ? 2 * geo.inter : geo.hidden;
+    const int kblocks = k_bytes / kBlock;
+    const int tiles_n = rows / kTileN;
+    const int lane = threadIdx.x & 31;
+    const long long total_rows = (long long)num_experts * rows;
+    for (long long gr = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); gr < total_rows; gr += (long long)gridDim.x * 8) {
+        const int e = (int)(gr / rows);
+        const int r = (int)(gr - (long long)e * rows);
+        int n, in_tile;
+        if (mode == 1) {
+            const int half = r >= geo.inter;
+            const int rr = r - half * geo.inter;
+            n = rr / kBlock;
+            in_tile = half * kBlock + (rr - n * kBlock);
+        } else {
+            n = r / kTileN;
+            in_tile = r - n * kTileN;
+        }
+        const uint4* s4 = reinterpret_cast<const uint4*>(src + (size_t)gr * k_bytes);
+        uint8_t* tile0 = dst + ((size_t)(e * tiles_n + n) * kblocks * kTileN + in_tile) * kBlock;
+        for (int c = lane; c < k_bytes / 16; c += 32) {
+            const int kb = c >> 3;
+            *reinterpret_cast<uint4*>(tile0 + (size_t)kb * kTileN * kBlock + (c & 7) * 16) = __ldg(s4 + c);
+        }
+    }
+}
+
+cudaError_t launch_tile_weights(int mode, const void* src, void* dst, int num_experts, const Geometry& geo, int num_sms,
+                                cudaStream_t stream)
+{
+    tile_weights_kernel<<<num_sms * 8, 256, 0, stream>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), mode,
+                                                         num_experts, geo);
     return cudaGetLastError();
 }
 

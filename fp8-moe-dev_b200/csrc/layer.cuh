@@ -147,6 +147,7 @@ struct Workspace {
     int m_cap;              // packed-row capacity (multiple of 128)
     int max_tiles;
     Geometry geo;
+    int w_tiled;            // the GEMMs' weight map covers the tile-ordered copy (one 32 KB piece per tile and K block)
 };
 
 }  // namespace moe

@@ -33,6 +33,7 @@ cudaError_t launch_grouped_gemm(int, const void*, const void*, const void*, cons
 int gemm_tiles_n(int mode, const Geometry& geo);
 size_t packed_scale_floats(int mode, int num_experts, const Geometry& geo);
 cudaError_t launch_repack_weight_scales(const float*, const float*, float*, float*, int, const Geometry&, cudaStream_t);
+cudaError_t launch_tile_weights(int, const void*, void*, int, const Geometry&, int, cudaStream_t);
 }  // namespace moe
 
 using namespace moe;
@@ -133,6 +134,15 @@ struct moe_fp8_b200_ctx {
     alignas(64) unsigned char tmap_dec_w2[128];
     const void* cached_w1 = nullptr;
     const void* cached_w2 = nullptr;
+    // tile-ordered copies of the weights for the chain's GEMMs (MOE_FP8_B200_OPT_WEIGHT_PRELAYOUT):
+    // allocated when the option is switched on, filled once per weight pointer
+    int opt_weight_prelayout = 0;
+    uint8_t* w1_tiled = nullptr;
+    uint8_t* w2_tiled = nullptr;
+    const void* tiled_src1 = nullptr;
+    const void* tiled_src2 = nullptr;
+    alignas(64) unsigned char tmap_w1_tiled[128];
+    alignas(64) unsigned char tmap_w2_tiled[128];
     // weight scales in the promotion's order (made once per pair of scale tensors, remembered by address)
     float* sw1_packed = nullptr;
     float* sw2_packed = nullptr;
@@ -297,6 +307,17 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
                                         stream);
         if (e == cudaSuccess) { h->cached_s1 = a.gemm1_weights_scale; h->cached_s2 = a.gemm2_weights_scale; }
     }
+    const bool tiled = h->opt_weight_prelayout != 0;
+    if (e == cudaSuccess && tiled && a.gemm1_weights != h->tiled_src1) {
+        e = launch_tile_weights(1, a.gemm1_weights, h->w1_tiled, E, h->geo, h->num_sms, stream);
+        if (e == cudaSuccess) h->tiled_src1 = a.gemm1_weights;
+    }
+    if (e == cudaSuccess && tiled && a.gemm2_weights != h->tiled_src2) {
+        e = launch_tile_weights(2, a.gemm2_weights, h->w2_tiled, E, h->geo, h->num_sms, stream);
+        if (e == cudaSuccess) h->tiled_src2 = a.gemm2_weights;
+    }
+    Workspace gemm_ws = h->ws;
+    gemm_ws.w_tiled = tiled ? 1 : 0;
     mark(0);
     if (e == cudaSuccess)
         e = launch_route_dispatch(a.routing_logits, a.routing_bias, h->ws, T, (int)a.local_expert_offset, E,
@@ -312,11 +333,12 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
     if (e == cudaSuccess && stop >= 2) e = launch_permute(a.hidden_states, a.hidden_states_scale, h->ws, T, stream);
     mark(3);
     if (e == cudaSuccess && stop >= 3)
-        e = launch_grouped_gemm(1, h->tmap_a1, h->tmap_w1, h->tmap_y, h->ws, h->sw1_packed, h->opt_exact_silu,
-                                ctas(1), split_k, stream);
+        e = launch_grouped_gemm(1, h->tmap_a1, tiled ? h->tmap_w1_tiled : h->tmap_w1, h->tmap_y, gemm_ws, h->sw1_packed,
+                                h->opt_exact_silu, ctas(1), split_k, stream);
     mark(4);
     if (e == cudaSuccess && stop >= 4)
-        e = launch_grouped_gemm(2, h->tmap_a2, h->tmap_w2, h->tmap_y, h->ws, h->sw2_packed, 0, ctas(2), split_k, stream);
+        e = launch_grouped_gemm(2, h->tmap_a2, tiled ? h->tmap_w2_tiled : h->tmap_w2, h->tmap_y, gemm_ws, h->sw2_packed, 0,
+                                ctas(2), split_k, stream);
     mark(5);
     if (e == cudaSuccess && stop >= 5 && finalize) {
         if (ex) {
@@ -538,6 +560,8 @@ int moe_fp8_b200_destroy(moe_fp8_b200_handle h)
     }
     if (h->pipe_in) cudaStreamDestroy(h->pipe_in);
     if (h->pipe_out) cudaStreamDestroy(h->pipe_out);
+    if (h->w1_tiled) cudaFree(h->w1_tiled);
+    if (h->w2_tiled) cudaFree(h->w2_tiled);
     if (h->base) cudaFree(h->base);
     delete h;
     return MOE_FP8_B200_OK;
@@ -564,6 +588,44 @@ int moe_fp8_b200_set_option(moe_fp8_b200_handle h, int option, int value)
             if (value < 1) return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "wait limit must be at least 1 us");
             h->opt_wait_limit_us = value;
             return MOE_FP8_B200_OK;
+        case MOE_FP8_B200_OPT_WEIGHT_PRELAYOUT: {
+            const int on = value ? 1 : 0;
+            if (on == h->opt_weight_prelayout) return MOE_FP8_B200_OK;
+            int prev_device = 0;
+            cudaGetDevice(&prev_device);
+            cudaSetDevice(h->device);
+            struct Restore { int d; ~Restore() { cudaSetDevice(d); } } restore{prev_device};
+            if (!on) {
+                // kernels of earlier runs may still read the copies
+                cudaDeviceSynchronize();
+                cudaFree(h->w1_tiled);
+                cudaFree(h->w2_tiled);
+                h->w1_tiled = h->w2_tiled = nullptr;
+                h->tiled_src1 = h->tiled_src2 = nullptr;
+                h->opt_weight_prelayout = 0;
+                return MOE_FP8_B200_OK;
+            }
+            const size_t E = (size_t)h->num_local_experts;
+            const size_t bytes1 = E * 2 * h->geo.inter * h->geo.hidden, bytes2 = E * h->geo.hidden * h->geo.inter;
+            cudaError_t ce = cudaMalloc(&h->w1_tiled, bytes1);
+            if (ce == cudaSuccess) ce = cudaMalloc(&h->w2_tiled, bytes2);
+            int mr = 0;
+            if (ce == cudaSuccess) mr = encode_kmajor_u8_map(h->tmap_w1_tiled, h->w1_tiled, 128, bytes1 / 128, 0, 256);
+            if (ce == cudaSuccess && mr == 0) mr = encode_kmajor_u8_map(h->tmap_w2_tiled, h->w2_tiled, 128, bytes2 / 128, 0, 256);
+            if (ce != cudaSuccess || mr != 0) {
+                cudaGetLastError();
+                cudaFree(h->w1_tiled);
+                cudaFree(h->w2_tiled);
+                h->w1_tiled = h->w2_tiled = nullptr;
+                if (ce != cudaSuccess)
+                    return fail(h, MOE_FP8_B200_ERR_CUDA, "no room for the tile-ordered weight copies (%zu bytes): %s", bytes1 + bytes2,
+                                cudaGetErrorString(ce));
+                return fail(h, MOE_FP8_B200_ERR_CUDA, "cuTensorMapEncodeTiled(tile-ordered weights) failed: %d", mr);
+            }
+            h->tiled_src1 = h->tiled_src2 = nullptr;
+            h->opt_weight_prelayout = 1;
+            return MOE_FP8_B200_OK;
+        }
         case MOE_FP8_B200_OPT_STAGE_TIMING:
             h->opt_stage_timing = value ? 1 : 0;
             h->timed_runs = 0;
@@ -699,6 +761,7 @@ int moe_fp8_b200_invalidate_weights(moe_fp8_b200_handle h)
     if (!h) return MOE_FP8_B200_ERR_INVALID_ARGUMENT;
     h->cached_w1 = h->cached_w2 = nullptr;
     h->cached_s1 = h->cached_s2 = nullptr;
+    h->tiled_src1 = h->tiled_src2 = nullptr;
     return MOE_FP8_B200_OK;
 }
 

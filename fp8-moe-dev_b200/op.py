@@ -121,6 +121,14 @@ class MoeLayer:
         if rc != _lib.OK:
             self._raise(rc)
 
+    def set_weight_prelayout(self, on: bool):
+        """Tile-ordered copies of the weights for the chain's GEMMs (one contiguous 32 KB piece per tile and K
+        block): allocates num_local_experts x the size of one expert's weights on the handle's device, filled
+        once per weight pointer.  Same results; for batches that are bound by streaming the weights."""
+        rc = self._lib.moe_fp8_b200_set_option(self._h, _lib.OPT_WEIGHT_PRELAYOUT, int(bool(on)))
+        if rc != _lib.OK:
+            self._raise(rc)
+
     def inject_device_status(self, status: int, stale_barrier_arrivals: int = 0):
         """Host-side failure injection for tests of the error path (see the header)."""
         stream = torch.cuda.current_stream(self.device).cuda_stream

@@ -97,7 +97,16 @@ enum {
      * rows (default 1 000 000).  When it runs out the kernel completes with zero rows, the device status
      * word records it and moe_fp8_b200_check returns MOE_FP8_B200_ERR_DEVICE; the GPU never hangs on a
      * peer that does not arrive.  The waits inside the GEMM and decode kernels keep their fixed 1 s. */
-    MOE_FP8_B200_OPT_WAIT_LIMIT_US = 7
+    MOE_FP8_B200_OPT_WAIT_LIMIT_US = 7,
+    /* 1: the chain's GEMMs read the weights from tile-ordered copies kept by the handle (the operand of one
+     * (expert, n tile, K block) is one contiguous 32 KB piece instead of 256 pieces of 128 bytes a weight row
+     * apart), which is what a batch that is bound by streaming the weights wants.  Switching it on allocates
+     * num_local_experts x 44 MB (reference geometry) on the handle's device, outside the workspace; the copies are
+     * filled by one kernel in front of the first run that sees a weight pointer and remembered by address, like
+     * the scale layout (moe_fp8_b200_invalidate_weights drops them).  Results are bit-identical either way.
+     * Replaces the reference's per-pointer W1 pre-layout cache (kernel/moe_fp8.cu:981-994, 3007-3014).
+     * Default 0.  The decode kernel (batches of at most 8 tokens) always reads the caller's weights. */
+    MOE_FP8_B200_OPT_WEIGHT_PRELAYOUT = 8
 };
 #define MOE_FP8_B200_DECODE_MAX_TOKENS 8
 

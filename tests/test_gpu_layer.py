@@ -750,3 +750,55 @@ def test_weight_scale_prelayout_follows_pointers_and_invalidation(pkg, layer32):
     layer32.invalidate_weights()
     assert torch.equal(run(s1b, s2b), base)
     layer32.invalidate_weights()
+
+
+@pytest.mark.parametrize("T,offset", [(9, 0), (40, 32), (300, 96), (1024, 0)])
+def test_tile_ordered_weight_copies_change_nothing(pkg, T, offset):
+    """MOE_FP8_B200_OPT_WEIGHT_PRELAYOUT: the GEMMs read the weights from the handle's tile-ordered copies (one
+    contiguous 32 KB piece per tile and K block) and every bit of the result stays the same, also after the option
+    has been switched off again (the copies are freed) and on once more."""
+    dev = [x.cuda() for x in hp.cpu_inputs(T, seed=6100 + T)]
+    w = hp.gpu_shard(offset, 32)
+    lay = pkg.MoeLayer(T, 32, 0)
+    try:
+        lay.set_decode_kernel(False)
+        outs = []
+        for on in (False, True, False, True):
+            lay.set_weight_prelayout(on)
+            out = torch.zeros(T, H, dtype=torch.bfloat16, device="cuda")
+            lay.run(*dev, *w, offset, RSF, out)
+            lay.check()
+            outs.append(out)
+        assert outs[0].float().abs().sum() > 0
+        for o in outs[1:]:
+            assert torch.equal(o.view(torch.int16), outs[0].view(torch.int16))
+    finally:
+        lay.close()
+
+
+def test_tile_ordered_weight_copies_follow_pointers_and_invalidation(pkg):
+    T = 64
+    dev = [x.cuda() for x in hp.cpu_inputs(T, seed=6200)]
+    w1, s1, w2, s2 = hp.gpu_shard(0, 32)
+    lay = pkg.MoeLayer(T, 32, 0)
+    try:
+        lay.set_weight_prelayout(True)
+        out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+
+        def run(wa, wb):
+            lay.run(*dev, wa, s1, wb, s2, 0, RSF, out)
+            lay.check()
+            return out.clone()
+
+        base = run(w1, w2)
+        w1b = w1.clone()
+        w1b.view(torch.uint8)[:, :, :128] ^= 0x80          # flip the signs of the first K block of every row
+        w2b = w2.clone()
+        changed = run(w1b, w2b)                            # other addresses: seen at once
+        assert not torch.equal(changed, base)
+        w1b.copy_(w1)                                      # same addresses, old contents back
+        assert torch.equal(run(w1b, w2b), changed), "the copies are keyed by address"
+        lay.invalidate_weights()
+        assert torch.equal(run(w1b, w2b), base)
+    finally:
+        lay.close()

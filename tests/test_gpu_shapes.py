@@ -259,3 +259,20 @@ def test_paths_that_exist_for_the_reference_geometry_only_are_refused(pkg):
         assert torch.isfinite(out.float()).all()
     finally:
         layer.close()
+
+
+@pytest.mark.parametrize("hidden,inter", [(1024, 512), (2048, 768), (256, 4096)])
+def test_tile_ordered_weight_copies_of_another_geometry(pkg, hidden, inter):
+    """The weight pre-layout option with other hidden / intermediate sizes: bit-identical results."""
+    T, offset = 150, 64
+    layer = pkg.MoeLayer(256, 32, 0, hidden=hidden, intermediate=inter)
+    try:
+        inputs = _inputs(T, 1300, hidden)
+        weights = _shard(offset, 32, hidden, inter)
+        plain = _run(layer, inputs, weights, offset, hidden)
+        layer.set_weight_prelayout(True)
+        tiled = _run(layer, inputs, weights, offset, hidden)
+        assert plain.float().abs().sum() > 0
+        assert torch.equal(plain.view(torch.int16), tiled.view(torch.int16))
+    finally:
+        layer.close()
