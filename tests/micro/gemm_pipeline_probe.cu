@@ -1,5 +1,5 @@
 // Micro-benchmark of the grouped GEMM's inner pipeline on ONE SM (or one CTA on each of N SMs), without
-// TMA and without real data: the MMA-issuing thread, the two 256-column TMEM accumulator stages and the
+// real data and (but for the *_tma forms) without TMA: the MMA-issuing thread, the two 256-column TMEM accumulator stages and the
 // eight promotion warps with the kernel's own handshake (ptx.cuh of the package).  It reports SM cycles
 // per 128-wide K block for a few forms of the loop, which is where the figures quoted in the design notes
 // about the promotion pipeline come from:
@@ -15,10 +15,19 @@
 //                       load issued one block ahead, two multiplies): the kernel's loop minus TMA and tiles
 //   ring_scales_relayed the stage is freed by a promotion warp's plain arrive instead of a second commit
 //   ring_scales_two     two MMA-issuing threads, one per accumulator stage
+//   ring_scales_tma     ring_scales with a real producer: per K block one 128 x 128-byte and one 256 x 128-byte TMA
+//                       box (48 KB) from a 58 MB buffer into a three-stage ring, as in the kernel; groups of six CTAs
+//                       share their weight boxes, so that with many CTAs the boxes come from L2 as they do there
+//   ring_scales_two_tma the same with two issuing threads
+//   ring_far_tma, ring_far_two_tma     the row-scale load of the next K block reads a new line of a 7 MB array
+//                       every block (an L1 miss, as in the kernel) instead of a 4 KB array
+//   ring_far2_two_tma   ... issued two K blocks ahead
+//   ring_farlate_tma, ring_farlate_two_tma   ... issued after the wait for the accumulator stage, not before it
 // Build: nvcc -std=c++17 -O3 -gencode arch=compute_100a,code=sm_100a -I <package>/csrc gemm_pipeline_probe.cu
 // Run:   ./a.out [ctas=1] [k_blocks=4000]     (every wait is bounded; a failed wait ends the kernel)
 #include <cstdio>
 #include <cstdlib>
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include "ptx.cuh"
@@ -33,7 +42,14 @@ enum : int {
     F_SCALES = 32,      // per-block scale handling in the promotion warps
     F_RELAY = 64,       // a promotion warp frees the operand stage
     F_TWO = 128,        // two issuing threads (warps 1 and 3)
+    F_TMA = 256,        // a real TMA producer behind the ring
+    F_FAR = 512,        // the per-block scale load misses L1 (a new line of a large array per K block, as in the kernel)
+    F_AHEAD2 = 1024,    // ... and is issued two K blocks ahead instead of one
+    F_LATE = 2048,      // ... or is issued after the wait for the accumulator stage instead of before it
 };
+constexpr int kScaleRows = 32768;   // the far scale array: [56 K blocks][kScaleRows] floats (7 MB)
+constexpr int kOperandRows = 8192, kOperandK = 7168;   // the buffer the TMA forms read (58 MB)
+constexpr int kStageBytes = 48 * 1024;
 
 __device__ __forceinline__ void wait_loads(uint32_t (&a)[32], uint32_t (&b)[32]) {
     // tcgen05.wait::ld with the destination registers as in/out operands (no use may move above it)
@@ -69,10 +85,12 @@ constexpr int kRingStages = 3;
 constexpr int kRingBars = 6;
 
 template <int FORM>
-__global__ void __launch_bounds__(384, 1) probe(float* out, long long* cycles, int iters) {
+__global__ void __launch_bounds__(384, 1) probe(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                                float* out, long long* cycles, int iters) {
     constexpr bool kN128 = FORM & F_N128, kLoads = FORM & F_LOADS, kFma = FORM & (F_FMA_SCALAR | F_FMA_PACKED);
     constexpr bool kPacked = FORM & F_FMA_PACKED, kRing = FORM & F_RING, kScales = FORM & F_SCALES;
-    constexpr bool kRelay = FORM & F_RELAY, kTwo = FORM & F_TWO;
+    constexpr bool kRelay = FORM & F_RELAY, kTwo = FORM & F_TWO, kTma = FORM & F_TMA;
+    constexpr bool kFar = FORM & F_FAR, kAhead2 = FORM & F_AHEAD2, kLate = FORM & F_LATE;
     __shared__ uint32_t slot;
     __shared__ uint64_t acc_full[2], acc_empty[2];
     __shared__ uint64_t st_full[kRingBars], st_empty[kRingBars];
@@ -95,19 +113,34 @@ __global__ void __launch_bounds__(384, 1) probe(float* out, long long* cycles, i
         setmaxnreg_dec<56>();
         if (kRing && warp == 0 && lane == 0) {
             // stand-in for the TMA producer: same barrier traffic, no data
-            for (int it = 0; it < iters; ++it) {
+            int it = 0;
+            for (; it < iters; ++it) {
                 if (it >= kRingStages) {
                     const int pit = it - kRingStages;   // the K block that last used this stage
                     if (!mbar_wait(smem_u32(&st_empty[pit % kRingBars]), (pit / kRingBars) & 1, abort_flag)) break;
                 }
-                mbar_arrive(smem_u32(&st_full[it % kRingBars]));
+                const uint32_t full = smem_u32(&st_full[it % kRingBars]);
+                if (kTma) {
+                    const uint32_t dst = ((smem_u32(tiles) + 1023u) & ~1023u) + (uint32_t)(it % kRingStages) * kStageBytes;
+                    const int kb = it % (kOperandK / 128), tile = it / (kOperandK / 128);
+                    mbar_expect_tx(full, kStageBytes);
+                    tma_load_2d(dst, &map_a, full, kb * 128, (int)(((blockIdx.x * 7u + tile) * 128u) % kOperandRows));
+                    tma_load_2d(dst + 16384, &map_b, full, kb * 128, (int)((((blockIdx.x / 6u) * 13u + tile) * 256u) % kOperandRows));
+                } else {
+                    mbar_arrive(full);
+                }
+            }
+            if (kTma && it < iters) {
+                // a wait ran out: leave only after the copies still in flight have landed (bounded)
+                for (int j = it > kRingStages ? it - kRingStages : 0; j < it; ++j)
+                    mbar_wait(smem_u32(&st_full[j % kRingBars]), (j / kRingBars) & 1, abort_flag);
             }
         }
         if ((warp == 1 || (kTwo && warp == 3)) && lane == 0) {
             const uint32_t mine = warp == 3 ? 1u : 0u;
             const int step = kTwo ? 2 : 1;
-            const uint32_t tb = (smem_u32(tiles) + 1023u) & ~1023u;   // operand bytes are whatever the SM holds
-            const uint64_t ad = make_kmajor_sw128_desc(tb), bd = make_kmajor_sw128_desc(tb + 16384);
+            const uint32_t tb = (smem_u32(tiles) + 1023u) & ~1023u;   // without TMA the operand bytes are whatever the SM holds
+            uint64_t ad = make_kmajor_sw128_desc(tb), bd = make_kmajor_sw128_desc(tb + 16384);
             const uint32_t idesc = make_idesc_e4m3(128, 256), idesc128 = make_idesc_e4m3(128, 128);
             const long long t0 = clock64();
             bool next_ready = false;
@@ -117,6 +150,11 @@ __global__ void __launch_bounds__(384, 1) probe(float* out, long long* cycles, i
                 if (kRing && !next_ready && !mbar_wait(smem_u32(&st_full[it % kRingBars]), (it / kRingBars) & 1, abort_flag)) break;
                 if (!mbar_wait(smem_u32(&acc_empty[as]), aph ^ 1, abort_flag)) break;
                 tc_fence_after();
+                if (kTma) {
+                    const uint32_t st = tb + (uint32_t)(it % kRingStages) * kStageBytes;
+                    ad = make_kmajor_sw128_desc(st);
+                    bd = make_kmajor_sw128_desc(st + 16384);
+                }
                 if (kN128) {
                     for (int hh = 0; hh < 2; ++hh)
                         for (int kk = 0; kk < 4; ++kk)
@@ -138,7 +176,8 @@ __global__ void __launch_bounds__(384, 1) probe(float* out, long long* cycles, i
 #pragma unroll
         for (int j = 0; j < 128; ++j) acc[j] = 0.f;
         uint32_t r0[32], r1[32];
-        float sa_n = 1.0f;
+        float sa_n = 1.0f, sa_n2 = 1.0f;
+        const float* far = out + 4096 + (blockIdx.x * 128 + (warp & 3) * 32 + lane) % (kScaleRows - 4096);
         for (int it = 0; it < iters; ++it) {
             const uint32_t as = it & 1, aph = (it >> 1) & 1;
             float s_lo = 1.0f + it * 1e-9f, s_hi = 1.0f - it * 1e-9f;
@@ -146,12 +185,31 @@ __global__ void __launch_bounds__(384, 1) probe(float* out, long long* cycles, i
                 const float lo_w = __shfl_sync(0xffffffffu, s_lo, it & 31), hi_w = __shfl_sync(0xffffffffu, s_hi, it & 31);
                 s_lo = sa_n * lo_w;
                 s_hi = sa_n * hi_w;
-                asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(sa_n) : "l"(out + 1024 + ((it * 128 + threadIdx.x) & 1023)));
+                if (kFar && !kLate) {
+                    // row scale of K block it + 1 (or it + 2): line (it % 56) of the [56][rows] array, at a row offset
+                    // that moves with the tile, so that no line is met twice in a row
+                    const int nit = it + (kAhead2 ? 2 : 1);
+                    const float* src = far + (size_t)(nit % 56) * kScaleRows + (size_t)((nit / 56) % 32) * 128;
+                    if (kAhead2) {
+                        sa_n = sa_n2;
+                        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(sa_n2) : "l"(src));
+                    } else {
+                        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(sa_n) : "l"(src));
+                    }
+                } else if (!kFar) {
+                    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(sa_n) : "l"(out + 1024 + ((it * 128 + threadIdx.x) & 1023)));
+                }
             }
             bool ok = mbar_wait(smem_u32(&acc_full[as]), aph, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
+            if (kScales && kFar && kLate) {
+                const int nit = it + 1;
+                asm volatile("ld.global.nc.f32 %0, [%1];"
+                             : "=f"(sa_n)
+                             : "l"(far + (size_t)(nit % 56) * kScaleRows + (size_t)((nit / 56) % 32) * 128));
+            }
             if (kRing && kRelay && warp == 4 && lane == 0) mbar_arrive(smem_u32(&st_empty[it % kRingBars]));
             if (!kLoads) {
                 tc_fence_before();
@@ -185,11 +243,31 @@ __global__ void __launch_bounds__(384, 1) probe(float* out, long long* cycles, i
     if (threadIdx.x == 0 && blockIdx.x == 0) cycles[1] = abort_word;
 }
 
+static CUtensorMap g_map_a, g_map_b;
+
+// [kOperandRows, kOperandK] bytes, K contiguous; box = 128 bytes x box_rows with the 128-byte swizzle
+static bool encode_map(CUtensorMap* m, void* base, uint32_t box_rows) {
+    typedef CUresult (*Fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                           const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                           CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || !p) return false;
+    const cuuint64_t dims[2] = {kOperandK, kOperandRows};
+    const cuuint64_t strides[1] = {kOperandK};
+    const cuuint32_t box[2] = {128, box_rows};
+    const cuuint32_t es[2] = {1, 1};
+    return reinterpret_cast<Fn>(p)(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int FORM>
 static int run(const char* name, int ctas, int iters, float* out, long long* d) {
-    cudaFuncSetAttribute(probe<FORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 50 * 1024);
+    const int smem = (FORM & F_TMA) ? 3 * kStageBytes + 2048 : 50 * 1024;
+    cudaFuncSetAttribute(probe<FORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     cudaMemset(d, 0, 64);
-    probe<FORM><<<ctas, 384, 50 * 1024>>>(out, d, iters);
+    probe<FORM><<<ctas, 384, smem>>>(g_map_a, g_map_b, out, d, iters);
     const cudaError_t e = cudaDeviceSynchronize();
     long long h[2] = {0, 0};
     cudaMemcpy(h, d, sizeof h, cudaMemcpyDeviceToHost);
@@ -203,9 +281,17 @@ int main(int argc, char** argv) {
     const int iters = argc > 2 ? atoi(argv[2]) : 4000;
     float* out;
     long long* d;
-    cudaMalloc(&out, 16384);
-    cudaMemset(out, 0, 16384);
+    const size_t out_bytes = 16384 + sizeof(float) * 56 * (size_t)kScaleRows;
+    cudaMalloc(&out, out_bytes);
+    cudaMemset(out, 0, out_bytes);
     cudaMalloc(&d, 64);
+    void* operands;
+    cudaMalloc(&operands, (size_t)kOperandRows * kOperandK);
+    cudaMemset(operands, 0x31, (size_t)kOperandRows * kOperandK);   // e4m3 0.625 everywhere: finite products
+    if (!encode_map(&g_map_a, operands, 128) || !encode_map(&g_map_b, operands, 256)) {
+        printf("cuTensorMapEncodeTiled failed\n");
+        return 1;
+    }
     printf("ctas %d, K blocks %d\n", ctas, iters);
     constexpr int kPromote = F_LOADS | F_FMA_PACKED;
     int bad = 0;
@@ -218,5 +304,12 @@ int main(int argc, char** argv) {
     bad |= run<kPromote | F_RING | F_SCALES>("ring_scales", ctas, iters, out, d);
     bad |= run<kPromote | F_RING | F_SCALES | F_RELAY>("ring_scales_relayed", ctas, iters, out, d);
     bad |= run<kPromote | F_RING | F_SCALES | F_TWO>("ring_scales_two", ctas, iters, out, d);
+    bad |= run<kPromote | F_RING | F_SCALES | F_TMA>("ring_scales_tma", ctas, iters, out, d);
+    bad |= run<kPromote | F_RING | F_SCALES | F_TWO | F_TMA>("ring_scales_two_tma", ctas, iters, out, d);
+    bad |= run<kPromote | F_RING | F_SCALES | F_TMA | F_FAR>("ring_far_tma", ctas, iters, out, d);
+    bad |= run<kPromote | F_RING | F_SCALES | F_TWO | F_TMA | F_FAR>("ring_far_two_tma", ctas, iters, out, d);
+    bad |= run<kPromote | F_RING | F_SCALES | F_TWO | F_TMA | F_FAR | F_AHEAD2>("ring_far2_two_tma", ctas, iters, out, d);
+    bad |= run<kPromote | F_RING | F_SCALES | F_TMA | F_FAR | F_LATE>("ring_farlate_tma", ctas, iters, out, d);
+    bad |= run<kPromote | F_RING | F_SCALES | F_TWO | F_TMA | F_FAR | F_LATE>("ring_farlate_two_tma", ctas, iters, out, d);
     return bad;
 }

@@ -34,3 +34,11 @@ def test_gemm_pipeline_probe(tmp_path):
     # ... and a second issuing thread takes most of it back (in this probe; see the design notes for the kernel)
     assert cyc["ring_scales_two"] < cyc["ring_scales"] - 100, cyc
     assert cyc["ring_scales_relayed"] < cyc["ring_scales"], cyc
+    # a real TMA producer behind the ring (48 KB per K block) changes little: the data movement is not the cost
+    assert abs(cyc["ring_scales_tma"] - cyc["ring_scales"]) < 60, cyc
+    assert abs(cyc["ring_scales_two_tma"] - cyc["ring_scales_two"]) < 60, cyc
+    # a row-scale load that misses L1, pending while the warp polls the accumulator barrier, holds the warp up
+    # (issuing it two blocks ahead does not help); issued after the wait it is free again
+    assert cyc["ring_far_tma"] > cyc["ring_scales_tma"] + 80, cyc
+    assert cyc["ring_far2_two_tma"] > cyc["ring_scales_two_tma"] + 150, cyc
+    assert cyc["ring_farlate_two_tma"] < cyc["ring_far_two_tma"] - 150, cyc
