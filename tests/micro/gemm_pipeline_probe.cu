@@ -24,9 +24,11 @@
 //   ring_far2_two_tma   ... issued two K blocks ahead
 //   ring_farlate_tma, ring_farlate_two_tma   ... issued after the wait for the accumulator stage, not before it
 // Build: nvcc -std=c++17 -O3 -gencode arch=compute_100a,code=sm_100a -I <package>/csrc gemm_pipeline_probe.cu
-// Run:   ./a.out [ctas=1] [k_blocks=4000]     (every wait is bounded; a failed wait ends the kernel)
+//   ring_scales_tma_m64 ring_scales_tma with M = 64 instructions
+// Run:   ./a.out [ctas=1] [k_blocks=4000] [name filter]   (every wait is bounded; a failed wait ends the kernel)
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -46,6 +48,7 @@ enum : int {
     F_FAR = 512,        // the per-block scale load misses L1 (a new line of a large array per K block, as in the kernel)
     F_AHEAD2 = 1024,    // ... and is issued two K blocks ahead instead of one
     F_LATE = 2048,      // ... or is issued after the wait for the accumulator stage instead of before it
+    F_M64 = 4096,       // M = 64 instructions (same operands in shared memory, half of the rows multiplied)
 };
 constexpr int kScaleRows = 32768;   // the far scale array: [56 K blocks][kScaleRows] floats (7 MB)
 constexpr int kOperandRows = 8192, kOperandK = 7168;   // the buffer the TMA forms read (58 MB)
@@ -90,7 +93,7 @@ __global__ void __launch_bounds__(384, 1) probe(const __grid_constant__ CUtensor
     constexpr bool kN128 = FORM & F_N128, kLoads = FORM & F_LOADS, kFma = FORM & (F_FMA_SCALAR | F_FMA_PACKED);
     constexpr bool kPacked = FORM & F_FMA_PACKED, kRing = FORM & F_RING, kScales = FORM & F_SCALES;
     constexpr bool kRelay = FORM & F_RELAY, kTwo = FORM & F_TWO, kTma = FORM & F_TMA;
-    constexpr bool kFar = FORM & F_FAR, kAhead2 = FORM & F_AHEAD2, kLate = FORM & F_LATE;
+    constexpr bool kFar = FORM & F_FAR, kAhead2 = FORM & F_AHEAD2, kLate = FORM & F_LATE, kM64 = FORM & F_M64;
     __shared__ uint32_t slot;
     __shared__ uint64_t acc_full[2], acc_empty[2];
     __shared__ uint64_t st_full[kRingBars], st_empty[kRingBars];
@@ -141,7 +144,7 @@ __global__ void __launch_bounds__(384, 1) probe(const __grid_constant__ CUtensor
             const int step = kTwo ? 2 : 1;
             const uint32_t tb = (smem_u32(tiles) + 1023u) & ~1023u;   // without TMA the operand bytes are whatever the SM holds
             uint64_t ad = make_kmajor_sw128_desc(tb), bd = make_kmajor_sw128_desc(tb + 16384);
-            const uint32_t idesc = make_idesc_e4m3(128, 256), idesc128 = make_idesc_e4m3(128, 128);
+            const uint32_t idesc = make_idesc_e4m3(kM64 ? 64 : 128, 256), idesc128 = make_idesc_e4m3(128, 128);
             const long long t0 = clock64();
             bool next_ready = false;
             for (int it = 0; it < iters; ++it) {
@@ -243,7 +246,18 @@ __global__ void __launch_bounds__(384, 1) probe(const __grid_constant__ CUtensor
     if (threadIdx.x == 0 && blockIdx.x == 0) cycles[1] = abort_word;
 }
 
+// pseudo-random e4m3 bytes with the top exponent bit clear (finite, |x| < 2), so that the tensor pipe toggles as
+// it does on real operands
+__global__ void fill_operands(uint32_t* p, size_t words) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < words; i += (size_t)gridDim.x * blockDim.x) {
+        uint32_t x = (uint32_t)i * 2654435761u + 12345u;
+        x ^= x >> 15; x *= 2246822519u; x ^= x >> 13;
+        p[i] = x & 0xBFBFBFBFu;
+    }
+}
+
 static CUtensorMap g_map_a, g_map_b;
+static const char* g_only = nullptr;   // argv[3]: run only the forms whose name contains it
 
 // [kOperandRows, kOperandK] bytes, K contiguous; box = 128 bytes x box_rows with the 128-byte swizzle
 static bool encode_map(CUtensorMap* m, void* base, uint32_t box_rows) {
@@ -266,19 +280,28 @@ template <int FORM>
 static int run(const char* name, int ctas, int iters, float* out, long long* d) {
     const int smem = (FORM & F_TMA) ? 3 * kStageBytes + 2048 : 50 * 1024;
     cudaFuncSetAttribute(probe<FORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (g_only && !strstr(name, g_only)) return 0;
     cudaMemset(d, 0, 64);
+    cudaEvent_t ev0, ev1;
+    cudaEventCreate(&ev0);
+    cudaEventCreate(&ev1);
+    cudaEventRecord(ev0);
     probe<FORM><<<ctas, 384, smem>>>(g_map_a, g_map_b, out, d, iters);
+    cudaEventRecord(ev1);
     const cudaError_t e = cudaDeviceSynchronize();
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, ev0, ev1);
     long long h[2] = {0, 0};
     cudaMemcpy(h, d, sizeof h, cudaMemcpyDeviceToHost);
-    printf("%-20s %8.1f cycles per K block   (%s%s)\n", name, (double)h[0] / iters, cudaGetErrorString(e),
-           h[1] ? ", a wait ran out" : "");
+    printf("%-20s %8.1f cycles per K block   (%s%s)   %.1f ns per K block\n", name, (double)h[0] / iters, cudaGetErrorString(e),
+           h[1] ? ", a wait ran out" : "", ms * 1e6 / iters);
     return (e == cudaSuccess && h[1] == 0) ? 0 : 1;
 }
 
 int main(int argc, char** argv) {
     const int ctas = argc > 1 ? atoi(argv[1]) : 1;
     const int iters = argc > 2 ? atoi(argv[2]) : 4000;
+    g_only = argc > 3 ? argv[3] : nullptr;
     float* out;
     long long* d;
     const size_t out_bytes = 16384 + sizeof(float) * 56 * (size_t)kScaleRows;
@@ -287,7 +310,7 @@ int main(int argc, char** argv) {
     cudaMalloc(&d, 64);
     void* operands;
     cudaMalloc(&operands, (size_t)kOperandRows * kOperandK);
-    cudaMemset(operands, 0x31, (size_t)kOperandRows * kOperandK);   // e4m3 0.625 everywhere: finite products
+    fill_operands<<<1024, 256>>>(static_cast<uint32_t*>(operands), (size_t)kOperandRows * kOperandK / 4);
     if (!encode_map(&g_map_a, operands, 128) || !encode_map(&g_map_b, operands, 256)) {
         printf("cuTensorMapEncodeTiled failed\n");
         return 1;
@@ -309,6 +332,7 @@ int main(int argc, char** argv) {
     bad |= run<kPromote | F_RING | F_SCALES | F_TMA | F_FAR>("ring_far_tma", ctas, iters, out, d);
     bad |= run<kPromote | F_RING | F_SCALES | F_TWO | F_TMA | F_FAR>("ring_far_two_tma", ctas, iters, out, d);
     bad |= run<kPromote | F_RING | F_SCALES | F_TWO | F_TMA | F_FAR | F_AHEAD2>("ring_far2_two_tma", ctas, iters, out, d);
+    bad |= run<kPromote | F_RING | F_SCALES | F_TMA | F_M64>("ring_scales_tma_m64", ctas, iters, out, d);
     bad |= run<kPromote | F_RING | F_SCALES | F_TMA | F_FAR | F_LATE>("ring_farlate_tma", ctas, iters, out, d);
     bad |= run<kPromote | F_RING | F_SCALES | F_TWO | F_TMA | F_FAR | F_LATE>("ring_farlate_two_tma", ctas, iters, out, d);
     return bad;
