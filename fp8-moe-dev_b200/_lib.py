@@ -16,6 +16,7 @@ ERR_INVALID_ARGUMENT, ERR_CUDA, ERR_CAPACITY, ERR_DEVICE, ERR_UNSUPPORTED = -1, 
 OPT_REFERENCE_PRUNING, OPT_EXACT_SILU, OPT_STAGE_TIMING = 1, 2, 3
 OPT_STOP_AFTER_STAGE, OPT_DECODE_KERNEL, OPT_EXPERT_STRIDE, OPT_WAIT_LIMIT_US = 4, 5, 6, 7
 OPT_WEIGHT_PRELAYOUT = 8
+OPT_SMALL_BATCH_RING = 9
 DECODE_MAX_TOKENS = 8
 
 BUF = dict(

@@ -94,6 +94,15 @@ constexpr size_t gemm_smem_bytes() {
            (SPLITK ? sizeof(GemmScratch) : (size_t)kTileStageBytes);
 }
 static_assert(gemm_smem_bytes<2, false>() <= 227 * 1024 && gemm_smem_bytes<1, true>() <= 227 * 1024, "shared memory");
+// Batches of at most 64 tokens: an expert has at most 64 rows, so the activation box is 64 rows high (8 KB instead
+// of 16 KB per stage; the MMAs still multiply 128 rows, the upper 64 read whatever follows and are never stored)
+// and the room goes to a fourth operand stage: 128 KB instead of 96 KB of weights in flight per SM, which is what
+// a batch that only streams weights wants.
+constexpr int kSmallATileBytes = kATileBytes / 2;
+constexpr int kSmallAStages = 4;
+constexpr int kSmallAMaxTokens = 64;
+constexpr size_t kSmallASmemBytes = 1024 + (size_t)kSmallAStages * (kSmallATileBytes + kBTileBytes) + kGemmCoreBytes + kTileStageBytes;
+static_assert(kSmallASmemBytes <= 227 * 1024, "shared memory");
 
 struct TileCoord {
     int e, n, row0, rows;
@@ -225,7 +234,7 @@ __device__ __forceinline__ float round_bf16(float x) {
 // GENERIC takes hidden / intermediate from Workspace::geo instead of the reference's 7168 / 2048
 // (hidden a multiple of 256, intermediate of 128, at most 64 K blocks each); the reference's
 // geometry keeps its compile-time instantiation.
-template <int MODE, bool SPLITK, bool GENERIC = false>
+template <int MODE, bool SPLITK, bool GENERIC = false, bool SMALLA = false>
 __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
     const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
     const __grid_constant__ CUtensorMap tmap_out, Workspace ws, const float2* __restrict__ w_scale_packed, int silu_exact)
@@ -235,12 +244,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
     const int inter = GENERIC ? ws.geo.inter : kInter;
     const int kKBlocks = ((MODE == 1) ? hidden : inter) / kBlock;                   // 56 / 16
     const int kTilesN = (MODE == 1) ? (inter / kBlock) : (hidden / kTileN);         // 16 / 28
-    constexpr int kStages = gemm_stages<SPLITK>();
+    static_assert(!(SMALLA && (SPLITK || GENERIC)), "the 64-row activation box is a variant of the plain kernel");
+    constexpr int kStages = SMALLA ? kSmallAStages : gemm_stages<SPLITK>();
+    constexpr int kABytes = SMALLA ? kSmallATileBytes : kATileBytes;
+    constexpr int kStageSize = kABytes + kBTileBytes;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
-    GemmShared* sh = reinterpret_cast<GemmShared*>(smem_raw + (base - raw_addr) + (size_t)kStages * kStageBytes);
+    GemmShared* sh = reinterpret_cast<GemmShared*>(smem_raw + (base - raw_addr) + (size_t)kStages * kStageSize);
     uint8_t* after_core = reinterpret_cast<uint8_t*>(sh) + kGemmCoreBytes;   // 1 KB aligned
     GemmScratch* sc = reinterpret_cast<GemmScratch*>(after_core);           // split-K kernels only
     (void)sc;
@@ -304,9 +316,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                     const uint32_t ph = (it / kStages) & 1u;
                     if (!mbar_wait(smem_u32(&sh->empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
                     const uint32_t full = smem_u32(&sh->full[s]);
-                    mbar_expect_tx(full, kStageBytes);
-                    const uint32_t a_dst = base + s * kStageBytes;
-                    const uint32_t b_dst = a_dst + kATileBytes;
+                    mbar_expect_tx(full, kStageSize);
+                    const uint32_t a_dst = base + s * kStageSize;
+                    const uint32_t b_dst = a_dst + kABytes;
                     tma_load_2d(a_dst, &tmap_a, full, kb * kBlock, tc.row0);
                     if (ws.w_tiled) {
                         // tile-ordered copy of the weights: the operand of (expert, n tile, K block) is one
@@ -351,9 +363,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(
                     // probed while the previous block's MMAs ran (next_full_ready), which keeps
                     // that probe's latency off the release -> issue chain below.
                     if (!next_full_ready && !mbar_wait(smem_u32(&sh->full[s]), ph, abort_flag)) { ok = false; break; }
-                    const uint32_t a_addr = base + s * kStageBytes;
+                    const uint32_t a_addr = base + s * kStageSize;
                     const uint64_t adesc = make_kmajor_sw128_desc(a_addr);
-                    const uint64_t bdesc = make_kmajor_sw128_desc(a_addr + kATileBytes);
+                    const uint64_t bdesc = make_kmajor_sw128_desc(a_addr + kABytes);
                     const uint32_t d = tmem_base + as * kTileN;
                     if (!mbar_wait(smem_u32(&sh->acc_empty[as]), aph ^ 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after();
@@ -893,13 +905,20 @@ cudaError_t configure_gemm_kernels()
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(grouped_gemm_kernel<2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)gemm_smem_bytes<2, false>());
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(grouped_gemm_kernel<1, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kSmallASmemBytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(grouped_gemm_kernel<2, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kSmallASmemBytes);
     return e;
 }
 
 int gemm_tiles_n(int mode, const Geometry& geo) { return mode == 1 ? geo.inter / kBlock : geo.hidden / kTileN; }
 
 cudaError_t launch_grouped_gemm(int mode, const void* tmap_a, const void* tmap_b, const void* tmap_out, const Workspace& ws,
-                                const float* w_scale_packed, int silu_exact, int num_ctas, int split_k, cudaStream_t stream)
+                                const float* w_scale_packed, int silu_exact, int num_ctas, int split_k, int small_a,
+                                cudaStream_t stream)
 {
     const float2* w_scale = reinterpret_cast<const float2*>(w_scale_packed);
     const CUtensorMap* ma = static_cast<const CUtensorMap*>(tmap_a);
@@ -920,6 +939,13 @@ cudaError_t launch_grouped_gemm(int mode, const void* tmap_a, const void* tmap_b
         if (split_k) return cudaErrorInvalidValue;
         if (mode == 1) return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<1, false, true>, *ma, *mb, *mo, ws, w_scale, silu_exact);
         return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<2, false, true>, *ma, *mb, *mo, ws, w_scale, silu_exact);
+    }
+    if (small_a && !split_k) {
+        // at most 64 tokens: tmap_a is the 64-row view of the packed activations
+        cfg.dynamicSmemBytes = kSmallASmemBytes;
+        if (mode == 1)
+            return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<1, false, false, true>, *ma, *mb, *mo, ws, w_scale, silu_exact);
+        return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<2, false, false, true>, *ma, *mb, *mo, ws, w_scale, silu_exact);
     }
     if (mode == 1) {
         cfg.dynamicSmemBytes = split_k ? gemm_smem_bytes<1, true>() : gemm_smem_bytes<1, false>();

@@ -28,7 +28,7 @@ int encode_rows_1k_map(void*, const void*, uint64_t, uint64_t, uint32_t);
 int encode_out_bf16_map(void*, void*, uint64_t, uint64_t);
 size_t tensor_map_bytes();
 cudaError_t configure_gemm_kernels();
-cudaError_t launch_grouped_gemm(int, const void*, const void*, const void*, const Workspace&, const float*, int, int, int,
+cudaError_t launch_grouped_gemm(int, const void*, const void*, const void*, const Workspace&, const float*, int, int, int, int,
                                 cudaStream_t);
 int gemm_tiles_n(int mode, const Geometry& geo);
 size_t packed_scale_floats(int mode, int num_experts, const Geometry& geo);
@@ -127,6 +127,9 @@ struct moe_fp8_b200_ctx {
     Workspace ws{};
     alignas(64) unsigned char tmap_a1[128];
     alignas(64) unsigned char tmap_a2[128];
+    alignas(64) unsigned char tmap_a1_small[128];   // the same tensors with a 64-row box (batches of at most 64 tokens)
+    alignas(64) unsigned char tmap_a2_small[128];
+    int opt_small_batch_ring = 1;
     alignas(64) unsigned char tmap_y[128];    // GEMM2's staged output stores
     alignas(64) unsigned char tmap_w1[128];
     alignas(64) unsigned char tmap_w2[128];
@@ -328,17 +331,19 @@ int enqueue_layer(moe_fp8_b200_handle h, const moe_fp8_b200_args& a, cudaStream_
     // decode-sized batches may leave most SMs without a tile: there the split-K instantiation
     // (chosen here from T alone, it decides on the device whether to split) spreads the K range
     const int split_k = (T <= 4 && ref_geo) ? 1 : 0;   // 4 = kSplitKMaxRows of the GEMM kernel
+    // at most 64 tokens (an expert then has at most 64 rows): 64-row activation boxes and a fourth operand stage
+    const int small_a = (h->opt_small_batch_ring && T > 4 && T <= 64 && ref_geo) ? 1 : 0;
     // one persistent CTA per SM; CTAs without work leave at once, spare ones take split-K units
     auto ctas = [&](int) { return h->num_sms; };
     if (e == cudaSuccess && stop >= 2) e = launch_permute(a.hidden_states, a.hidden_states_scale, h->ws, T, stream);
     mark(3);
     if (e == cudaSuccess && stop >= 3)
-        e = launch_grouped_gemm(1, h->tmap_a1, tiled ? h->tmap_w1_tiled : h->tmap_w1, h->tmap_y, gemm_ws, h->sw1_packed,
-                                h->opt_exact_silu, ctas(1), split_k, stream);
+        e = launch_grouped_gemm(1, small_a ? h->tmap_a1_small : h->tmap_a1, tiled ? h->tmap_w1_tiled : h->tmap_w1, h->tmap_y,
+                                gemm_ws, h->sw1_packed, h->opt_exact_silu, ctas(1), split_k, small_a, stream);
     mark(4);
     if (e == cudaSuccess && stop >= 4)
-        e = launch_grouped_gemm(2, h->tmap_a2, tiled ? h->tmap_w2_tiled : h->tmap_w2, h->tmap_y, gemm_ws, h->sw2_packed, 0,
-                                ctas(2), split_k, stream);
+        e = launch_grouped_gemm(2, small_a ? h->tmap_a2_small : h->tmap_a2, tiled ? h->tmap_w2_tiled : h->tmap_w2, h->tmap_y,
+                                gemm_ws, h->sw2_packed, 0, ctas(2), split_k, small_a, stream);
     mark(5);
     if (e == cudaSuccess && stop >= 5 && finalize) {
         if (ex) {
@@ -529,6 +534,8 @@ int moe_fp8_b200_create_shaped(moe_fp8_b200_handle* out, int device, int max_tok
         if (tensor_map_bytes() > sizeof(h->tmap_a1)) mr = -100;
         if (mr == 0) mr = encode_kmajor_u8_map(h->tmap_a1, w.a1, h->geo.hidden, L.m_cap, 0, kTileM);
         if (mr == 0) mr = encode_kmajor_u8_map(h->tmap_a2, w.a2, h->geo.inter, L.m_cap, 0, kTileM);
+        if (mr == 0) mr = encode_kmajor_u8_map(h->tmap_a1_small, w.a1, h->geo.hidden, L.m_cap, 0, kTileM / 2);
+        if (mr == 0) mr = encode_kmajor_u8_map(h->tmap_a2_small, w.a2, h->geo.inter, L.m_cap, 0, kTileM / 2);
         if (mr == 0) mr = encode_out_bf16_map(h->tmap_y, w.y, h->geo.hidden, L.m_cap);
     }
     if (e != cudaSuccess || mr != 0) {
@@ -588,6 +595,7 @@ int moe_fp8_b200_set_option(moe_fp8_b200_handle h, int option, int value)
             if (value < 1) return fail(h, MOE_FP8_B200_ERR_INVALID_ARGUMENT, "wait limit must be at least 1 us");
             h->opt_wait_limit_us = value;
             return MOE_FP8_B200_OK;
+        case MOE_FP8_B200_OPT_SMALL_BATCH_RING: h->opt_small_batch_ring = value ? 1 : 0; return MOE_FP8_B200_OK;
         case MOE_FP8_B200_OPT_WEIGHT_PRELAYOUT: {
             const int on = value ? 1 : 0;
             if (on == h->opt_weight_prelayout) return MOE_FP8_B200_OK;

@@ -129,6 +129,12 @@ class MoeLayer:
         if rc != _lib.OK:
             self._raise(rc)
 
+    def set_small_batch_ring(self, on: bool):
+        """Batches of 5 to 64 tokens: 64-row activation boxes and a fourth operand stage in the GEMMs (default on)."""
+        rc = self._lib.moe_fp8_b200_set_option(self._h, _lib.OPT_SMALL_BATCH_RING, int(bool(on)))
+        if rc != _lib.OK:
+            self._raise(rc)
+
     def inject_device_status(self, status: int, stale_barrier_arrivals: int = 0):
         """Host-side failure injection for tests of the error path (see the header)."""
         stream = torch.cuda.current_stream(self.device).cuda_stream

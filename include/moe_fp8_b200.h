@@ -106,7 +106,11 @@ enum {
      * the scale layout (moe_fp8_b200_invalidate_weights drops them).  Results are bit-identical either way.
      * Replaces the reference's per-pointer W1 pre-layout cache (kernel/moe_fp8.cu:981-994, 3007-3014).
      * Default 0.  The decode kernel (batches of at most 8 tokens) always reads the caller's weights. */
-    MOE_FP8_B200_OPT_WEIGHT_PRELAYOUT = 8
+    MOE_FP8_B200_OPT_WEIGHT_PRELAYOUT = 8,
+    /* Batches of 5 to 64 tokens (reference geometry): the GEMMs load 64-row activation boxes (an expert cannot
+     * have more rows) and use the room for a fourth operand stage, i.e. more weight bytes in flight per SM
+     * (default 1).  0 = the three-stage kernel of the larger batches.  Bit-identical results. */
+    MOE_FP8_B200_OPT_SMALL_BATCH_RING = 9
 };
 #define MOE_FP8_B200_DECODE_MAX_TOKENS 8
 

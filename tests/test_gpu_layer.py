@@ -802,3 +802,32 @@ def test_tile_ordered_weight_copies_follow_pointers_and_invalidation(pkg):
         assert torch.equal(run(w1b, w2b), base)
     finally:
         lay.close()
+
+
+@pytest.mark.parametrize("T,offset", [(5, 0), (9, 32), (16, 0), (40, 96), (64, 0), (65, 0)])
+def test_small_batch_ring_changes_nothing(pkg, T, offset):
+    """Batches of 5 to 64 tokens run the GEMMs with 64-row activation boxes and a fourth operand stage
+    (MOE_FP8_B200_OPT_SMALL_BATCH_RING, on by default): same arithmetic in the same order, so the results are
+    bit-identical to the three-stage kernel's.  The handle has seen a larger batch before, so that the rows the
+    64-row boxes leave out hold stale data, not zeros."""
+    w = hp.gpu_shard(offset, 32)
+    lay = pkg.MoeLayer(512, 32, 0)
+    try:
+        lay.set_decode_kernel(False)
+        big = [x.cuda() for x in hp.cpu_inputs(512, seed=6400)]
+        out_big = torch.empty(512, H, dtype=torch.bfloat16, device="cuda")
+        lay.run(*big, *w, offset, RSF, out_big)
+        lay.check()
+        dev = [x.cuda() for x in hp.cpu_inputs(T, seed=6400 + T)]
+        outs = []
+        for on in (True, False, True):
+            lay.set_small_batch_ring(on)
+            out = torch.full((T, H), float("nan"), dtype=torch.bfloat16, device="cuda")
+            lay.run(*dev, *w, offset, RSF, out)
+            lay.check()
+            outs.append(out)
+        assert torch.isfinite(outs[0].float()).all() and outs[0].float().abs().sum() > 0
+        for o in outs[1:]:
+            assert torch.equal(o.view(torch.int16), outs[0].view(torch.int16))
+    finally:
+        lay.close()
