@@ -187,6 +187,8 @@ def test_python_binding_constants_match_the_header(pkg):
     assert int(consts["MOE_FP8_B200_OPT_DECODE_KERNEL"]) == L.OPT_DECODE_KERNEL
     assert int(consts["MOE_FP8_B200_OPT_EXPERT_STRIDE"]) == L.OPT_EXPERT_STRIDE
     assert int(consts["MOE_FP8_B200_OPT_WAIT_LIMIT_US"]) == L.OPT_WAIT_LIMIT_US
+    assert int(consts["MOE_FP8_B200_OPT_WEIGHT_PRELAYOUT"]) == L.OPT_WEIGHT_PRELAYOUT
+    assert int(consts["MOE_FP8_B200_OPT_SMALL_BATCH_RING"]) == L.OPT_SMALL_BATCH_RING
     for name, val in L.BUF.items():
         assert int(consts["MOE_FP8_B200_BUF_" + name.upper()]) == val, name
     assert int(re.search(r"MOE_FP8_B200_DECODE_MAX_TOKENS\s+(\d+)", txt).group(1)) == L.DECODE_MAX_TOKENS
