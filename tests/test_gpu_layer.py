@@ -752,7 +752,7 @@ def test_weight_scale_prelayout_follows_pointers_and_invalidation(pkg, layer32):
     layer32.invalidate_weights()
 
 
-@pytest.mark.parametrize("T,offset", [(9, 0), (40, 32), (300, 96), (1024, 0)])
+@pytest.mark.parametrize("T,offset", [(3, 96), (9, 0), (40, 32), (300, 96), (1024, 0)])
 def test_tile_ordered_weight_copies_change_nothing(pkg, T, offset):
     """MOE_FP8_B200_OPT_WEIGHT_PRELAYOUT: the GEMMs read the weights from the handle's tile-ordered copies (one
     contiguous 32 KB piece per tile and K block) and every bit of the result stays the same, also after the option
