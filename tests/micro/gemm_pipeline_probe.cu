@@ -1,8 +1,7 @@
 // Micro-benchmark of the grouped GEMM's inner pipeline on ONE SM (or one CTA on each of N SMs), without
 // real data and (but for the *_tma forms) without TMA: the MMA-issuing thread, the two 256-column TMEM accumulator stages and the
 // eight promotion warps with the kernel's own handshake (ptx.cuh of the package).  It reports SM cycles
-// per 128-wide K block for a few forms of the loop, which is where the figures quoted in the design notes
-// about the promotion pipeline come from:
+// per 128-wide K block (and the wall time) for a few forms of the loop:
 //   mma_only            4 x tcgen05.mma M128 N256 K32 per K block, promotion warps release the stage at once
 //   mma_only_n128       the same block issued as 8 x M128 N128 K32 (what a finer accumulator split would need)
 //   drain               promotion warps read the whole stage from TMEM (4 x 32 columns each), no arithmetic

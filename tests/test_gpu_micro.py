@@ -1,6 +1,6 @@
 """Micro-benchmark of the grouped GEMM's MMA <-> promotion pipeline (tests/micro/gemm_pipeline_probe.cu),
-compiled with nvcc and run on one SM: it is where the per-K-block cycle figures of the design notes come
-from, and it guards the handshake of ptx.cuh (bounded waits, TMEM allocation and release) in isolation."""
+compiled with nvcc and run on one SM: it gives the cycles per K block of each part of the loop in isolation
+and guards the handshake of ptx.cuh (bounded waits, TMEM allocation and release) in isolation."""
 import re
 import shutil
 import subprocess
@@ -31,7 +31,7 @@ def test_gemm_pipeline_probe(tmp_path):
     assert cyc["mma_only_n128"] >= cyc["mma_only"], cyc
     # the operand ring's barrier work on the issuing thread is not hidden by the tensor pipe ...
     assert cyc["ring"] > cyc["promote_packed"] + 100, cyc
-    # ... and a second issuing thread takes most of it back (in this probe; see the design notes for the kernel)
+    # ... and a second issuing thread takes most of it back (in this probe; the kernel itself did not gain from one)
     assert cyc["ring_scales_two"] < cyc["ring_scales"] - 100, cyc
     assert cyc["ring_scales_relayed"] < cyc["ring_scales"], cyc
     # a real TMA producer behind the ring (48 KB per K block) changes little: the data movement is not the cost
